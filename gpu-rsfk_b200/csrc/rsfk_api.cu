@@ -1,0 +1,431 @@
+// C ABI of librsfk.so (declarations and reference citations: include/rsfk_b200.h).
+#include <algorithm>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/rsfk_b200.h"
+#include "rsfk_context.h"
+
+using rsfk::Context;
+using rsfk::TreeResult;
+
+struct rsfk_ctx {
+    Context c;
+    TreeResult tree;
+    bool has_tree = false;
+};
+
+namespace {
+
+std::mutex g_mutex;
+rsfk_ctx* g_default = nullptr; // context behind the host-pointer entry points
+int g_last_status = RSFK_OK;
+std::string g_last_message;
+
+double now_s()
+{
+    return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+rsfk_ctx* make_ctx(int device, void* stream, bool private_stream)
+{
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        fprintf(stderr, "rsfk: no CUDA device available\n");
+        return nullptr;
+    }
+    if (device < 0 || device >= count) {
+        fprintf(stderr, "rsfk: device %d out of range\n", device);
+        return nullptr;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) return nullptr;
+    rsfk_ctx* h = new rsfk_ctx();
+    h->c.device = device;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) h->c.sm_count = prop.multiProcessorCount;
+    if (!private_stream) {
+        h->c.stream = (cudaStream_t)stream; // NULL is the legacy default stream
+        h->c.owns_stream = false;
+    } else {
+        if (cudaStreamCreateWithFlags(&h->c.stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete h;
+            return nullptr;
+        }
+        h->c.owns_stream = true;
+    }
+    return h;
+}
+
+rsfk_ctx* default_ctx()
+{
+    if (!g_default) {
+        int device = 0;
+        if (const char* e = getenv("RSFK_DEVICE")) device = atoi(e);
+        g_default = make_ctx(device, nullptr, true);
+    }
+    if (g_default) {
+        cudaSetDevice(g_default->c.device);
+        g_default->c.status = RSFK_OK;
+        g_default->c.message.clear();
+    }
+    return g_default;
+}
+
+void publish(const Context& c)
+{
+    g_last_status = c.status;
+    g_last_message = c.message;
+}
+
+// Trees + bucket KNN into canonical device lists; fills the ForestLog rows.
+bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_trees, int first_tree,
+                int tree_stride, int min_children, int max_children, int max_depth, int seed,
+                int* d_idx, float* d_dist, float* log_forest, int verbose)
+{
+    Context& c = h->c;
+    std::vector<cudaEvent_t> ev;
+    if (log_forest) {
+        memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
+        ev.resize(2 * (size_t)n_trees);
+        for (auto& e : ev) cudaEventCreate(&e);
+    }
+    const double t0 = now_s();
+    bool ok = true;
+    for (int i = 0; i < n_trees && ok; ++i) {
+        const int t = first_tree + i * tree_stride;
+        const double tb0 = now_s();
+        ok = rsfk::tree_build(c, d_points, N, D, min_children, max_children, max_depth, seed + t,
+                              nullptr, 0, h->tree);
+        h->has_tree = ok;
+        const double tb1 = now_s();
+        if (!ok) break;
+        if (log_forest) cudaEventRecord(ev[2 * i], c.stream);
+        ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist);
+        if (log_forest) {
+            cudaEventRecord(ev[2 * i + 1], c.stream);
+            log_forest[0 * n_trees + i] = (float)h->tree.levels;
+            log_forest[1 * n_trees + i] = (float)h->tree.max_leaf;
+            log_forest[2 * n_trees + i] = (float)h->tree.min_leaf;
+            log_forest[3 * n_trees + i] = (float)h->tree.n_leaves;
+            log_forest[5 * n_trees + i] = (float)(tb1 - tb0);
+        }
+        if (verbose >= 2)
+            printf("tree %d: depth %d, leaves %d, leaf size %d..%d, build %.6f s\n", t, h->tree.levels,
+                   h->tree.n_leaves, h->tree.min_leaf, h->tree.max_leaf, tb1 - tb0);
+    }
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
+    if (log_forest) {
+        if (ok)
+            for (int i = 0; i < n_trees; ++i) {
+                float ms = 0.0f;
+                if (cudaEventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]) == cudaSuccess)
+                    log_forest[15 * n_trees + i] = ms * 1e-3f;
+            }
+        for (auto& e : ev) cudaEventDestroy(e);
+        log_forest[16 * n_trees] = (float)(now_s() - t0);
+    }
+    return ok;
+}
+
+bool run_sweeps(rsfk_ctx* h, const float* d_points, int N, int D, int K, int sweeps, int* d_idx,
+                float* d_dist)
+{
+    Context& c = h->c;
+    if (sweeps <= 0) return true;
+    int* snap = (int*)c.scratch(Context::SNAPSHOT, sizeof(int) * (size_t)N * K);
+    if (!snap) return false;
+    for (int s = 0; s < sweeps; ++s) {
+        if (!c.check(cudaMemcpyAsync(snap, d_idx, sizeof(int) * (size_t)N * K, cudaMemcpyDeviceToDevice,
+                                     c.stream), "snapshot"))
+            return false;
+        if (!rsfk::explore_sweep(c, d_points, N, D, K, snap, d_idx, d_dist, 0, N)) return false;
+    }
+    return true;
+}
+
+} // namespace
+
+extern "C" {
+
+int rsfk_last_status(void) { return g_last_status; }
+const char* rsfk_last_message(void) { return g_last_message.c_str(); }
+void rsfk_free(void* p) { free(p); }
+int rsfk_max_neighbors(void) { return rsfk::list_capacity(); }
+
+long long rsfk_kernel_launches(void) { return rsfk::g_kernel_launches.load(); }
+
+void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TREE_CHILD,
+                       int MAX_TREE_CHILD, int MAX_DEPTH, int VERBOSE, int RANDOM_STATE,
+                       int nn_exploring_factor, float* points, int* knn_indices,
+                       float* knn_sqr_distances, float* log_forest)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    rsfk_ctx* h = default_ctx();
+    if (!h) {
+        g_last_status = RSFK_ERR_CUDA;
+        g_last_message = "no usable CUDA device";
+        return;
+    }
+    Context& c = h->c;
+    const int K = num_neighbors;
+    if (N <= 0 || D <= 0 || K <= 0 || n_trees < 0 || !points || !knn_indices || !knn_sqr_distances) {
+        c.fail(RSFK_ERR_ARG, "pymodule_rsfk_knn: invalid argument");
+        publish(c);
+        return;
+    }
+    if (K > rsfk::list_capacity()) {
+        c.fail(RSFK_ERR_UNSUPPORTED, "pymodule_rsfk_knn: K above 256 is not supported");
+        publish(c);
+        return;
+    }
+    const size_t pts_bytes = sizeof(float) * (size_t)N * D, list_elems = (size_t)N * K;
+    float* d_points = nullptr;
+    int* d_idx = nullptr;
+    float* d_dist = nullptr;
+    bool ok = c.check(cudaMalloc((void**)&d_points, pts_bytes), "cudaMalloc(points)") &&
+              c.check(cudaMalloc((void**)&d_idx, sizeof(int) * list_elems), "cudaMalloc(indices)") &&
+              c.check(cudaMalloc((void**)&d_dist, sizeof(float) * list_elems), "cudaMalloc(distances)");
+    ok = ok && c.check(cudaMemcpyAsync(d_points, points, pts_bytes, cudaMemcpyHostToDevice, c.stream), "H2D points");
+    ok = ok && c.check(cudaMemcpyAsync(d_idx, knn_indices, sizeof(int) * list_elems, cudaMemcpyHostToDevice, c.stream), "H2D indices");
+    ok = ok && c.check(cudaMemcpyAsync(d_dist, knn_sqr_distances, sizeof(float) * list_elems, cudaMemcpyHostToDevice, c.stream), "H2D distances");
+    ok = ok && rsfk::sort_rows(c, d_idx, d_dist, N, K);
+    const double t0 = now_s();
+    ok = ok && run_forest(h, d_points, N, D, K, n_trees, 0, 1, MIN_TREE_CHILD, MAX_TREE_CHILD, MAX_DEPTH,
+                          RANDOM_STATE, d_idx, d_dist, log_forest, VERBOSE);
+    const double t1 = now_s();
+    if (ok && VERBOSE >= 1) printf("Creating RSFK forest takes %lf seconds\n", t1 - t0);
+    ok = ok && run_sweeps(h, d_points, N, D, K, nn_exploring_factor, d_idx, d_dist);
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "exploration");
+    const double t2 = now_s();
+    if (ok && VERBOSE >= 1)
+        printf("Nearest Neighbors Exploring computation Kernel takes %lf seconds\n", t2 - t1);
+    if (ok && log_forest) log_forest[16 * n_trees + 1] = (float)(t2 - t1);
+    // outputs are written only when every step succeeded
+    ok = ok && c.check(cudaMemcpyAsync(knn_indices, d_idx, sizeof(int) * list_elems, cudaMemcpyDeviceToHost, c.stream), "D2H indices");
+    ok = ok && c.check(cudaMemcpyAsync(knn_sqr_distances, d_dist, sizeof(float) * list_elems, cudaMemcpyDeviceToHost, c.stream), "D2H distances");
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "D2H");
+    cudaStreamSynchronize(c.stream);
+    if (d_points) cudaFree(d_points);
+    if (d_idx) cudaFree(d_idx);
+    if (d_dist) cudaFree(d_dist);
+    publish(c);
+}
+
+void pymodule_cluster_by_sample_tree(int N, int D, int MIN_TREE_CHILD, int MAX_TREE_CHILD,
+                                     int MAX_DEPTH, int VERBOSE, int RANDOM_STATE, float* points,
+                                     int** nodes_buckets, int** bucket_sizes, int* total_leaves,
+                                     int* max_child)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    rsfk_ctx* h = default_ctx();
+    if (!h) {
+        g_last_status = RSFK_ERR_CUDA;
+        g_last_message = "no usable CUDA device";
+        return;
+    }
+    Context& c = h->c;
+    if (N <= 0 || D <= 0 || !points || !nodes_buckets || !bucket_sizes || !total_leaves || !max_child) {
+        c.fail(RSFK_ERR_ARG, "pymodule_cluster_by_sample_tree: invalid argument");
+        publish(c);
+        return;
+    }
+    const double t0 = now_s();
+    float* d_points = nullptr;
+    bool ok = c.check(cudaMalloc((void**)&d_points, sizeof(float) * (size_t)N * D), "cudaMalloc(points)");
+    ok = ok && c.check(cudaMemcpyAsync(d_points, points, sizeof(float) * (size_t)N * D, cudaMemcpyHostToDevice, c.stream), "H2D points");
+    ok = ok && rsfk::tree_build(c, d_points, N, D, MIN_TREE_CHILD, MAX_TREE_CHILD, MAX_DEPTH, RANDOM_STATE,
+                                nullptr, 0, h->tree);
+    h->has_tree = ok;
+    if (ok) {
+        const TreeResult& t = h->tree;
+        std::vector<int> perm(N), ls(t.n_leaves), lc(t.n_leaves);
+        ok = c.check(cudaMemcpyAsync(perm.data(), t.perm, sizeof(int) * (size_t)N, cudaMemcpyDeviceToHost, c.stream), "D2H perm") &&
+             c.check(cudaMemcpyAsync(ls.data(), t.leaf_start, sizeof(int) * (size_t)t.n_leaves, cudaMemcpyDeviceToHost, c.stream), "D2H leaves") &&
+             c.check(cudaMemcpyAsync(lc.data(), t.leaf_count, sizeof(int) * (size_t)t.n_leaves, cudaMemcpyDeviceToHost, c.stream), "D2H leaves") &&
+             c.check(cudaStreamSynchronize(c.stream), "D2H tree");
+        if (ok) {
+            std::vector<int> order(t.n_leaves);
+            for (int i = 0; i < t.n_leaves; ++i) order[i] = i;
+            std::sort(order.begin(), order.end(), [&](int a, int b) { return ls[a] < ls[b]; });
+            const int mc = t.max_leaf;
+            int* table = (int*)malloc(sizeof(int) * (size_t)std::max(1, t.n_leaves) * (size_t)std::max(1, mc));
+            int* sizes = (int*)malloc(sizeof(int) * (size_t)std::max(1, t.n_leaves));
+            if (!table || !sizes) {
+                free(table);
+                free(sizes);
+                ok = c.fail(RSFK_ERR_NOMEM, "pymodule_cluster_by_sample_tree: malloc failed");
+            } else {
+                for (int b = 0; b < t.n_leaves; ++b) {
+                    const int s = ls[order[b]], n = lc[order[b]];
+                    sizes[b] = n;
+                    memcpy(table + (size_t)b * mc, perm.data() + s, sizeof(int) * (size_t)n);
+                    for (int k = n; k < mc; ++k) table[(size_t)b * mc + k] = -1;
+                }
+                *nodes_buckets = table;
+                *bucket_sizes = sizes;
+                *total_leaves = t.n_leaves;
+                *max_child = mc;
+                if (VERBOSE >= 1) {
+                    printf("Tree depth: %d\nMax child count: %d\nMin child count: %d\nTotal leaves: %d\n",
+                           t.levels, t.max_leaf, t.min_leaf, t.n_leaves);
+                    printf("Creating cluster with one tree takes %lf seconds\n", now_s() - t0);
+                }
+            }
+        }
+    }
+    cudaStreamSynchronize(c.stream);
+    if (d_points) cudaFree(d_points);
+    publish(c);
+}
+
+void pymodule_rsfk_knn_ann(int, int, int, int, int, int, int, int, int, int, int, float*, float*, int*,
+                           float*, float*)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_last_status = RSFK_ERR_UNSUPPORTED;
+    g_last_message = "pymodule_rsfk_knn_ann: the base/query path is not part of this library";
+    fprintf(stderr, "rsfk: %s\n", g_last_message.c_str());
+}
+
+// ------------------------------------------------------------------ part 3 --
+
+rsfk_ctx* rsfk_ctx_create(int device, void* stream) { return make_ctx(device, stream, false); }
+
+void rsfk_ctx_destroy(rsfk_ctx* ctx)
+{
+    if (!ctx) return;
+    cudaSetDevice(ctx->c.device);
+    cudaStreamSynchronize(ctx->c.stream);
+    ctx->c.release();
+    delete ctx;
+}
+
+int rsfk_ctx_status(const rsfk_ctx* ctx) { return ctx ? ctx->c.status : RSFK_ERR_ARG; }
+
+int rsfk_ctx_synchronize(rsfk_ctx* ctx)
+{
+    if (!ctx) return RSFK_ERR_ARG;
+    ctx->c.check(cudaStreamSynchronize(ctx->c.stream), "synchronize");
+    return ctx->c.status;
+}
+
+#define RSFK_ENTER(ctx)                   \
+    if (!(ctx)) return RSFK_ERR_ARG;      \
+    cudaSetDevice((ctx)->c.device);       \
+    (ctx)->c.status = RSFK_OK;            \
+    (ctx)->c.message.clear();
+
+int rsfk_dev_sort_rows(rsfk_ctx* ctx, int* d_idx, float* d_dist, long long rows, int K)
+{
+    RSFK_ENTER(ctx);
+    rsfk::sort_rows(ctx->c, d_idx, d_dist, rows, K);
+    return ctx->c.status;
+}
+
+int rsfk_dev_tree_build(rsfk_ctx* ctx, const float* d_points, int N, int D, int min_children,
+                        int max_children, int max_depth, int seed, const int* d_table, int n_table,
+                        int* n_leaves, int* max_leaf, int* min_leaf, int* levels)
+{
+    RSFK_ENTER(ctx);
+    ctx->has_tree = rsfk::tree_build(ctx->c, d_points, N, D, min_children, max_children, max_depth, seed,
+                                     d_table, n_table, ctx->tree);
+    if (ctx->has_tree) {
+        if (n_leaves) *n_leaves = ctx->tree.n_leaves;
+        if (max_leaf) *max_leaf = ctx->tree.max_leaf;
+        if (min_leaf) *min_leaf = ctx->tree.min_leaf;
+        if (levels) *levels = ctx->tree.levels;
+    }
+    return ctx->c.status;
+}
+
+int rsfk_dev_tree_export(rsfk_ctx* ctx, int N, int* perm, int* leaf_start, int* leaf_count)
+{
+    RSFK_ENTER(ctx);
+    Context& c = ctx->c;
+    if (!ctx->has_tree) {
+        c.fail(RSFK_ERR_ARG, "rsfk_dev_tree_export: no tree in this context");
+        return c.status;
+    }
+    const TreeResult& t = ctx->tree;
+    std::vector<int> ls(t.n_leaves), lc(t.n_leaves);
+    bool ok = c.check(cudaMemcpyAsync(perm, t.perm, sizeof(int) * (size_t)N, cudaMemcpyDeviceToHost, c.stream), "D2H perm") &&
+              c.check(cudaMemcpyAsync(ls.data(), t.leaf_start, sizeof(int) * (size_t)t.n_leaves, cudaMemcpyDeviceToHost, c.stream), "D2H leaves") &&
+              c.check(cudaMemcpyAsync(lc.data(), t.leaf_count, sizeof(int) * (size_t)t.n_leaves, cudaMemcpyDeviceToHost, c.stream), "D2H leaves") &&
+              c.check(cudaStreamSynchronize(c.stream), "D2H tree");
+    if (ok) {
+        std::vector<int> order(t.n_leaves);
+        for (int i = 0; i < t.n_leaves; ++i) order[i] = i;
+        std::sort(order.begin(), order.end(), [&](int a, int b) { return ls[a] < ls[b]; });
+        for (int b = 0; b < t.n_leaves; ++b) {
+            leaf_start[b] = ls[order[b]];
+            leaf_count[b] = lc[order[b]];
+        }
+    }
+    return c.status;
+}
+
+int rsfk_dev_bucket_knn(rsfk_ctx* ctx, const float* d_points, int N, int D, int K, int* d_idx,
+                        float* d_dist)
+{
+    RSFK_ENTER(ctx);
+    if (!ctx->has_tree) {
+        ctx->c.fail(RSFK_ERR_ARG, "rsfk_dev_bucket_knn: no tree in this context");
+        return ctx->c.status;
+    }
+    rsfk::bucket_knn(ctx->c, d_points, N, D, K, ctx->tree, d_idx, d_dist);
+    return ctx->c.status;
+}
+
+int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, int N, int D, int K,
+                              const int* d_perm, const int* d_leaf_start, const int* d_leaf_count,
+                              int n_leaves, int max_leaf, int* d_idx, float* d_dist)
+{
+    RSFK_ENTER(ctx);
+    TreeResult t;
+    t.perm = d_perm;
+    t.leaf_start = d_leaf_start;
+    t.leaf_count = d_leaf_count;
+    t.n_leaves = n_leaves;
+    t.max_leaf = max_leaf;
+    rsfk::bucket_knn(ctx->c, d_points, N, D, K, t, d_idx, d_dist);
+    return ctx->c.status;
+}
+
+int rsfk_dev_forest(rsfk_ctx* ctx, const float* d_points, int N, int D, int K, int n_trees,
+                    int first_tree, int tree_stride, int min_children, int max_children,
+                    int max_depth, int seed, int* d_idx, float* d_dist, float* log_forest)
+{
+    RSFK_ENTER(ctx);
+    if (N <= 0 || D <= 0 || K <= 0 || n_trees < 0 || tree_stride < 1) {
+        ctx->c.fail(RSFK_ERR_ARG, "rsfk_dev_forest: invalid argument");
+        return ctx->c.status;
+    }
+    run_forest(ctx, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children, max_children,
+               max_depth, seed, d_idx, d_dist, log_forest, 0);
+    return ctx->c.status;
+}
+
+int rsfk_dev_explore(rsfk_ctx* ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
+                     int* d_idx, float* d_dist, int row_begin, int row_end)
+{
+    RSFK_ENTER(ctx);
+    if (row_begin < 0 || row_end > N || row_begin > row_end) {
+        ctx->c.fail(RSFK_ERR_ARG, "rsfk_dev_explore: invalid row range");
+        return ctx->c.status;
+    }
+    rsfk::explore_sweep(ctx->c, d_points, N, D, K, d_old_idx, d_idx, d_dist, row_begin, row_end);
+    return ctx->c.status;
+}
+
+int rsfk_dev_merge_lists(rsfk_ctx* ctx, long long rows, int K, int G, const int* const* d_idx_lists,
+                         const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist)
+{
+    RSFK_ENTER(ctx);
+    rsfk::merge_lists(ctx->c, rows, K, G, d_idx_lists, d_dist_lists, d_out_idx, d_out_dist);
+    return ctx->c.status;
+}
+
+} // extern "C"

@@ -1,0 +1,120 @@
+// Host-side context of the sm_100a RSFK library: one device, one stream, a
+// grow-only pool of scratch buffers (no allocation inside the per-tree loop),
+// pinned mailboxes for the few counters the host reads back, and the status
+// word the C ABI exposes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <atomic>
+#include <string>
+#include <vector>
+
+#include "rsfk_common.cuh"
+
+namespace rsfk {
+
+// kernels of this library launched so far in this process
+inline std::atomic<long long> g_kernel_launches{0};
+inline void count_launches(int n) { g_kernel_launches.fetch_add(n, std::memory_order_relaxed); }
+
+struct Buffer {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+// Active node of the level being split.  Its points are perm[start, start+count).
+// The split pair is drawn from perm[pstart, pstart+pcount) (the node's own
+// segment before a sibling was merged into it).
+struct Node {
+    int start, count;
+    int pstart, pcount;
+    int tbl;        // row of the replay table, or -1
+    int chunk_base; // first work chunk of this node in the level's chunk list
+    int pad0, pad1;
+};
+
+struct LevelCounters {
+    int n_nodes_next;
+    int n_chunks_next;
+    int n_leaves;
+    int max_leaf;
+    int min_leaf;
+    int error;
+    int pad0, pad1;
+};
+
+struct TreeResult {
+    const int* perm = nullptr;       // device, [N]: points ordered by leaf
+    const int* leaf_start = nullptr; // device, [n_leaves] (unordered)
+    const int* leaf_count = nullptr; // device, [n_leaves]
+    int n_leaves = 0;
+    int max_leaf = 0;
+    int min_leaf = 0;
+    int levels = 0;
+};
+
+struct Context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 148;
+    int status = RSFK_OK;
+    std::string message;
+
+    enum Slot {
+        PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
+        NODES_A, NODES_B, NODE_SPLIT, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
+        SNAPSHOT, N_SLOTS
+    };
+    Buffer slots[N_SLOTS];
+    LevelCounters* host_counters = nullptr; // pinned
+
+    bool fail(int code, const std::string& msg)
+    {
+        if (status == RSFK_OK) { status = code; message = msg; }
+        fprintf(stderr, "rsfk: %s\n", msg.c_str());
+        return false;
+    }
+    bool check(cudaError_t e, const char* what)
+    {
+        if (e == cudaSuccess) return true;
+        return fail(RSFK_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    // grow-only scratch; contents are not preserved across growth
+    void* scratch(Slot s, size_t bytes)
+    {
+        Buffer& b = slots[s];
+        if (b.bytes >= bytes && b.ptr) return b.ptr;
+        if (b.ptr) cudaFree(b.ptr);
+        b.ptr = nullptr;
+        b.bytes = 0;
+        size_t want = bytes + bytes / 8 + 256;
+        if (!check(cudaMalloc(&b.ptr, want), "cudaMalloc(scratch)")) { status = RSFK_ERR_NOMEM; return nullptr; }
+        b.bytes = want;
+        return b.ptr;
+    }
+    void release()
+    {
+        for (auto& b : slots) { if (b.ptr) cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
+        if (host_counters) { cudaFreeHost(host_counters); host_counters = nullptr; }
+        if (owns_stream && stream) { cudaStreamDestroy(stream); stream = nullptr; }
+    }
+};
+
+// rsfk_tree.cu
+bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_children,
+                int max_children, int max_depth, int seed, const int* d_table, int n_table,
+                TreeResult& out);
+
+// rsfk_knn.cu
+int list_capacity();                      // largest supported K
+bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K);
+bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
+                int* d_idx, float* d_dist);
+bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
+                   int* d_idx, float* d_dist, int row_begin, int row_end);
+bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,
+                 const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist);
+
+} // namespace rsfk

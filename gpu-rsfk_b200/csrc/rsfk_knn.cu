@@ -1,0 +1,479 @@
+// K-list kernels for sm_100a: canonical row sort, leaf-bucket all-pairs KNN,
+// neighbour-of-neighbour exploration and the G-way list merge used when trees
+// are sharded across GPUs.
+//
+// Every K-list row in device memory is kept canonical: ascending by
+// (squared distance, index), distinct indices, unused slots (+inf, -1).  A
+// row update is "the K smallest distinct of row + candidates", which equals
+// the reference's replace-the-worst-slot rule
+// (src/kernels/compute_knn_from_buckets.cu:1205-1285,
+//  src/kernels/nearest_neighbors_exploring.cu:83-141) whenever no two
+// competing distances tie; ties go to the lower index here.
+//
+// Squared distances keep the reference's summation order (term i in lane i%32,
+// fused multiply-add, xor butterfly), so their bits equal the reference's.
+#include "rsfk_context.h"
+
+namespace rsfk {
+
+constexpr int KNN_THREADS = 256;
+constexpr int KNN_WARPS = KNN_THREADS / 32;
+constexpr int MAX_KPL = 8; // K <= 256
+
+int list_capacity() { return 32 * MAX_KPL; }
+
+// ---------------------------------------------------------------------------
+// sort_rows: one warp per row; entries are inserted in slot order into an
+// empty list, so the first occurrence of a repeated index wins.
+// ---------------------------------------------------------------------------
+template <int KPL>
+__global__ void __launch_bounds__(KNN_THREADS)
+k_sort_rows(int* __restrict__ idx, float* __restrict__ dist, long long rows, int K)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long row = warp0; row < rows; row += n_warps) {
+        int* gi = idx + row * K;
+        float* gd = dist + row * K;
+        float rd[KPL];
+        int ri[KPL];
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            int e = r * 32 + lane;
+            rd[r] = e < K ? gd[e] : CUDART_INF_F;
+            ri[r] = e < K ? gi[e] : -1;
+        }
+        WarpList<KPL> L;
+        L.clear();
+        bool sorted = true; // already canonical? then nothing to write
+        float pd = -1.0f;
+        int pi = -1;
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            for (int b = 0; b < 32; ++b) {
+                if (r * 32 + b >= K) break;
+                float cd = __shfl_sync(RSFK_FULL, rd[r], b);
+                int ci = __shfl_sync(RSFK_FULL, ri[r], b);
+                if (ci < 0) {
+                    if (!(cd == CUDART_INF_F)) sorted = false;
+                    pd = CUDART_INF_F; pi = -1;
+                    continue;
+                }
+                if (!key_less(pd, pi, cd, ci)) sorted = false;
+                pd = cd; pi = ci;
+                if (!L.try_insert(cd, ci, K, lane)) sorted = false; // repeated index
+            }
+        }
+        if (!sorted) L.store(gi, gd, K, lane);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Leaf-bucket KNN.
+//
+// One CTA per leaf.  The leaf's rows are processed in blocks of B rows; for a
+// block pair (I, J >= I) the rows are staged in shared memory, the B x B tile
+// of squared distances is computed by warps in 4x4 register tiles (lane l owns
+// dimensions l, l+32, ...; a transposed butterfly yields 16 distances per
+// warp step in the reference's bit pattern), and then every row of I merges
+// the tile row into its K-list (and, for J != I, every row of J the tile
+// column).  Leaves that fit one block (the common case) stage each row once.
+// ---------------------------------------------------------------------------
+template <int KPL>
+__device__ __forceinline__ void merge_candidates(WarpList<KPL>& L, const float* cand_d, int cand_stride,
+                                                 const int* cand_ids, int n_cand, int self_id, int K,
+                                                 int lane, bool& changed)
+{
+    for (int c0 = 0; c0 < n_cand; c0 += 32) {
+        const int j = c0 + lane;
+        float cd = CUDART_INF_F;
+        int ci = -1;
+        if (j < n_cand) {
+            cd = cand_d[(size_t)j * cand_stride];
+            ci = cand_ids[j];
+        }
+        bool pass = (j < n_cand) && ci != self_id && L.beats_threshold(cd, ci);
+        unsigned mask = __ballot_sync(RSFK_FULL, pass);
+        while (mask) {
+            const int b = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const float d = __shfl_sync(RSFK_FULL, cd, b);
+            const int id = __shfl_sync(RSFK_FULL, ci, b);
+            changed |= L.try_insert(d, id, K, lane);
+        }
+    }
+}
+
+__device__ __forceinline__ void stage_rows(const float* __restrict__ pts, int D, const int* ids, int n,
+                                           float* X, int warp, int lane)
+{
+    for (int r = warp; r < n; r += KNN_WARPS) {
+        const float* src = pts + (size_t)ids[r] * D;
+        float* dst = X + (size_t)r * D;
+        for (int k = lane; k < D; k += 32) dst[k] = __ldg(src + k);
+    }
+}
+
+template <int KPL>
+__global__ void __launch_bounds__(KNN_THREADS)
+k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict__ perm,
+             const int* __restrict__ leaf_start, const int* __restrict__ leaf_count,
+             int* __restrict__ knn_idx, float* __restrict__ knn_dist, int B, int two_blocks)
+{
+    extern __shared__ float smem[];
+    // layout: tile[B][B+1] | XI[B][D] | XJ[B][D] (only when two_blocks) | idsI[B] | idsJ[B]
+    const int TS = B + 1;
+    float* tile = smem;
+    float* XI = tile + (size_t)B * TS;
+    float* XJ = two_blocks ? XI + (size_t)B * D : XI;
+    int* idsI = (int*)(XJ + (size_t)B * D);
+    int* idsJ = two_blocks ? idsI + B : idsI;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int leaf = blockIdx.x;
+    const int m = leaf_count[leaf];
+    const int* ids = perm + leaf_start[leaf];
+    const int n_blocks = (m + B - 1) / B;
+
+    for (int bi = 0; bi < n_blocks; ++bi) {
+        const int i0 = bi * B, mI = min(B, m - i0);
+        __syncthreads();
+        for (int r = threadIdx.x; r < mI; r += blockDim.x) idsI[r] = ids[i0 + r];
+        __syncthreads();
+        stage_rows(pts, D, idsI, mI, XI, warp, lane);
+        for (int bj = bi; bj < n_blocks; ++bj) {
+            const int j0 = bj * B, mJ = min(B, m - j0);
+            const bool diag = (bj == bi);
+            if (!diag) {
+                __syncthreads();
+                for (int r = threadIdx.x; r < mJ; r += blockDim.x) idsJ[r] = ids[j0 + r];
+                __syncthreads();
+                stage_rows(pts, D, idsJ, mJ, XJ, warp, lane);
+            }
+            __syncthreads();
+            const float* XJc = diag ? XI : XJ;
+            const int* idsJc = diag ? idsI : idsJ;
+            // ---- distance tile ------------------------------------------------
+            const int tI = (mI + 3) >> 2, tJ = (mJ + 3) >> 2;
+            for (int t = warp; t < tI * tJ; t += KNN_WARPS) {
+                const int ti = t / tJ, tj = t - ti * tJ;
+                if (diag && tj < ti) continue;
+                const float* xi[4];
+                const float* xj[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    xi[u] = XI + (size_t)min(ti * 4 + u, mI - 1) * D;
+                    xj[u] = XJc + (size_t)min(tj * 4 + u, mJ - 1) * D;
+                }
+                float acc[16];
+#pragma unroll
+                for (int q = 0; q < 16; ++q) acc[q] = 0.0f;
+                for (int k = lane; k < D; k += 32) {
+                    float a[4], b[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { a[u] = xi[u][k]; b[u] = xj[u][k]; }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const float df = __fsub_rn(a[u], b[v]);
+                            acc[u * 4 + v] = __fmaf_rn(df, df, acc[u * 4 + v]);
+                        }
+                }
+                const float dsum = transposed_sum16(acc, lane);
+                const int item = item16_of_lane(lane);
+                const int r = ti * 4 + (item >> 2), c = tj * 4 + (item & 3);
+                if (lane < 16 && r < mI && c < mJ) {
+                    tile[r * TS + c] = dsum;
+                    if (diag) tile[c * TS + r] = dsum;
+                }
+            }
+            __syncthreads();
+            // ---- rows of block I take the tile row ----------------------------
+            for (int r = warp; r < mI; r += KNN_WARPS) {
+                const int self = idsI[r];
+                WarpList<KPL> L;
+                L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                bool changed = false;
+                merge_candidates<KPL>(L, tile + r * TS, 1, idsJc, mJ, self, K, lane, changed);
+                if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+            }
+            // ---- rows of block J take the tile column -------------------------
+            if (!diag) {
+                for (int r = warp; r < mJ; r += KNN_WARPS) {
+                    const int self = idsJ[r];
+                    WarpList<KPL> L;
+                    L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                    bool changed = false;
+                    merge_candidates<KPL>(L, tile + r, TS, idsI, mI, self, K, lane, changed);
+                    if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Exploration sweep: one warp per point.  Candidates old[old[p][i]][k] that
+// are not already in p's row are queued; every 32 queued candidates are
+// evaluated together (each lane owns dimensions lane, lane+32, ... of all 32
+// rows, a transposed butterfly leaves candidate c's distance in one lane).
+// ---------------------------------------------------------------------------
+constexpr int EXP_QUEUE = 64;
+
+template <int KPL>
+__device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __restrict__ pts, int D,
+                                              const float* xp, int* queue, int n, int K, int lane,
+                                              bool& changed)
+{
+    // n in [1,32] candidates at queue[0..n)
+    float acc[32];
+    const float* row[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+        acc[c] = 0.0f;
+        row[c] = pts + (size_t)queue[min(c, n - 1)] * D;
+    }
+    for (int k = lane; k < D; k += 32) {
+        const float x = xp[k];
+        float v[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = __ldg(row[c] + k);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            const float df = __fsub_rn(v[c], x);
+            acc[c] = __fmaf_rn(df, df, acc[c]);
+        }
+    }
+    const float dsum = transposed_sum32(acc, lane);
+    const int item = item32_of_lane(lane);
+    const int ci = item < n ? queue[item] : -1;
+    // insert in queue order so that equal candidates behave like the serial scan
+    for (int c = 0; c < n; ++c) {
+        const int src = item32_of_lane(c); // lane holding item c (bit reversal is an involution)
+        const float d = __shfl_sync(RSFK_FULL, dsum, src);
+        const int id = __shfl_sync(RSFK_FULL, ci, src);
+        changed |= L.try_insert(d, id, K, lane);
+    }
+}
+
+template <int KPL>
+__global__ void __launch_bounds__(KNN_THREADS)
+k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restrict__ old_idx,
+          int* __restrict__ knn_idx, float* __restrict__ knn_dist, int row_begin, int row_end)
+{
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* xp = smem + (size_t)warp * D;
+    int* queue = (int*)(smem + (size_t)KNN_WARPS * D) + warp * EXP_QUEUE;
+
+    const int warp0 = blockIdx.x * KNN_WARPS + warp;
+    const int n_warps = gridDim.x * KNN_WARPS;
+    for (int p = row_begin + warp0; p < row_end; p += n_warps) {
+        __syncwarp();
+        for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)p * D + k);
+        WarpList<KPL> L;
+        L.load(knn_idx + (size_t)p * K, knn_dist + (size_t)p * K, K, lane);
+        int nb[KPL];
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            int e = r * 32 + lane;
+            nb[r] = e < K ? old_idx[(size_t)p * K + e] : -1;
+        }
+        __syncwarp();
+        bool changed = false;
+        int qn = 0;
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            for (int b = 0; b < 32; ++b) {
+                if (r * 32 + b >= K) break;
+                const int nbr = __shfl_sync(RSFK_FULL, nb[r], b);
+                if (nbr < 0 || nbr >= N) continue;
+                const int* nrow = old_idx + (size_t)nbr * K;
+                for (int e0 = 0; e0 < K; e0 += 32) {
+                    const int e = e0 + lane;
+                    int c = e < K ? nrow[e] : -1;
+                    bool ok = c >= 0 && c < N;
+                    // not in the row being updated
+                    bool dup = false;
+#pragma unroll
+                    for (int rr = 0; rr < KPL; ++rr)
+                        for (int bb = 0; bb < 32; ++bb) {
+                            if (rr * 32 + bb >= K) break;
+                            dup |= (__shfl_sync(RSFK_FULL, L.i[rr], bb) == c);
+                        }
+                    // not already waiting in the queue
+                    for (int q = 0; q < qn; ++q) dup |= (queue[q] == c);
+                    ok = ok && !dup;
+                    const unsigned mask = __ballot_sync(RSFK_FULL, ok);
+                    if (ok) queue[qn + __popc(mask & ((1u << lane) - 1u))] = c;
+                    qn += __popc(mask);
+                    __syncwarp();
+                    if (qn >= 32) {
+                        explore_flush<KPL>(L, pts, D, xp, queue, 32, K, lane, changed);
+                        __syncwarp();
+                        // move the tail to the front
+                        const int rest = qn - 32;
+                        int t = lane < rest ? queue[32 + lane] : -1;
+                        __syncwarp();
+                        if (lane < rest) queue[lane] = t;
+                        qn = rest;
+                        __syncwarp();
+                    }
+                }
+            }
+        }
+        if (qn > 0) explore_flush<KPL>(L, pts, D, xp, queue, qn, K, lane, changed);
+        if (changed) L.store(knn_idx + (size_t)p * K, knn_dist + (size_t)p * K, K, lane);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// G-way merge of canonical lists: out = K smallest distinct of all G rows.
+// ---------------------------------------------------------------------------
+struct MergeArgs {
+    const int* idx[16];
+    const float* dist[16];
+};
+
+template <int KPL>
+__global__ void __launch_bounds__(KNN_THREADS)
+k_merge_lists(MergeArgs args, int G, long long rows, int K, int* __restrict__ out_idx,
+              float* __restrict__ out_dist)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long row = warp0; row < rows; row += n_warps) {
+        WarpList<KPL> L;
+        L.load(args.idx[0] + row * K, args.dist[0] + row * K, K, lane);
+        for (int g = 1; g < G; ++g) {
+            const int* gi = args.idx[g] + row * K;
+            const float* gd = args.dist[g] + row * K;
+            for (int e0 = 0; e0 < K; e0 += 32) {
+                const int e = e0 + lane;
+                const float cd = e < K ? gd[e] : CUDART_INF_F;
+                const int ci = e < K ? gi[e] : -1;
+                unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(cd, ci));
+                while (mask) {
+                    const int b = __ffs(mask) - 1;
+                    mask &= mask - 1;
+                    L.try_insert(__shfl_sync(RSFK_FULL, cd, b), __shfl_sync(RSFK_FULL, ci, b), K, lane);
+                }
+            }
+        }
+        L.store(out_idx + row * K, out_dist + row * K, K, lane);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host launchers
+// ---------------------------------------------------------------------------
+static int kpl_for(int K)
+{
+    int kpl = 1;
+    while (kpl * 32 < K) kpl <<= 1;
+    return kpl;
+}
+
+#define RSFK_DISPATCH_KPL(K, ...)                                                     \
+    switch (kpl_for(K)) {                                                             \
+    case 1: { constexpr int KPL = 1; __VA_ARGS__; } break;                            \
+    case 2: { constexpr int KPL = 2; __VA_ARGS__; } break;                            \
+    case 4: { constexpr int KPL = 4; __VA_ARGS__; } break;                            \
+    default: { constexpr int KPL = 8; __VA_ARGS__; } break;                           \
+    }
+
+static bool check_k(Context& ctx, int K)
+{
+    if (K < 1) return ctx.fail(RSFK_ERR_ARG, "K must be at least 1");
+    if (K > list_capacity())
+        return ctx.fail(RSFK_ERR_UNSUPPORTED, "K above 256 is not supported by this build");
+    return true;
+}
+
+bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K)
+{
+    if (!check_k(ctx, K)) return false;
+    if (rows <= 0) return true;
+    long long blocks = (rows + KNN_WARPS - 1) / KNN_WARPS;
+    if (blocks > ctx.sm_count * 16) blocks = ctx.sm_count * 16;
+    RSFK_DISPATCH_KPL(K, (k_sort_rows<KPL><<<(int)blocks, KNN_THREADS, 0, ctx.stream>>>(d_idx, d_dist, rows, K)));
+    count_launches(1);
+    return ctx.check(cudaGetLastError(), "sort_rows launch");
+}
+
+bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
+                int* d_idx, float* d_dist)
+{
+    (void)N;
+    if (!check_k(ctx, K)) return false;
+    if (tree.n_leaves <= 0) return true;
+    // block size: the whole leaf when it fits, else the largest that fits twice
+    const size_t budget = 200 * 1024;
+    auto bytes = [&](int B, int two) {
+        return sizeof(float) * ((size_t)B * (B + 1) + (size_t)(two ? 2 : 1) * B * D) + sizeof(int) * (size_t)(two ? 2 : 1) * B;
+    };
+    int B = (tree.max_leaf + 3) & ~3;
+    if (B < 4) B = 4;
+    int two = 0;
+    if (bytes(B, 0) > budget) {
+        two = 1;
+        B = 128;
+        while (B > 4 && bytes(B, 1) > budget) B >>= 1;
+        if (bytes(B, 1) > budget)
+            return ctx.fail(RSFK_ERR_UNSUPPORTED, "bucket_knn: D too large for the shared-memory tile");
+    }
+    const size_t smem = bytes(B, two);
+    RSFK_DISPATCH_KPL(K, {
+        if (!ctx.check(cudaFuncSetAttribute(k_bucket_knn<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                       "bucket_knn smem attribute"))
+            return false;
+        k_bucket_knn<KPL><<<tree.n_leaves, KNN_THREADS, smem, ctx.stream>>>(
+            d_points, D, K, tree.perm, tree.leaf_start, tree.leaf_count, d_idx, d_dist, B, two);
+    });
+    count_launches(1);
+    return ctx.check(cudaGetLastError(), "bucket_knn launch");
+}
+
+bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
+                   int* d_idx, float* d_dist, int row_begin, int row_end)
+{
+    if (!check_k(ctx, K)) return false;
+    if (row_end <= row_begin) return true;
+    const size_t smem = sizeof(float) * (size_t)KNN_WARPS * D + sizeof(int) * (size_t)KNN_WARPS * EXP_QUEUE;
+    if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "explore_sweep: D too large");
+    long long rows = (long long)row_end - row_begin;
+    long long blocks = (rows + KNN_WARPS - 1) / KNN_WARPS;
+    if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
+    RSFK_DISPATCH_KPL(K, {
+        if (!ctx.check(cudaFuncSetAttribute(k_explore<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                       "explore smem attribute"))
+            return false;
+        k_explore<KPL><<<(int)blocks, KNN_THREADS, smem, ctx.stream>>>(d_points, N, D, K, d_old_idx, d_idx,
+                                                                      d_dist, row_begin, row_end);
+    });
+    count_launches(1);
+    return ctx.check(cudaGetLastError(), "explore launch");
+}
+
+bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,
+                 const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist)
+{
+    if (!check_k(ctx, K)) return false;
+    if (G < 1 || G > 16) return ctx.fail(RSFK_ERR_ARG, "merge_lists: between 1 and 16 lists");
+    if (rows <= 0) return true;
+    MergeArgs a;
+    for (int g = 0; g < 16; ++g) {
+        a.idx[g] = g < G ? d_idx_lists[g] : nullptr;
+        a.dist[g] = g < G ? d_dist_lists[g] : nullptr;
+    }
+    long long blocks = (rows + KNN_WARPS - 1) / KNN_WARPS;
+    if (blocks > ctx.sm_count * 16) blocks = ctx.sm_count * 16;
+    RSFK_DISPATCH_KPL(K, (k_merge_lists<KPL><<<(int)blocks, KNN_THREADS, 0, ctx.stream>>>(a, G, rows, K, d_out_idx, d_out_dist)));
+    count_launches(1);
+    return ctx.check(cudaGetLastError(), "merge_lists launch");
+}
+
+} // namespace rsfk

@@ -1,0 +1,225 @@
+"""Drop-in ``gpu_rsfk.RSFK`` surface over the sm_100a ``librsfk.so``.
+
+Same class, method names, keyword arguments, defaults, return values and
+raised exceptions as the reference wrapper (python/gpu_rsfk/RSFK.py:100-644 of
+the reference project); the native work happens behind the same three
+``extern "C"`` symbols.  Differences, all compatible refinements:
+
+* rows come back ordered by (squared distance, index) instead of unordered;
+* a failure inside the library raises ``RSFKLibraryError`` instead of ending
+  the process;
+* the library directory is found next to this file (no ``pkg_resources``) and
+  ``int`` replaces the removed ``np.int``.
+"""
+import ctypes
+import math
+import time
+
+import numpy as np
+
+from . import _lib
+
+_FOREST_LOG_FIELDS = (
+    # attribute order of the reference's flattened ForestLog
+    # (python/gpu_rsfk/RSFK.py:71-88, src/rsfk.cu:2148-2173)
+    ("Tree Depth", True),
+    ("Max Leaf Size", True),
+    ("Min Leaf Size", True),
+    ("Total Leaves", True),
+    ("Tree Initialization Time", False),
+    ("Total Tree Building Time", False),
+    ("Check Active Points Time", False),
+    ("Check Points Side Time", False),
+    ("Count New Nodes Time", False),
+    ("Dynamic Memory Allocation Time", False),
+    ("Preprocessing Split Points Time", False),
+    ("Create Nodes Time", False),
+    ("Update Nodes Time", False),
+    ("Bucket Creation Time", False),
+    ("End Tree Time", False),
+    ("KNN Sets Updates", False),
+)
+
+
+def random_motion(points, random_motion_force):
+    """Jitters ``points`` in place, one dimension at a time, by a uniform offset
+    of at most ``random_motion_force * (max - min) / N`` of that dimension, so
+    that coincident points separate (python/gpu_rsfk/RSFK.py:40-66)."""
+    n_points = points.shape[0]
+    for d in range(points.shape[1]):
+        column = points[:, d]
+        span = (column.max() - column.min()) / n_points
+        points[:, d] = column + random_motion_force * np.random.uniform(-span, span, n_points)
+
+
+class ForestLog(object):
+    """Per-tree statistics of the last ``find_nearest_neighbors`` call:
+    ``data[name]`` is a list with one value per tree."""
+
+    def __init__(self, data):
+        n_trees = (len(data) - 2) // 16
+        self.data = {}
+        for row, (name, integral) in enumerate(_FOREST_LOG_FIELDS):
+            values = data[row * n_trees:(row + 1) * n_trees]
+            self.data[name] = [int(round(v)) for v in values] if integral else values
+        self.total_forest_time = float(data[16 * n_trees]) if len(data) >= 2 else 0.0
+        self.exploration_time = float(data[16 * n_trees + 1]) if len(data) >= 2 else 0.0
+
+
+def _check_children(min_tree_children, max_tree_children):
+    if min_tree_children < 0:
+        raise Exception('min_tree_children = {} \t => min_tree_children must be at least 1'
+                        .format(min_tree_children))
+    if max_tree_children < 2 * min_tree_children:
+        raise Exception('min_tree_children = {}, max_tree_children = {} \t => max_tree_children '
+                        'must be at least 2*min_tree_children'.format(min_tree_children, max_tree_children))
+
+
+class RSFK(object):
+    def __init__(self, random_state=0):
+        """``random_state`` seeds the forest: tree ``t`` of a call uses
+        ``random_state + t``."""
+        self.random_state = int(random_state)
+        self._path = _lib._DIR
+        self._lib = _lib.load()
+        self.log_forest = None
+        self._last_search_time = None
+        self._last_cluster_time = None
+
+    # ------------------------------------------------------------------ KNN
+    def _knn_call(self, n_trees, K, min_children, max_children, max_depth, verbose, sweeps,
+                  points, indices, sq_dist):
+        N, D = points.shape
+        log = np.zeros(n_trees * 16 + 2, np.float32)
+        self._lib.pymodule_rsfk_knn(n_trees, K, N, D, min_children, max_children, max_depth, verbose,
+                                    self.random_state, sweeps, points, indices, sq_dist, log)
+        _lib.check_last("pymodule_rsfk_knn")
+        return log
+
+    def find_nearest_neighbors(self, points, num_nearest_neighbors,
+                               n_trees=-1, max_tree_depth=5000,
+                               verbose=0, min_tree_children=-1,
+                               max_tree_children=-1,
+                               ensure_valid_indices=True,
+                               add_bit_random_motion=False,
+                               random_motion_force=1.0,
+                               nn_exploring_factor=-1,
+                               point_in_self_neigh=True):
+        """Approximate K-NN graph of ``points`` (``[n_points, n_dimensions]``).
+
+        Returns ``(knn_indices int32 [N, K], knn_squared_dist float32 [N, K])``,
+        rows ordered by distance; with ``point_in_self_neigh`` each point is its
+        own first neighbour at distance 0.  Defaults: ``min_tree_children=K+1``,
+        ``max_tree_children=2*min_tree_children``, one exploration sweep when
+        ``K <= 32`` else none, ``n_trees`` from the reference's heuristic
+        (at least 50).  When ``min_tree_children < K+1`` and
+        ``ensure_valid_indices`` a further tree with buckets of ``K+1 .. 3(K+1)``
+        points guarantees that no slot keeps index -1.
+        """
+        points = np.require(points, np.float32, ['CONTIGUOUS', 'ALIGNED'])
+        max_tree_depth, verbose = int(max_tree_depth), int(verbose)
+        max_tree_children, n_trees = int(max_tree_children), int(n_trees)
+        N, D = points.shape
+        K = int(num_nearest_neighbors)
+
+        if nn_exploring_factor == -1:
+            nn_exploring_factor = 1 if K <= 32 else 0
+        if min_tree_children == -1:
+            min_tree_children = K + 1
+        if max_tree_children == -1 and min_tree_children >= 0:
+            max_tree_children = 2 * min_tree_children
+        _check_children(min_tree_children, max_tree_children)
+
+        if n_trees == -1:
+            mean_bucket = (min_tree_children + max_tree_children) / 2
+            n_trees = int(max(math.ceil((N * D) / (mean_bucket * 24913)), 50))
+            if verbose > 0:
+                print("Automatically setting n_trees to {}".format(n_trees))
+
+        if add_bit_random_motion:
+            random_motion(points, random_motion_force)
+
+        knn_indices = np.full((N, K), -1, np.int32)
+        knn_squared_dist = np.full((N, K), np.inf, np.float32)
+        if point_in_self_neigh:
+            knn_indices[:, 0] = np.arange(N, dtype=np.int32)
+            knn_squared_dist[:, 0] = 0.0
+
+        t_init = time.time()
+        log = self._knn_call(n_trees, K, int(min_tree_children), max_tree_children, max_tree_depth,
+                             verbose, int(nn_exploring_factor), points, knn_indices, knn_squared_dist)
+        self.log_forest = ForestLog(log)
+        if ensure_valid_indices and min_tree_children < K + 1:
+            self._knn_call(1, K, K + 1, 3 * (K + 1), max_tree_depth, verbose,
+                           int(nn_exploring_factor), points, knn_indices, knn_squared_dist)
+        self._last_search_time = time.time() - t_init
+        return knn_indices, knn_squared_dist
+
+    def find_nearest_neighbors_ann(self, *args, **kwargs):
+        """The base/query search of the reference is not part of this library."""
+        raise Exception('find_nearest_neighbors_ann is not available in the sm_100a build')
+
+    # -------------------------------------------------------------- cluster
+    def cluster_by_sample_tree(self, points, max_tree_depth=5000,
+                               verbose=1, min_tree_children=32,
+                               max_tree_children=128,
+                               add_bit_random_motion=False,
+                               random_motion_force=1.0,
+                               numpy_result_format=True):
+        """Partitions ``points`` with a single random sample tree.
+
+        Returns ``(total_leaves, max_child, nodes_buckets, bucket_sizes)``:
+        ``nodes_buckets`` holds ``total_leaves`` consecutive groups of
+        ``max_child`` point indices, padded with -1; ``bucket_sizes[b]`` is the
+        number of points of bucket ``b``.  With ``numpy_result_format=False`` the
+        raw ctypes values are returned instead of ints and ndarrays.
+        """
+        points = np.require(points, np.float32, ['CONTIGUOUS', 'ALIGNED'])
+        max_tree_depth, verbose = int(max_tree_depth), int(verbose)
+        max_tree_children = int(max_tree_children)
+        N, D = points.shape
+        _check_children(min_tree_children, max_tree_children)
+        if add_bit_random_motion:
+            random_motion(points, random_motion_force)
+
+        t_init = time.time()
+        nodes_buckets = ctypes.POINTER(ctypes.c_int)()
+        bucket_sizes = ctypes.POINTER(ctypes.c_int)()
+        total_leaves, max_child = ctypes.c_int(0), ctypes.c_int(0)
+        self._lib.pymodule_cluster_by_sample_tree(
+            N, D, int(min_tree_children), max_tree_children, max_tree_depth, verbose,
+            self.random_state, points, ctypes.byref(nodes_buckets), ctypes.byref(bucket_sizes),
+            ctypes.byref(total_leaves), ctypes.byref(max_child))
+        _lib.check_last("pymodule_cluster_by_sample_tree")
+        self._last_cluster_time = time.time() - t_init
+
+        if not numpy_result_format:
+            return total_leaves, max_child, nodes_buckets, bucket_sizes
+        n_leaves, width = int(total_leaves.value), int(max_child.value)
+        buckets = np.ctypeslib.as_array(nodes_buckets, shape=(n_leaves * width,)).copy()
+        sizes = np.ctypeslib.as_array(bucket_sizes, shape=(n_leaves,)).copy()
+        self._lib.rsfk_free(nodes_buckets)
+        self._lib.rsfk_free(bucket_sizes)
+        return n_leaves, width, buckets, sizes
+
+
+def test():
+    """Smoke checks in the spirit of the reference's ``test1``/``test2``
+    (python/gpu_rsfk/RSFK.py:841-903): no slot may keep index -1, and a
+    clustering call must cover every point once."""
+    rng = np.random.RandomState(0)
+    data = rng.random_sample((3000, 200))
+    indices, _ = RSFK(random_state=0).find_nearest_neighbors(
+        data, 30, max_tree_children=128, n_trees=10, random_motion_force=0.01,
+        nn_exploring_factor=2, add_bit_random_motion=True)
+    missing = int(np.sum(indices == -1))
+    if missing > 0:
+        raise Exception('{} Negative indices'.format(missing))
+    n_points = 2 ** 12
+    pts = rng.random_sample((n_points, 99))
+    low = n_points // 30
+    n_leaves, width, buckets, sizes = RSFK(random_state=0).cluster_by_sample_tree(
+        pts, min_tree_children=low, max_tree_children=3 * low, verbose=0)
+    members = buckets[buckets >= 0]
+    if len(members) != n_points or len(np.unique(members)) != n_points or sizes.sum() != n_points:
+        raise Exception('cluster_by_sample_tree did not partition the points')

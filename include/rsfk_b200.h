@@ -1,0 +1,142 @@
+/*
+ * C ABI of librsfk.so, the sm_100a implementation of the RSFK K-NN-graph path.
+ *
+ * Part 1 re-exports, with identical signatures, the entry points the reference
+ * library exposes to its ctypes wrapper, so the wrapper can load this library
+ * in place of the reference's.  Part 2 adds status reporting (the reference
+ * calls exit(1) on a CUDA error; this library never exits).  Part 3 is the
+ * device-resident interface the multi-GPU driver and the parity tests use:
+ * every pointer named d_* is a device pointer on the context's device.
+ *
+ * All functions of parts 2 and 3 that return int return 0 on success or an
+ * rsfk_status code.
+ */
+#ifndef RSFK_B200_H
+#define RSFK_B200_H
+
+#if defined(__GNUC__)
+#define RSFK_EXPORT __attribute__((visibility("default")))
+#else
+#define RSFK_EXPORT
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- part 1 -- */
+
+/* Replaces pymodule_rsfk_knn (reference: src/python/pymodule_ext.cu:45-59,124-147;
+ * bound at python/gpu_rsfk/RSFK.py:115-133).  Host pointers.  Builds n_trees random
+ * sample trees (tree t uses seed RANDOM_STATE+t), merges every leaf bucket's
+ * all-pairs candidates into the caller's K-lists, then runs nn_exploring_factor
+ * neighbour-of-neighbour sweeps.  knn_indices/knn_sqr_distances are IN/OUT
+ * ([N*K]; -1 / +inf or FLT_MAX mark an empty slot) and come back ordered by
+ * (distance, index).  log_forest receives 16*n_trees+2 floats laid out as the
+ * reference's ForestLog (src/rsfk.cu:2148-2173). */
+RSFK_EXPORT void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D,
+                       int MIN_TREE_CHILD, int MAX_TREE_CHILD, int MAX_DEPTH, int VERBOSE,
+                       int RANDOM_STATE, int nn_exploring_factor,
+                       float* points, int* knn_indices, float* knn_sqr_distances,
+                       float* log_forest);
+
+/* Replaces pymodule_cluster_by_sample_tree (reference: src/python/pymodule_ext.cu:79-91,
+ * 183-212; bound at python/gpu_rsfk/RSFK.py:153-168).  One tree; returns malloc()ed
+ * nodes_buckets[total_leaves*max_child] (-1 padded) and bucket_sizes[total_leaves];
+ * release them with rsfk_free (or free). */
+RSFK_EXPORT void pymodule_cluster_by_sample_tree(int N, int D, int MIN_TREE_CHILD, int MAX_TREE_CHILD,
+                                     int MAX_DEPTH, int VERBOSE, int RANDOM_STATE,
+                                     float* points, int** nodes_buckets, int** bucket_sizes,
+                                     int* total_leaves, int* max_child);
+
+/* Same symbol as the reference's base/query entry point (src/python/pymodule_ext.cu:61-77,
+ * 149-181).  That path is outside this library's scope: the call leaves its
+ * outputs untouched and sets status RSFK_ERR_UNSUPPORTED. */
+RSFK_EXPORT void pymodule_rsfk_knn_ann(int n_trees, int num_neighbors, int N, int NQ, int D,
+                           int MIN_TREE_CHILD, int MAX_TREE_CHILD, int MAX_DEPTH, int VERBOSE,
+                           int RANDOM_STATE, int nn_exploring_factor,
+                           float* points, float* query_points, int* knn_indices,
+                           float* knn_sqr_distances, float* log_forest);
+
+/* ---------------------------------------------------------------- part 2 -- */
+
+/* Status of the most recent part-1 call on this thread's process (0 = ok).
+ * Stands in for the reference's CudaTest()/exit(1) (src/rsfk.cu:40-50). */
+RSFK_EXPORT int rsfk_last_status(void);
+RSFK_EXPORT const char* rsfk_last_message(void);
+/* Frees memory returned by pymodule_cluster_by_sample_tree. */
+RSFK_EXPORT void rsfk_free(void* p);
+/* Number of this library's kernels launched so far in this process. */
+RSFK_EXPORT long long rsfk_kernel_launches(void);
+/* Largest K the K-list kernels support. */
+RSFK_EXPORT int rsfk_max_neighbors(void);
+
+/* ---------------------------------------------------------------- part 3 -- */
+
+typedef struct rsfk_ctx rsfk_ctx;
+
+/* A context owns scratch memory on `device` and issues all work on `stream`
+ * (a cudaStream_t passed as void*; NULL is the legacy default stream).
+ * No reference counterpart: the reference hard-codes device 0 and the default
+ * stream (src/rsfk.cu:679-684). */
+RSFK_EXPORT rsfk_ctx* rsfk_ctx_create(int device, void* stream);
+RSFK_EXPORT void rsfk_ctx_destroy(rsfk_ctx* ctx);
+RSFK_EXPORT int rsfk_ctx_status(const rsfk_ctx* ctx);
+RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
+
+/* Orders every row by (distance, index), dropping repeated indices; the other
+ * device entry points expect and keep rows in this form.  The reference leaves
+ * rows unordered (src/include/rsfk.h:404-411). */
+RSFK_EXPORT int rsfk_dev_sort_rows(rsfk_ctx* ctx, int* d_idx, float* d_dist, long long rows, int K);
+
+/* One random sample tree (reference: RSFK::create_bucket_from_sample_tree,
+ * src/rsfk.cu:500-1207).  d_table, when not NULL, supplies the split pairs
+ * explicitly: n_table rows of {p1, p2, row of left child, row of right child},
+ * row 0 the root; otherwise pairs come from a counter hash of
+ * (seed, depth, segment start).  The tree stays inside the context. */
+RSFK_EXPORT int rsfk_dev_tree_build(rsfk_ctx* ctx, const float* d_points, int N, int D,
+                        int min_children, int max_children, int max_depth, int seed,
+                        const int* d_table, int n_table,
+                        int* n_leaves, int* max_leaf, int* min_leaf, int* levels);
+/* Copies the context's tree to host arrays: perm[N], leaves ordered by start. */
+RSFK_EXPORT int rsfk_dev_tree_export(rsfk_ctx* ctx, int N, int* perm, int* leaf_start, int* leaf_count);
+
+/* Leaf-bucket KNN over the context's tree (reference: RSFK::update_knn_indice_with_buckets,
+ * src/rsfk.cu:1967-2030, kernel src/kernels/compute_knn_from_buckets.cu:998-1378). */
+RSFK_EXPORT int rsfk_dev_bucket_knn(rsfk_ctx* ctx, const float* d_points, int N, int D, int K,
+                        int* d_idx, float* d_dist);
+/* Same over an explicit bucket table: leaf b holds points
+ * d_perm[d_leaf_start[b] .. +d_leaf_count[b]). */
+RSFK_EXPORT int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, int N, int D, int K,
+                              const int* d_perm, const int* d_leaf_start,
+                              const int* d_leaf_count, int n_leaves, int max_leaf,
+                              int* d_idx, float* d_dist);
+
+/* Trees first_tree, first_tree+tree_stride, ... (n_trees of them), tree t with
+ * seed `seed`+t, each followed by its bucket KNN (reference: the tree loop of
+ * RSFK::knn_gpu_rsfk_forest, src/rsfk.cu:2073-2088).  log_forest (host,
+ * 16*n_trees+2 floats) may be NULL. */
+RSFK_EXPORT int rsfk_dev_forest(rsfk_ctx* ctx, const float* d_points, int N, int D, int K,
+                    int n_trees, int first_tree, int tree_stride,
+                    int min_children, int max_children, int max_depth, int seed,
+                    int* d_idx, float* d_dist, float* log_forest);
+
+/* One neighbour-of-neighbour sweep over rows [row_begin,row_end), candidates
+ * read from the snapshot d_old_idx (reference: src/kernels/nearest_neighbors_exploring.cu:41-146,
+ * driven at src/rsfk.cu:2117-2126). */
+RSFK_EXPORT int rsfk_dev_explore(rsfk_ctx* ctx, const float* d_points, int N, int D, int K,
+                     const int* d_old_idx, int* d_idx, float* d_dist,
+                     int row_begin, int row_end);
+
+/* out = the K smallest distinct entries of G canonical lists per row.
+ * d_idx_lists/d_dist_lists are HOST arrays of G device pointers (G <= 16).
+ * No reference counterpart (the reference is single-GPU); used to combine the
+ * lists of trees built on different GPUs. */
+RSFK_EXPORT int rsfk_dev_merge_lists(rsfk_ctx* ctx, long long rows, int K, int G,
+                         const int* const* d_idx_lists, const float* const* d_dist_lists,
+                         int* d_out_idx, float* d_out_dist);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RSFK_B200_H */
