@@ -1,0 +1,540 @@
+#!/usr/bin/env python
+"""Benchmark of the RSFK K-NN-graph build on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+
+A step is one complete K-NN-graph build of the workload (all trees, every leaf
+bucket, the exploration sweeps).  Rank 0 prints ONE JSON line.
+
+* ``value``  : points/s with the points already resident in HBM (CUDA events,
+               max over ranks).
+* ``e2e``    : the same build through the host-buffer entry point the reference
+               wrapper binds (``pymodule_rsfk_knn`` via ``gpu_rsfk.RSFK``), host
+               to device and device to host copies inside the timed region.
+* ``roofline``: the dominant kernel's algorithmic bytes per launch over its
+               average CUDA-event duration, against the measured HBM copy peak.
+* ``cpu_baseline``: exact brute-force KNN (the CPU oracle's OpenMP routine) on a
+               bounded sample of query rows, all host cores.
+
+``--impl reference`` times the reference project's own CUDA library (built from
+its unmodified sources into oracle/_ref by ``make -C oracle ref``) through the
+same C ABI, in a child process, on the same workload.
+
+Data are seeded synthetic stand-ins with the shapes and distributions of the
+configurations (no dataset is downloaded).
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "gpu-rsfk_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+# name: N, D, K, trees, min, max, sweeps, generator
+WORKLOADS = {
+    "c1": dict(N=20_000, D=32, K=16, trees=4, min=32, max=128, sweeps=1, gen="uniform", seed=0),
+    "c2": dict(N=1_000_000, D=100, K=32, trees=50, min=33, max=66, sweeps=1, gen="uniform", seed=0),
+    "c3": dict(N=4_000_000, D=2, K=32, trees=32, min=256, max=1024, sweeps=1, gen="gauss2d", seed=1),
+    "c4": dict(N=1_000_000, D=960, K=32, trees=20, min=33, max=2048, sweeps=2, gen="gauss960", seed=2),
+    "c5": dict(N=20_000_000, D=128, K=64, trees=64, min=65, max=130, sweeps=2, gen="bytes128", seed=3),
+}
+
+# DRAM bytes (read+write) per launch of the dominant kernel from the committed
+# ncu capture, per unit processed; None until a capture exists.  Filled from
+# the summaries under profiles/.
+NCU_TRAFFIC_PER_POINT = {"explore": None, "bucket_knn": None, "tree_project": None}
+
+
+def make_points(w, n_override=None):
+    N = n_override or w["N"]
+    D = w["D"]
+    if w["gen"] == "uniform":
+        np.random.seed(w["seed"])
+        return np.random.uniform(0, 1, (N, D)).astype(np.float32)
+    rng = np.random.default_rng(w["seed"])
+    if w["gen"] == "gauss2d":
+        c = rng.uniform(0, 100, (64, 2))
+        return (c[rng.integers(0, 64, N)] + rng.normal(0, 1.0, (N, 2))).astype(np.float32)
+    if w["gen"] == "gauss960":
+        c = rng.normal(0, 1, (100, D))
+        out = np.empty((N, D), np.float32)
+        for s in range(0, N, 100_000):
+            e = min(N, s + 100_000)
+            out[s:e] = c[rng.integers(0, 100, e - s)] + rng.normal(0, 0.3, (e - s, D))
+        return out
+    if w["gen"] == "bytes128":
+        c = rng.integers(0, 256, (1000, D)).astype(np.float32)
+        out = np.empty((N, D), np.float32)
+        for chunk, s in enumerate(range(0, N, 1_000_000)):
+            e = min(N, s + 1_000_000)
+            r = np.random.default_rng([w["seed"], chunk])
+            out[s:e] = np.clip(np.rint(c[r.integers(0, 1000, e - s)] + r.normal(0, 12, (e - s, D))), 0, 255)
+        return out
+    raise ValueError(w["gen"])
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler(object):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the
+    timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- ours
+class TimedEngine(object):
+    """DeviceForest proxy that brackets each phase with CUDA events on the
+    launching stream."""
+
+    def __init__(self, engine):
+        import torch
+        self._e, self._torch = engine, torch
+        self.records = {"forest": [], "merge": [], "explore": []}
+        self.stats = []
+        self.enabled = False
+
+    def init_lists(self, *a, **k):
+        return self._e.init_lists(*a, **k)
+
+    def _timed(self, key, fn, *a, **k):
+        if not self.enabled:
+            return fn(*a, **k)
+        t = self._torch
+        e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn(*a, **k)
+        e1.record()
+        self.records[key].append((e0, e1))
+        return out
+
+    def forest(self, *a, **k):
+        before = self._e.stats()
+        out = self._timed("forest", self._e.forest, *a, **k)
+        if self.enabled:
+            after = self._e.stats()
+            self.stats.append({n: after[n] - before[n] for n in after})
+        return out
+
+    def merge_lists(self, *a, **k):
+        return self._timed("merge", self._e.merge_lists, *a, **k)
+
+    def explore(self, *a, **k):
+        before = self._e.stats()
+        out = self._timed("explore", self._e.explore, *a, **k)
+        if self.enabled:
+            self._e.synchronize()
+            after = self._e.stats()
+            self.stats.append({n: after[n] - before[n] for n in after})
+        return out
+
+    def total_ms(self, key):
+        return sum(a.elapsed_time(b) for a, b in self.records[key])
+
+
+def exact_knn_torch(points_dev, queries, K):
+    """Exact KNN of the query rows on the GPU (evaluation only, torch)."""
+    import torch
+    q = torch.as_tensor(queries, device=points_dev.device, dtype=torch.long)
+    out = []
+    step = max(1, int(2.5e8 // points_dev.shape[0]))
+    for s in range(0, len(q), step):
+        d = torch.cdist(points_dev[q[s:s + step]], points_dev, compute_mode="donot_use_mm_for_euclid_dist")
+        out.append(torch.topk(d, K, dim=1, largest=False).indices.to(torch.int32))
+    return torch.cat(out)
+
+
+def recall_of(truth, approx):
+    hit = 0
+    for t, a in zip(truth, approx):
+        hit += len(set(t.tolist()) & set(a.tolist()))
+    return hit / float(truth.shape[0] * truth.shape[1])
+
+
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+    from gpu_rsfk import RSFK
+    from gpu_rsfk.device import DeviceForest
+    from gpu_rsfk import distributed as rdist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    N, D, K = args.points or w["N"], w["D"], w["K"]
+    X = make_points(w, args.points)
+    X_host = torch.from_numpy(X).pin_memory()
+    X_dev = X_host.to(dev, non_blocking=True)
+    torch.cuda.synchronize()
+
+    engine = TimedEngine(DeviceForest(dev))
+
+    def step():
+        return rdist.build_knn_graph(engine, X_dev, K, w["trees"], w["min"], w["max"], 5000, w["seed"],
+                                     w["sweeps"], True)
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    fence()
+    launches0 = engine._e.kernel_launches()
+    engine.enabled = True
+    sampler = ClockSampler(local)
+    with sampler:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fence()
+        e0.record()
+        for _ in range(args.steps):
+            own_idx, own_dst, rb, re_ = step()
+        e1.record()
+        fence()
+    engine.enabled = False
+    launches = engine._e.kernel_launches() - launches0
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = N / (ms_per_step * 1e-3)
+
+    # ---- phases and roofline (rank 0's kernels) ---------------------------
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+    tot = {}
+    for s in engine.stats:
+        for n, v in s.items():
+            tot[n] = tot.get(n, 0) + v
+    n_forest = max(1, len(engine.records["forest"]))
+    n_explore = max(1, len(engine.records["explore"]))
+    trees_run = max(1, tot.get("trees", 0))
+    rows_own = re_ - rb
+    phases = {}
+    knn_ms = tot.get("bucket_knn_us", 0) / 1e3
+    forest_ms = engine.total_ms("forest")
+    phases["bucket_knn"] = dict(
+        launches=trees_run, ms_per_launch=knn_ms / trees_run,
+        bytes_per_launch=4.0 * N * D + 4.0 * N + 2 * 8.0 * N * K)
+    phases["tree_build"] = dict(
+        launches=trees_run, ms_per_launch=(forest_ms - knn_ms) / trees_run,
+        bytes_per_launch=(4.0 * (D + 2) * tot.get("tree_active_points", 0)
+                          + 4.0 * (D + 1) * tot.get("tree_nodes", 0)) / trees_run)
+    if engine.records["explore"]:
+        C = tot.get("explore_candidates", 0) / n_explore
+        phases["explore"] = dict(
+            launches=n_explore, ms_per_launch=engine.total_ms("explore") / n_explore,
+            bytes_per_launch=4.0 * rows_own * K * (K + 1) + 4.0 * D * (rows_own + C) + 2 * 8.0 * rows_own * K,
+            candidates_per_point=C / max(1, rows_own))
+    if engine.records["merge"]:
+        phases["merge_lists"] = dict(launches=len(engine.records["merge"]),
+                                     ms_per_launch=engine.total_ms("merge") / len(engine.records["merge"]),
+                                     bytes_per_launch=8.0 * rows_own * K * (world + 1))
+    for p in phases.values():
+        p["gbs"] = p["bytes_per_launch"] / (p["ms_per_launch"] * 1e-3) / 1e9 if p["ms_per_launch"] > 0 else None
+        p["total_ms"] = p["ms_per_launch"] * p["launches"]
+    dom = max(phases, key=lambda n: phases[n]["total_ms"])
+    kernel_of = {"bucket_knn": "k_bucket_knn", "tree_build": "k_project_wide+k_decide+k_scatter (tree levels)",
+                 "explore": "k_explore", "merge_lists": "k_merge_lists"}
+    traffic_unit = NCU_TRAFFIC_PER_POINT.get({"tree_build": "tree_project"}.get(dom, dom))
+    roofline = dict(bound="hbm", kernel=kernel_of[dom], achieved=phases[dom]["gbs"], peak=peak_gbs,
+                    unit="GB/s", frac=(phases[dom]["gbs"] or 0) / peak_gbs, peak_kind=peak_kind,
+                    traffic=(traffic_unit * (rows_own if dom == "explore" else N)) if traffic_unit else None,
+                    algorithmic_bytes_per_launch=phases[dom]["bytes_per_launch"],
+                    ms_per_launch=phases[dom]["ms_per_launch"])
+
+    # ---- recall of the last build -----------------------------------------
+    recall = None
+    if not args.no_recall:
+        full_idx, _ = rdist.gather_graph(own_idx, own_dst, N)
+        if rank == 0:
+            nq = min(N, args.recall_queries)
+            queries = np.sort(np.random.default_rng(w["seed"] + 1000).choice(N, nq, replace=False))
+            truth = exact_knn_torch(X_dev, queries, K).cpu().numpy()
+            recall = recall_of(truth, full_idx[torch.as_tensor(queries, device=dev)].cpu().numpy())
+        del full_idx
+    del own_idx, own_dst
+    torch.cuda.empty_cache()
+
+    # ---- end to end through host buffers -----------------------------------
+    e2e = None
+    if world == 1:
+        r = RSFK(random_state=w["seed"])
+        times = []
+        for i in range(args.e2e_steps + 1):
+            r.find_nearest_neighbors(X, K, n_trees=w["trees"], min_tree_children=w["min"],
+                                     max_tree_children=w["max"], nn_exploring_factor=w["sweeps"])
+            if i > 0:
+                times.append(r._last_search_time)
+        t_e2e = float(np.mean(times))
+        e2e = dict(value=N / t_e2e, unit="points/s", h2d_bytes_per_step=4 * N * D + 8 * N * K,
+                   d2h_bytes_per_step=8 * N * K, ms_per_step=t_e2e * 1e3,
+                   api="gpu_rsfk.RSFK.find_nearest_neighbors -> pymodule_rsfk_knn (host buffers)")
+    else:
+        out_i = torch.empty((rdist.row_block(N, world), K), dtype=torch.int32).pin_memory()
+        out_d = torch.empty((rdist.row_block(N, world), K), dtype=torch.float32).pin_memory()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(args.e2e_steps + 1):
+            if i == 1:
+                fence()
+                e0.record()
+            xd = X_host.to(dev, non_blocking=True)
+            oi, od, rb, re_ = rdist.build_knn_graph(engine, xd, K, w["trees"], w["min"], w["max"], 5000,
+                                                    w["seed"], w["sweeps"], True)
+            out_i[:re_ - rb].copy_(oi, non_blocking=True)
+            out_d[:re_ - rb].copy_(od, non_blocking=True)
+            del xd, oi, od
+        e1.record()
+        fence()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_e2e = float(t.item()) * 1e-3 / args.e2e_steps
+        e2e = dict(value=N / t_e2e, unit="points/s", h2d_bytes_per_step=4 * N * D * world,
+                   d2h_bytes_per_step=8 * N * K, ms_per_step=t_e2e * 1e3,
+                   api="gpu_rsfk.distributed.build_knn_graph with pinned host copies on every rank")
+
+    # ---- CPU baseline: exact brute force on a bounded sample ---------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_bruteforce(X, K, w["seed"], args.cpu_seconds)
+
+    if rank == 0:
+        line = {
+            "metric": "K-NNG build points/s at fixed recall@K", "value": value, "unit": "points/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "%s: N=%d D=%d K=%d n_trees=%d min/max_tree_children=%d/%d sweeps=%d %s seed %d"
+                                   % (args.workload, N, D, K, w["trees"], w["min"], w["max"], w["sweeps"],
+                                      w["gen"], w["seed"]),
+                       "parallelism": "trees sharded %d-way, all-to-all merge, all-gather per sweep" % world
+                       if world > 1 else "single GPU",
+                       "l2": "inputs (%.0f MB points + %.0f MB lists) exceed the 126 MB L2; no flush"
+                             % (4e-6 * N * D, 8e-6 * N * K)},
+            "recall_at_k": recall,
+            "e2e": e2e, "gpu_launches": int(launches), "clocks": sampler.summary(),
+            "roofline": roofline,
+            "phases": {n: {k: (round(v, 4) if isinstance(v, float) else v) for k, v in p.items()}
+                       for n, p in phases.items()},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_bruteforce(X, K, seed, seconds):
+    """Exact KNN of a bounded sample of rows against all N points with the
+    oracle's OpenMP routine; rows/s is directly comparable to points/s."""
+    from oracle import rsfk_oracle as orc
+    N = X.shape[0]
+    rng = np.random.default_rng(seed + 2000)
+    probe = np.sort(rng.choice(N, min(N, 64), replace=False)).astype(np.int32)
+    t0 = time.time()
+    _, _, threads = orc.bruteforce_knn(X, K, probe)
+    per_row = (time.time() - t0) / len(probe)
+    nq = int(max(64, min(N, seconds / max(per_row, 1e-9))))
+    q = np.sort(rng.choice(N, nq, replace=False)).astype(np.int32)
+    t0 = time.time()
+    orc.bruteforce_knn(X, K, q)
+    dt = time.time() - t0
+    return {"value": nq / dt, "unit": "points/s", "cores": threads, "kind": "port",
+            "sample": "exact brute-force KNN (OpenMP, fmaf) of %d seeded query rows against all %d points, %.1f s"
+                      % (nq, N, dt)}
+
+
+# --------------------------------------------------------------------------- reference arm
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "librsfk_ref.so")
+
+
+def reference_worker(args, w):
+    """Child process: the reference's own library through its C ABI
+    (reference: src/python/pymodule_ext.cu:124-147), host buffers, as its wrapper calls it."""
+    L = ctypes.CDLL(REF_SO)
+    i = ctypes.c_int
+    L.pymodule_rsfk_knn.restype = None
+    L.pymodule_rsfk_knn.argtypes = [i] * 10 + [ctypes.c_void_p] * 4
+    N, D, K = args.points or w["N"], w["D"], w["K"]
+    X = make_points(w, args.points)
+    trees = args.ref_trees or w["trees"]
+    times = []
+    for s in range(args.warmup + args.steps):
+        idx = np.full((N, K), -1, np.int32)
+        dst = np.full((N, K), np.inf, np.float32)
+        idx[:, 0] = np.arange(N)
+        dst[:, 0] = 0
+        log = np.zeros(16 * trees + 2, np.float32)
+        t0 = time.time()
+        L.pymodule_rsfk_knn(trees, K, N, D, w["min"], min(w["max"], 1024), 5000, 0, w["seed"], w["sweeps"],
+                            X.ctypes.data, idx.ctypes.data, dst.ctypes.data, log.ctypes.data)
+        if s >= args.warmup:
+            times.append(time.time() - t0)
+    recall = None
+    if not args.no_recall:
+        import torch
+        nq = min(N, args.recall_queries)
+        queries = np.sort(np.random.default_rng(w["seed"] + 1000).choice(N, nq, replace=False))
+        truth = exact_knn_torch(torch.from_numpy(X).cuda(), queries, K).cpu().numpy()
+        recall = recall_of(truth, idx[queries])
+    print("REFRESULT " + json.dumps({"times": times, "recall": recall, "trees": trees,
+                                     "forest_s": float(log[16 * trees]), "explore_s": float(log[16 * trees + 1])}))
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    N, D, K = args.points or w["N"], w["D"], w["K"]
+    base = {"impl": "reference"}
+    if not os.path.exists(REF_SO):
+        print(json.dumps(dict(base, unavailable="oracle/_ref/librsfk_ref.so was not built (make -C oracle ref)")))
+        return
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-worker", "--workload", args.workload,
+           "--steps", str(args.steps), "--warmup", str(args.warmup), "--recall-queries", str(args.recall_queries)]
+    if args.points:
+        cmd += ["--points", str(args.points)]
+    if args.ref_trees:
+        cmd += ["--ref-trees", str(args.ref_trees)]
+    if args.no_recall:
+        cmd += ["--no-recall"]
+    env = dict(os.environ)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    env["CUDA_VISIBLE_DEVICES"] = os.environ.get("LOCAL_RANK", "0") if "CUDA_VISIBLE_DEVICES" not in os.environ else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[0]
+    try:
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.ref_timeout)
+    except subprocess.TimeoutExpired:
+        print(json.dumps(dict(base, unavailable="reference library did not finish within %d s" % args.ref_timeout)))
+        return
+    res = [l for l in out.stdout.splitlines() if l.startswith("REFRESULT ")]
+    if out.returncode != 0 or not res:
+        tail = (out.stderr or out.stdout).strip().splitlines()[-1:] or ["no output"]
+        print(json.dumps(dict(base, unavailable="reference library failed (exit %d): %s" % (out.returncode, tail[0][:200]))))
+        return
+    r = json.loads(res[0][len("REFRESULT "):])
+    t = float(np.mean(r["times"]))
+    scale = w["trees"] / float(r["trees"])
+    note = ""
+    if r["trees"] != w["trees"]:
+        # bounded sample: fewer trees; the forest part scales with the tree count
+        t = r["forest_s"] * scale + (t - r["forest_s"])
+        note = " (forest time of %d trees scaled to %d)" % (r["trees"], w["trees"])
+    value = N / t
+    line = {
+        "impl": "reference", "metric": "K-NNG build points/s at fixed recall@K", "value": value,
+        "unit": "points/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "%s: N=%d D=%d K=%d n_trees=%d min/max_tree_children=%d/%d sweeps=%d %s seed %d"
+                               % (args.workload, N, D, K, w["trees"], w["min"], min(w["max"], 1024), w["sweeps"],
+                                  w["gen"], w["seed"])},
+        "recall_at_k": r["recall"],
+        "cpu_baseline": {"value": value, "unit": "points/s", "cores": 0, "kind": "reference",
+                         "sample": "the reference's own CUDA library (it has no CPU path), unmodified sources "
+                                   "compiled for sm_100, one GPU, host buffers, whole workload" + note},
+        "e2e": {"value": value, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-worker"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--points", type=int, default=0, help="override N (debugging)")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--recall-queries", type=int, default=10_000)
+    ap.add_argument("--no-recall", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--ref-trees", type=int, default=0, help="reference arm: time this many trees and scale")
+    ap.add_argument("--ref-timeout", type=int, default=900)
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    elif args.impl == "reference-worker":
+        reference_worker(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

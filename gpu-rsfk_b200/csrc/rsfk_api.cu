@@ -86,12 +86,9 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
                 int* d_idx, float* d_dist, float* log_forest, int verbose)
 {
     Context& c = h->c;
-    std::vector<cudaEvent_t> ev;
-    if (log_forest) {
-        memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
-        ev.resize(2 * (size_t)n_trees);
-        for (auto& e : ev) cudaEventCreate(&e);
-    }
+    std::vector<cudaEvent_t> ev(2 * (size_t)n_trees);
+    for (auto& e : ev) cudaEventCreate(&e);
+    if (log_forest) memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
     const double t0 = now_s();
     bool ok = true;
     for (int i = 0; i < n_trees && ok; ++i) {
@@ -102,10 +99,10 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
         h->has_tree = ok;
         const double tb1 = now_s();
         if (!ok) break;
-        if (log_forest) cudaEventRecord(ev[2 * i], c.stream);
+        cudaEventRecord(ev[2 * i], c.stream);
         ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist);
+        cudaEventRecord(ev[2 * i + 1], c.stream);
         if (log_forest) {
-            cudaEventRecord(ev[2 * i + 1], c.stream);
             log_forest[0 * n_trees + i] = (float)h->tree.levels;
             log_forest[1 * n_trees + i] = (float)h->tree.max_leaf;
             log_forest[2 * n_trees + i] = (float)h->tree.min_leaf;
@@ -117,16 +114,16 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
                    h->tree.n_leaves, h->tree.min_leaf, h->tree.max_leaf, tb1 - tb0);
     }
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
-    if (log_forest) {
-        if (ok)
-            for (int i = 0; i < n_trees; ++i) {
-                float ms = 0.0f;
-                if (cudaEventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]) == cudaSuccess)
-                    log_forest[15 * n_trees + i] = ms * 1e-3f;
+    if (ok)
+        for (int i = 0; i < n_trees; ++i) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]) == cudaSuccess) {
+                c.stats.bucket_knn_us += ms * 1e3;
+                if (log_forest) log_forest[15 * n_trees + i] = ms * 1e-3f;
             }
-        for (auto& e : ev) cudaEventDestroy(e);
-        log_forest[16 * n_trees] = (float)(now_s() - t0);
-    }
+        }
+    for (auto& e : ev) cudaEventDestroy(e);
+    if (log_forest) log_forest[16 * n_trees] = (float)(now_s() - t0);
     return ok;
 }
 
@@ -141,7 +138,7 @@ bool run_sweeps(rsfk_ctx* h, const float* d_points, int N, int D, int K, int swe
         if (!c.check(cudaMemcpyAsync(snap, d_idx, sizeof(int) * (size_t)N * K, cudaMemcpyDeviceToDevice,
                                      c.stream), "snapshot"))
             return false;
-        if (!rsfk::explore_sweep(c, d_points, N, D, K, snap, d_idx, d_dist, 0, N)) return false;
+        if (!rsfk::explore_sweep(c, d_points, N, D, K, snap, d_idx, d_dist, 0, N, 0)) return false;
     }
     return true;
 }
@@ -305,6 +302,24 @@ void rsfk_ctx_destroy(rsfk_ctx* ctx)
 
 int rsfk_ctx_status(const rsfk_ctx* ctx) { return ctx ? ctx->c.status : RSFK_ERR_ARG; }
 
+int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
+{
+    if (!ctx || !out) return RSFK_ERR_ARG;
+    Context& c = ctx->c;
+    cudaSetDevice(c.device);
+    unsigned long long evaluated = 0;
+    if (c.slots[Context::EXPLORE_COUNT].ptr) {
+        if (!c.check(cudaMemcpyAsync(&evaluated, c.slots[Context::EXPLORE_COUNT].ptr, sizeof(evaluated),
+                                     cudaMemcpyDeviceToHost, c.stream), "stats D2H") ||
+            !c.check(cudaStreamSynchronize(c.stream), "stats"))
+            return c.status;
+    }
+    const double v[5] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+                         c.stats.bucket_knn_us, (double)evaluated};
+    for (int i = 0; i < n && i < 5; ++i) out[i] = v[i];
+    return RSFK_OK;
+}
+
 int rsfk_ctx_synchronize(rsfk_ctx* ctx)
 {
     if (!ctx) return RSFK_ERR_ARG;
@@ -409,14 +424,14 @@ int rsfk_dev_forest(rsfk_ctx* ctx, const float* d_points, int N, int D, int K, i
 }
 
 int rsfk_dev_explore(rsfk_ctx* ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
-                     int* d_idx, float* d_dist, int row_begin, int row_end)
+                     int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0)
 {
     RSFK_ENTER(ctx);
-    if (row_begin < 0 || row_end > N || row_begin > row_end) {
+    if (row_begin < 0 || row_end > N || row_begin > row_end || list_row0 < 0 || list_row0 > row_begin) {
         ctx->c.fail(RSFK_ERR_ARG, "rsfk_dev_explore: invalid row range");
         return ctx->c.status;
     }
-    rsfk::explore_sweep(ctx->c, d_points, N, D, K, d_old_idx, d_idx, d_dist, row_begin, row_end);
+    rsfk::explore_sweep(ctx->c, d_points, N, D, K, d_old_idx, d_idx, d_dist, row_begin, row_end, list_row0);
     return ctx->c.status;
 }
 

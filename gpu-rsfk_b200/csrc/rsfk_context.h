@@ -41,7 +41,16 @@ struct LevelCounters {
     int max_leaf;
     int min_leaf;
     int error;
-    int pad0, pad1;
+    int active_next; // points of the next level's open nodes
+    int pad1;
+};
+
+// Work counters a benchmark reads to turn kernel times into achieved bytes/s.
+struct Stats {
+    long long trees = 0;              // trees built
+    long long tree_active_points = 0; // sum over levels of the points projected
+    long long tree_nodes = 0;         // nodes split (hyperplanes formed)
+    double bucket_knn_us = 0.0;       // device time of the bucket-KNN kernels
 };
 
 struct TreeResult {
@@ -65,8 +74,9 @@ struct Context {
     enum Slot {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
         NODES_A, NODES_B, NODE_SPLIT, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
-        SNAPSHOT, N_SLOTS
+        SNAPSHOT, EXPLORE_COUNT, N_SLOTS
     };
+    Stats stats;
     Buffer slots[N_SLOTS];
     LevelCounters* host_counters = nullptr; // pinned
 
@@ -94,6 +104,14 @@ struct Context {
         b.bytes = want;
         return b.ptr;
     }
+    // device counter of candidates evaluated by exploration sweeps (zeroed once)
+    unsigned long long* explore_counter()
+    {
+        const bool fresh = slots[EXPLORE_COUNT].ptr == nullptr;
+        auto* p = (unsigned long long*)scratch(EXPLORE_COUNT, sizeof(unsigned long long));
+        if (p && fresh) cudaMemsetAsync(p, 0, sizeof(unsigned long long), stream);
+        return p;
+    }
     void release()
     {
         for (auto& b : slots) { if (b.ptr) cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
@@ -113,7 +131,7 @@ bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K);
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
                 int* d_idx, float* d_dist);
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
-                   int* d_idx, float* d_dist, int row_begin, int row_end);
+                   int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0);
 bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,
                  const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist);
 

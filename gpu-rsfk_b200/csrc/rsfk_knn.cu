@@ -261,7 +261,8 @@ __device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __r
 template <int KPL>
 __global__ void __launch_bounds__(KNN_THREADS)
 k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restrict__ old_idx,
-          int* __restrict__ knn_idx, float* __restrict__ knn_dist, int row_begin, int row_end)
+          int* __restrict__ knn_idx, float* __restrict__ knn_dist, int row_begin, int row_end,
+          int list_row0, unsigned long long* __restrict__ evaluated)
 {
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -270,11 +271,12 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
 
     const int warp0 = blockIdx.x * KNN_WARPS + warp;
     const int n_warps = gridDim.x * KNN_WARPS;
+    unsigned long long n_eval = 0;
     for (int p = row_begin + warp0; p < row_end; p += n_warps) {
         __syncwarp();
         for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)p * D + k);
         WarpList<KPL> L;
-        L.load(knn_idx + (size_t)p * K, knn_dist + (size_t)p * K, K, lane);
+        L.load(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
         int nb[KPL];
 #pragma unroll
         for (int r = 0; r < KPL; ++r) {
@@ -311,6 +313,7 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
                     qn += __popc(mask);
                     __syncwarp();
                     if (qn >= 32) {
+                        n_eval += 32;
                         explore_flush<KPL>(L, pts, D, xp, queue, 32, K, lane, changed);
                         __syncwarp();
                         // move the tail to the front
@@ -324,9 +327,14 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
                 }
             }
         }
-        if (qn > 0) explore_flush<KPL>(L, pts, D, xp, queue, qn, K, lane, changed);
-        if (changed) L.store(knn_idx + (size_t)p * K, knn_dist + (size_t)p * K, K, lane);
+        if (qn > 0) {
+            n_eval += qn;
+            explore_flush<KPL>(L, pts, D, xp, queue, qn, K, lane, changed);
+        }
+        if (changed)
+            L.store(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
     }
+    if (lane == 0 && n_eval) atomicAdd(evaluated, n_eval);
 }
 
 // ---------------------------------------------------------------------------
@@ -438,7 +446,7 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
 }
 
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
-                   int* d_idx, float* d_dist, int row_begin, int row_end)
+                   int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0)
 {
     if (!check_k(ctx, K)) return false;
     if (row_end <= row_begin) return true;
@@ -447,12 +455,14 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
     long long rows = (long long)row_end - row_begin;
     long long blocks = (rows + KNN_WARPS - 1) / KNN_WARPS;
     if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
+    unsigned long long* counter = ctx.explore_counter();
+    if (!counter) return false;
     RSFK_DISPATCH_KPL(K, {
         if (!ctx.check(cudaFuncSetAttribute(k_explore<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                        "explore smem attribute"))
             return false;
         k_explore<KPL><<<(int)blocks, KNN_THREADS, smem, ctx.stream>>>(d_points, N, D, K, d_old_idx, d_idx,
-                                                                      d_dist, row_begin, row_end);
+                                                                      d_dist, row_begin, row_end, list_row0, counter);
     });
     count_launches(1);
     return ctx.check(cudaGetLastError(), "explore launch");

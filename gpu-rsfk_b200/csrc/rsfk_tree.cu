@@ -298,6 +298,7 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
         if (lane == 0) {
             slot = atomicAdd(&cnt->n_nodes_next, 1);
             cb = atomicAdd(&cnt->n_chunks_next, nch);
+            atomicAdd(&cnt->active_next, ch_count[k]);
         }
         slot = __shfl_sync(RSFK_FULL, slot, 0);
         cb = __shfl_sync(RSFK_FULL, cb, 0);
@@ -409,7 +410,7 @@ __global__ void k_tree_init(Node* nodes, int* chunk_node, int n_chunks, int N, i
         r.chunk_base = 0; r.pad0 = r.pad1 = 0;
         nodes[0] = r;
         cnt->n_nodes_next = 0; cnt->n_chunks_next = 0; cnt->n_leaves = 0;
-        cnt->max_leaf = 0; cnt->min_leaf = 0x7fffffff; cnt->error = 0;
+        cnt->max_leaf = 0; cnt->min_leaf = 0x7fffffff; cnt->error = 0; cnt->active_next = 0;
     }
     for (int c = t; c < n_chunks; c += gridDim.x * blockDim.x) chunk_node[c] = 0;
 }
@@ -418,6 +419,7 @@ __global__ void k_reset_level(LevelCounters* cnt)
 {
     cnt->n_nodes_next = 0;
     cnt->n_chunks_next = 0;
+    cnt->active_next = 0;
 }
 
 __global__ void k_single_leaf(int* leaf_start, int* leaf_count, int N, LevelCounters* cnt)
@@ -509,8 +511,11 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     }
 
     int depth = 1;
+    long long active = N;
     for (; depth < max_depth && n_nodes > 0; ++depth) {
         const int level = depth - 1; // level of the nodes being split
+        ctx.stats.tree_active_points += active;
+        ctx.stats.tree_nodes += n_nodes;
         launch_project(ctx, d_points, D, perm[cur], nodes[cur], chunk_node[cur], n_chunks, side_bits,
                        chunk_left, table, n_table, seed, level);
         k_reset_level<<<1, 1, 0, st>>>(cnt);
@@ -528,6 +533,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
             return ctx.fail(ctx.host_counters->error, "tree_build: internal table overflow");
         n_nodes = ctx.host_counters->n_nodes_next;
         n_chunks = ctx.host_counters->n_chunks_next;
+        active = ctx.host_counters->active_next;
         cur ^= 1;
         levels = depth;
     }
@@ -543,6 +549,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     if (ctx.host_counters->error)
         return ctx.fail(ctx.host_counters->error, "tree_build: internal table overflow");
 
+    ctx.stats.trees++;
     out.perm = perm_final;
     out.leaf_start = leaf_start;
     out.leaf_count = leaf_count;

@@ -66,6 +66,8 @@ def load():
     L.rsfk_ctx_status.argtypes = [vp]
     L.rsfk_ctx_synchronize.restype = i
     L.rsfk_ctx_synchronize.argtypes = [vp]
+    L.rsfk_ctx_stats.restype = i
+    L.rsfk_ctx_stats.argtypes = [vp, ctypes.POINTER(ctypes.c_double), i]
     L.rsfk_dev_sort_rows.restype = i
     L.rsfk_dev_sort_rows.argtypes = [vp, vp, vp, ll, i]
     L.rsfk_dev_tree_build.restype = i
@@ -79,7 +81,7 @@ def load():
     L.rsfk_dev_forest.restype = i
     L.rsfk_dev_forest.argtypes = [vp, vp, i, i, i, i, i, i, i, i, i, i, vp, vp, vp]
     L.rsfk_dev_explore.restype = i
-    L.rsfk_dev_explore.argtypes = [vp, vp, i, i, i, vp, vp, vp, i, i]
+    L.rsfk_dev_explore.argtypes = [vp, vp, i, i, i, vp, vp, vp, i, i, i]
     L.rsfk_dev_merge_lists.restype = i
     L.rsfk_dev_merge_lists.argtypes = [vp, ll, i, i, vp, vp, vp, vp]
     _lib = L

@@ -118,13 +118,16 @@ class DeviceForest(object):
         _lib.raise_on_status(code, "forest")
         return log
 
-    def explore(self, points, old_idx, idx, dist, row_begin=0, row_end=None):
+    def explore(self, points, old_idx, idx, dist, row_begin=0, row_end=None, list_row0=0):
+        """One sweep over rows [row_begin,row_end); ``idx``/``dist`` start at row ``list_row0``."""
         _want(points, torch.float32, "points"); _want(old_idx, torch.int32, "old_idx")
         _want(idx, torch.int32, "idx"); _want(dist, torch.float32, "dist")
         N, D = points.shape
         row_end = N if row_end is None else row_end
+        if idx.shape[0] < row_end - list_row0:
+            raise ValueError("idx/dist do not cover rows up to row_end")
         code = self._lib.rsfk_dev_explore(self._ctx, _ptr(points), N, D, idx.shape[1], _ptr(old_idx),
-                                          _ptr(idx), _ptr(dist), row_begin, row_end)
+                                          _ptr(idx), _ptr(dist), row_begin, row_end, list_row0)
         _lib.raise_on_status(code, "explore")
 
     def merge_lists(self, idx_lists, dist_lists, out_idx, out_dist):
@@ -139,6 +142,13 @@ class DeviceForest(object):
         code = self._lib.rsfk_dev_merge_lists(self._ctx, rows, K, G, ctypes.cast(ip, ctypes.c_void_p),
                                               ctypes.cast(dp, ctypes.c_void_p), _ptr(out_idx), _ptr(out_dist))
         _lib.raise_on_status(code, "merge_lists")
+
+    def stats(self):
+        """Work counters of this context (synchronizes the stream)."""
+        out = (ctypes.c_double * 5)()
+        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 5), "stats")
+        names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates")
+        return dict(zip(names, [float(v) for v in out]))
 
     def kernel_launches(self):
         return int(self._lib.rsfk_kernel_launches())

@@ -83,6 +83,13 @@ RSFK_EXPORT rsfk_ctx* rsfk_ctx_create(int device, void* stream);
 RSFK_EXPORT void rsfk_ctx_destroy(rsfk_ctx* ctx);
 RSFK_EXPORT int rsfk_ctx_status(const rsfk_ctx* ctx);
 RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
+/* Work counters since the context was created, for turning kernel times into
+ * achieved bytes/s: out[0] trees built, out[1] points projected summed over
+ * tree levels, out[2] nodes split, out[3] device microseconds spent in the
+ * bucket-KNN kernels, out[4] candidates whose distance the exploration sweeps
+ * evaluated.  The reference's counterpart is its ForestLog of per-phase
+ * wall-clock times (src/include/rsfk.h:274-392). */
+RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
 /* Orders every row by (distance, index), dropping repeated indices; the other
  * device entry points expect and keep rows in this form.  The reference leaves
@@ -122,11 +129,13 @@ RSFK_EXPORT int rsfk_dev_forest(rsfk_ctx* ctx, const float* d_points, int N, int
                     int* d_idx, float* d_dist, float* log_forest);
 
 /* One neighbour-of-neighbour sweep over rows [row_begin,row_end), candidates
- * read from the snapshot d_old_idx (reference: src/kernels/nearest_neighbors_exploring.cu:41-146,
- * driven at src/rsfk.cu:2117-2126). */
+ * read from the snapshot d_old_idx ([N*K], all rows) (reference:
+ * src/kernels/nearest_neighbors_exploring.cu:41-146, driven at src/rsfk.cu:2117-2126).
+ * d_idx/d_dist hold the lists being updated starting at row list_row0
+ * (0 for full [N*K] arrays; row_begin when a rank keeps only its own rows). */
 RSFK_EXPORT int rsfk_dev_explore(rsfk_ctx* ctx, const float* d_points, int N, int D, int K,
                      const int* d_old_idx, int* d_idx, float* d_dist,
-                     int row_begin, int row_end);
+                     int row_begin, int row_end, int list_row0);
 
 /* out = the K smallest distinct entries of G canonical lists per row.
  * d_idx_lists/d_dist_lists are HOST arrays of G device pointers (G <= 16).

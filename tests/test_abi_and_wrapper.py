@@ -1,0 +1,97 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports every
+symbol the header declares; the drop-in Python class validates arguments and
+parses the forest log like the reference wrapper."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "rsfk_b200.h")).read()
+    return re.findall(r"RSFK_EXPORT\s+[\w\s\*]+?\b(\w+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    from gpu_rsfk import _lib
+    L = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared_symbols()
+    assert len(names) >= 20
+    for required in ("pymodule_rsfk_knn", "pymodule_cluster_by_sample_tree", "pymodule_rsfk_knn_ann"):
+        assert required in names
+    for name in names:
+        assert hasattr(L, name), name
+
+
+def test_library_is_named_and_placed_like_the_reference():
+    from gpu_rsfk import _lib
+    assert os.path.basename(_lib.LIB_PATH) == "librsfk.so"
+    assert os.path.dirname(_lib.LIB_PATH) == os.path.dirname(os.path.abspath(_lib.__file__))
+
+
+def test_status_entry_points_without_a_gpu():
+    from gpu_rsfk import _lib
+    L = _lib.load()
+    assert L.rsfk_max_neighbors() == 256
+    assert L.rsfk_kernel_launches() >= 0
+    assert isinstance(L.rsfk_last_message(), bytes)
+    L.rsfk_free(None)
+
+
+def test_ann_entry_point_reports_unsupported():
+    from gpu_rsfk import _lib, RSFK
+    L = _lib.load()
+    L.pymodule_rsfk_knn_ann(*([0] * 11 + [None] * 5))
+    assert L.rsfk_last_status() == 3
+    with pytest.raises(Exception):
+        RSFK().find_nearest_neighbors_ann(np.zeros((4, 2), np.float32), np.zeros((1, 2), np.float32), 2)
+
+
+def test_wrapper_argument_validation_matches_reference():
+    from gpu_rsfk import RSFK
+    r = RSFK(random_state=3)
+    assert r.random_state == 3
+    X = np.zeros((10, 3), np.float32)
+    with pytest.raises(Exception, match="max_tree_children must be at least 2\\*min_tree_children"):
+        r.find_nearest_neighbors(X, 4, min_tree_children=8, max_tree_children=9)
+    with pytest.raises(Exception, match="min_tree_children must be at least 1"):
+        r.find_nearest_neighbors(X, 4, min_tree_children=-5, max_tree_children=10)
+    with pytest.raises(Exception, match="max_tree_children must be at least"):
+        r.cluster_by_sample_tree(X, min_tree_children=32, max_tree_children=40)
+
+
+def test_forest_log_layout():
+    from gpu_rsfk import ForestLog
+    T = 3
+    data = np.arange(16 * T + 2, dtype=np.float32)
+    log = ForestLog(data)
+    assert log.data["Tree Depth"] == [0, 1, 2]
+    assert log.data["Total Leaves"] == [9, 10, 11]
+    assert list(log.data["KNN Sets Updates"]) == [45.0, 46.0, 47.0]
+    assert len(log.data) == 16
+    assert log.total_forest_time == 48.0 and log.exploration_time == 49.0
+
+
+def test_random_motion_moves_points_slightly():
+    from gpu_rsfk import random_motion
+    np.random.seed(0)
+    X = np.random.rand(100, 4)
+    Y = X.copy()
+    random_motion(Y, 1.0)
+    assert (Y != X).any() and np.abs(Y - X).max() <= 1.0 / 100 + 1e-12
+
+
+def test_no_gpu_means_loud_failure():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from gpu_rsfk import RSFK, RSFKLibraryError
+    with pytest.raises(RSFKLibraryError):
+        RSFK().find_nearest_neighbors(np.random.rand(50, 4).astype(np.float32), 3, n_trees=1)
+    from gpu_rsfk.device import DeviceForest
+    with pytest.raises(RSFKLibraryError):
+        DeviceForest()

@@ -1,0 +1,129 @@
+"""The CPU oracle against outputs of the reference project's own CUDA library.
+
+The fixtures under tests/golden/ were produced on a B200 by
+tests/golden/make_ref_golden.py from the reference's unmodified sources.  They
+pin the oracle's distance bits, bucket update rule and exploration sweep; the
+tree's split rule is pinned by recovering, for a reference tree, split pairs
+that reproduce its buckets exactly."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _load(pattern):
+    files = sorted(glob.glob(os.path.join(GOLDEN, pattern)))
+    assert files, "fixtures missing: " + pattern
+    return files
+
+
+@pytest.mark.parametrize("path", _load("ref_buckets_*.npz"))
+def test_reference_distance_bits_and_bucket_partition(oracle, path):
+    z = np.load(path)
+    X, idx, dist = z["X"], z["idx"], z["dist"]
+    N, D, MIN, MAX, K = [int(v) for v in z["params"]]
+    # every row lists its whole bucket (K > MAX): buckets are the row sets
+    buckets = {}
+    for p in range(N):
+        members = frozenset(idx[p][idx[p] >= 0].tolist())
+        assert p in members
+        buckets.setdefault(members, 0)
+        buckets[members] += 1
+    sizes = []
+    for members, rows in buckets.items():
+        assert rows == len(members)            # all members agree on the bucket
+        sizes.append(len(members))
+    assert sum(sizes) == N
+    assert min(sizes) >= MIN and max(sizes) <= MAX
+    # the oracle's squared distance carries the reference's bits for every pair
+    checked = 0
+    for p in range(N):
+        for k in range(K):
+            q = idx[p, k]
+            if q < 0 or q == p:
+                continue
+            assert np.float32(oracle.dist_sqr(X[p], X[q])) == dist[p, k], (p, q)
+            checked += 1
+    assert checked > N
+    # and the canonical bucket update over those buckets returns the same rows
+    perm = np.concatenate([np.array(sorted(b), np.int32) for b in buckets])
+    counts = np.array([len(b) for b in buckets], np.int32)
+    starts = (np.cumsum(counts) - counts).astype(np.int32)
+    i0, d0 = oracle.init_lists(N, K)
+    oi, od = oracle.bucket_knn(X, K, perm, starts, counts, i0, d0)
+    si, sd = oracle.sort_rows(idx, dist)
+    np.testing.assert_array_equal(oi, si)
+    np.testing.assert_array_equal(od, sd)
+
+
+@pytest.mark.parametrize("path", _load("ref_explore_*.npz"))
+def test_reference_exploration_sweep(oracle, path):
+    z = np.load(path)
+    X = z["X"]
+    N, D, K, sweeps = [int(v) for v in z["params"]]
+    idx, dist = z["idx_in"], z["dist_in"]
+    ci, cd = oracle.sort_rows(idx, dist)
+    for _ in range(sweeps):
+        idx, dist = oracle.explore_ref(X, idx, idx, dist)      # slot-for-slot restatement
+        ci, cd = oracle.explore(X, ci, ci, cd)                 # canonical statement
+    np.testing.assert_array_equal(idx, z["idx_out"])
+    np.testing.assert_array_equal(dist, z["dist_out"])
+    si, sd = oracle.sort_rows(z["idx_out"], z["dist_out"])
+    np.testing.assert_array_equal(ci, si)
+    np.testing.assert_array_equal(cd, sd)
+
+
+@pytest.mark.parametrize("path", _load("ref_update_*.npz"))
+def test_reference_bucket_update_rule(oracle, path):
+    z = np.load(path)
+    X = z["X"]
+    N, D, K, MAX = [int(v) for v in z["params"]]
+    big = z["big_idx"]
+    buckets = sorted({frozenset(r[r >= 0].tolist()) for r in big}, key=min)
+    assert len(buckets) == 2 and sum(len(b) for b in buckets) == N
+    perm = np.concatenate([np.array(sorted(b), np.int32) for b in buckets])
+    counts = np.array([len(b) for b in buckets], np.int32)
+    starts = (np.cumsum(counts) - counts).astype(np.int32)
+    i0, d0 = oracle.init_lists(N, K)
+    oi, od = oracle.bucket_knn(X, K, perm, starts, counts, i0, d0)
+    ri, rd = oracle.bucket_knn_ref(X, K, perm, starts, counts, i0, d0)
+    si, sd = oracle.sort_rows(z["idx"], z["dist"])
+    np.testing.assert_array_equal(oi, si)
+    np.testing.assert_array_equal(od, sd)
+    ri, rd = oracle.sort_rows(ri, rd)
+    np.testing.assert_array_equal(ri, si)
+    np.testing.assert_array_equal(rd, sd)
+
+
+@pytest.mark.parametrize("path", _load("ref_update_*.npz"))
+def test_reference_root_split_is_reproduced_by_some_pair(oracle, path):
+    """The two leaves of a reference tree over N <= MAX-2 points are the two
+    sides of the root hyperplane of SOME pair of points; the oracle's split rule
+    (n.x < c goes right, serial-sum offset at the root) must reproduce that
+    partition exactly for at least one pair."""
+    z = np.load(path)
+    X = z["X"]
+    N = X.shape[0]
+    buckets = sorted({frozenset(r[r >= 0].tolist()) for r in z["big_idx"]}, key=min)
+    target = np.zeros(N, bool)
+    target[list(buckets[1])] = True
+    found = None
+    for p1 in range(N):
+        for p2 in range(N):
+            if p1 == p2 or target[p1] == target[p2]:
+                continue
+            n, c = oracle.hyperplane(X[p1], X[p2], True)
+            # cheap float64 screen before the bit-exact check
+            right = (X.astype(np.float64) @ n.astype(np.float64)) < float(c)
+            if (right != target).sum() > 2 and (right == target).sum() > 2:
+                continue
+            exact = np.array([oracle.project(n, X[q]) < c for q in range(N)])
+            if (exact == target).all() or (exact == ~target).all():
+                found = (p1, p2)
+                break
+        if found:
+            break
+    assert found is not None
