@@ -330,7 +330,9 @@ def run_ours(args, w):
 
     # ---- end to end through host buffers -----------------------------------
     e2e = None
-    if world == 1:
+    if args.no_e2e:
+        pass
+    elif world == 1:
         r = RSFK(random_state=w["seed"])
         times = []
         for i in range(args.e2e_steps + 1):
@@ -523,6 +525,7 @@ def main():
     ap.add_argument("--recall-queries", type=int, default=10_000)
     ap.add_argument("--no-recall", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--ref-trees", type=int, default=0, help="reference arm: time this many trees and scale")
     ap.add_argument("--ref-timeout", type=int, default=900)

@@ -31,7 +31,8 @@ struct Node {
     int pstart, pcount;
     int tbl;        // row of the replay table, or -1
     int chunk_base; // first work chunk of this node in the level's chunk list
-    int pad0, pad1;
+    int level;      // depth of the node (root = 0)
+    int pad1;
 };
 
 struct LevelCounters {
@@ -42,7 +43,11 @@ struct LevelCounters {
     int min_leaf;
     int error;
     int active_next; // points of the next level's open nodes
-    int pad1;
+    int n_small;     // nodes handed to the in-CTA subtree kernel
+    int max_level;   // deepest level any subtree reached
+    int pad0;
+    unsigned long long sub_active; // points projected inside subtree CTAs (all levels)
+    unsigned long long sub_nodes;  // nodes split inside subtree CTAs
 };
 
 // Work counters a benchmark reads to turn kernel times into achieved bytes/s.
@@ -73,7 +78,7 @@ struct Context {
 
     enum Slot {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
-        NODES_A, NODES_B, NODE_SPLIT, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
+        NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
         SNAPSHOT, EXPLORE_COUNT, N_SLOTS
     };
     Stats stats;

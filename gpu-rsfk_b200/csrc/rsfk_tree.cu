@@ -20,6 +20,8 @@
 // src/kernels/build_tree_create_nodes.cu:88-104, src/kernels/create_node.cu:60-66,120-134.
 // The arithmetic keeps the reference's summation order so that the side of
 // every point is bit-for-bit the reference's for the same split pair.
+#include <cstdlib>
+
 #include "rsfk_context.h"
 
 namespace rsfk {
@@ -79,16 +81,115 @@ __device__ __forceinline__ float load_hyperplane(const float* __restrict__ pts, 
 }
 
 // ---------------------------------------------------------------------------
+// Side bits of up to 32 rows against the hyperplane (sN[D] in shared memory, c).
+// Lane q < here holds the id of row q in my_id.  Returns the mask of rows with
+// n.x < c.  Both variants accumulate term k in "virtual lane" k%32 and combine
+// the 32 partial sums in the xor-butterfly order, so the projection carries the
+// bits of the reference's warp-per-point sum.
+// ---------------------------------------------------------------------------
+
+// Scalar loads: the warp takes four rows at a time, lane l owns terms l, l+32, ...
+__device__ __forceinline__ unsigned project_group_scalar(const float* __restrict__ pts, int D,
+                                                         const float* sN, float c, int my_id, int here,
+                                                         int lane)
+{
+    unsigned mask = 0;
+    for (int q = 0; q < here; q += 4) {
+        float acc[4];
+        const float* row[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int id = __shfl_sync(RSFK_FULL, my_id, min(q + u, here - 1));
+            row[u] = pts + (size_t)id * D;
+            acc[u] = 0.0f;
+        }
+        for (int k = lane; k < D; k += 32) {
+            const float nk = sN[k];
+            float x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) x[u] = __ldg(row[u] + k);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = __fmaf_rn(nk, x[u], acc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float pr = butterfly_sum(acc[u]);
+            if (q + u < here && pr < c) mask |= 1u << (q + u);
+        }
+    }
+    return mask;
+}
+
+// 16-byte loads (D % 4 == 0, 16-byte aligned rows): eight lanes share a row,
+// lane g of the eight owns terms 4g..4g+3 (+32, +64, ...), i.e. virtual lanes
+// 4g..4g+3; sixteen rows are in flight per warp.
+__device__ __forceinline__ unsigned project_group_vec4(const float* __restrict__ pts, int D,
+                                                       const float* sN, float c, int my_id, int here,
+                                                       int lane)
+{
+    const int g = lane & 7, rr = lane >> 3;
+    const float4* sN4 = reinterpret_cast<const float4*>(sN);
+    const int D4 = D >> 2;
+    unsigned mask = 0;
+    for (int q0 = 0; q0 < here; q0 += 16) {
+        float acc[4][4];
+        const float4* row[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int q = q0 + 4 * r + rr;
+            const int id = __shfl_sync(RSFK_FULL, my_id, min(q, here - 1));
+            row[r] = reinterpret_cast<const float4*>(pts + (size_t)id * D);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+        }
+#pragma unroll 2
+        for (int k4 = g; k4 < D4; k4 += 8) {
+            const float4 n = sN4[k4];
+            float4 x[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) x[r] = __ldg(row[r] + k4);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                acc[r][0] = __fmaf_rn(n.x, x[r].x, acc[r][0]);
+                acc[r][1] = __fmaf_rn(n.y, x[r].y, acc[r][1]);
+                acc[r][2] = __fmaf_rn(n.z, x[r].z, acc[r][2]);
+                acc[r][3] = __fmaf_rn(n.w, x[r].w, acc[r][3]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float t = __fadd_rn(__fadd_rn(acc[r][0], acc[r][1]), __fadd_rn(acc[r][2], acc[r][3]));
+            t = __fadd_rn(t, __shfl_xor_sync(RSFK_FULL, t, 1));
+            t = __fadd_rn(t, __shfl_xor_sync(RSFK_FULL, t, 2));
+            t = __fadd_rn(t, __shfl_xor_sync(RSFK_FULL, t, 4));
+            const int q = q0 + 4 * r + rr;
+            const unsigned bal = __ballot_sync(RSFK_FULL, g == 0 && q < here && t < c);
+            // lanes 0, 8, 16, 24 carry rows q0+4r+0..3
+            mask |= (((bal >> 0) & 1u) | (((bal >> 8) & 1u) << 1) | (((bal >> 16) & 1u) << 2) |
+                     (((bal >> 24) & 1u) << 3)) << (q0 + 4 * r);
+        }
+    }
+    return mask;
+}
+
+__device__ __forceinline__ unsigned project_group(const float* __restrict__ pts, int D, bool vec4,
+                                                  const float* sN, float c, int my_id, int here, int lane)
+{
+    return vec4 ? project_group_vec4(pts, D, sN, c, my_id, here, lane)
+                : project_group_scalar(pts, D, sN, c, my_id, here, lane);
+}
+
+// ---------------------------------------------------------------------------
 // project, any D: one warp per point, four points in flight per warp.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(TREE_THREADS)
 k_project_wide(const float* __restrict__ pts, int D, const int* __restrict__ perm,
                const Node* __restrict__ nodes, const int* __restrict__ chunk_node,
                unsigned* __restrict__ side_bits, int* __restrict__ chunk_left,
-               const int4* __restrict__ table, int n_table, int seed, int level)
+               const int4* __restrict__ table, int n_table, int seed, int level, int vec4)
 {
-    extern __shared__ float smem[];
-    float* sN = smem;
+    extern __shared__ float4 smem4[];
+    float* sN = reinterpret_cast<float*>(smem4);
     __shared__ float sC;
     __shared__ int sPair[2];
     __shared__ int sLeft;
@@ -114,30 +215,7 @@ k_project_wide(const float* __restrict__ pts, int D, const int* __restrict__ per
         const int base = w * 32;
         const int here = min(32, cnt - base);
         const int my_id = lane < here ? ids[base + lane] : -1;
-        unsigned mask = 0;
-        for (int q = 0; q < here; q += 4) {
-            float acc[4];
-            const float* row[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                int id = __shfl_sync(RSFK_FULL, my_id, min(q + u, here - 1));
-                row[u] = pts + (size_t)id * D;
-                acc[u] = 0.0f;
-            }
-            for (int k = lane; k < D; k += 32) {
-                const float nk = sN[k];
-                float x[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) x[u] = __ldg(row[u] + k);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) acc[u] = __fmaf_rn(nk, x[u], acc[u]);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                float pr = butterfly_sum(acc[u]);
-                if (q + u < here && pr < c) mask |= 1u << (q + u);
-            }
-        }
+        const unsigned mask = project_group(pts, D, vec4 != 0, sN, c, my_id, here, lane);
         if (lane == 0) {
             side_bits[(size_t)chunk * CHUNK_WORDS + w] = mask;
             left_total += here - __popc(mask);
@@ -225,11 +303,63 @@ __device__ __forceinline__ void emit_leaf(int start, int count, int* leaf_start,
     atomicMin(&cnt->min_leaf, count);
 }
 
+// Children of a node whose stable partition put n_left points on the left.
+struct Children {
+    int n;            // 1 or 2
+    int start[2], count[2];
+    int pstart[2], pcount[2]; // segment the child's own split pair is drawn from
+    int side[2];      // which side of the parent the child (or the survivor of a merge) is
+    bool leaf[2];
+    int final_flags;  // bit0: left points are final, bit1: right points are final
+};
+
+__device__ __forceinline__ Children decide_children(int start, int count, int nL, int min_children,
+                                                    int max_children)
+{
+    Children c;
+    const int nR = count - nL;
+    if (nL > 0 && nR > 0 && nL >= min_children && nR >= min_children) {
+        c.n = 2;
+        c.start[0] = c.pstart[0] = start;      c.count[0] = c.pcount[0] = nL; c.side[0] = 0;
+        c.start[1] = c.pstart[1] = start + nL; c.count[1] = c.pcount[1] = nR; c.side[1] = 1;
+        c.leaf[0] = nL <= max_children - 2;
+        c.leaf[1] = nR <= max_children - 2;
+    } else if (nL > 0 && nR > 0) {
+        // the side with fewer than min_children points dissolves into the other,
+        // which keeps the split pair drawn from its own segment
+        int keep = (nL < min_children) ? 1 : 0;
+        if (nL < min_children && nR < min_children) keep = 0;
+        c.n = 1;
+        c.start[0] = start; c.count[0] = count;
+        c.pstart[0] = keep ? start + nL : start;
+        c.pcount[0] = keep ? nR : nL;
+        c.side[0] = keep;
+        c.leaf[0] = count <= max_children;
+        c.leaf[1] = c.leaf[0];
+    } else {
+        c.n = 1;
+        c.start[0] = c.pstart[0] = start; c.count[0] = c.pcount[0] = count;
+        c.side[0] = nL > 0 ? 0 : 1;
+        c.leaf[0] = count <= max_children - 2;
+        c.leaf[1] = c.leaf[0];
+    }
+    c.final_flags = 0;
+    return c;
+}
+
+__device__ __forceinline__ int child_table_row(const int4* __restrict__ table, int n_table, int tbl, int side)
+{
+    if (table == nullptr || tbl < 0 || tbl >= n_table) return -1;
+    const int4 t = table[tbl];
+    return side ? t.w : t.z;
+}
+
 __global__ void __launch_bounds__(TREE_THREADS)
 k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_left,
          Node* __restrict__ nodes_out, int node_cap, int* __restrict__ chunk_node_out, int chunk_cap,
          NodeSplit* __restrict__ split, int* __restrict__ leaf_start, int* __restrict__ leaf_count,
-         int leaf_cap, LevelCounters* __restrict__ cnt, const int4* __restrict__ table, int n_table,
+         int leaf_cap, Node* __restrict__ small_nodes, int small_cap, int small_limit, int child_level,
+         LevelCounters* __restrict__ cnt, const int4* __restrict__ table, int n_table,
          int min_children, int max_children)
 {
     const int lane = threadIdx.x & 31;
@@ -252,53 +382,41 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
         if (c < n_chunks) chunk_left[nd.chunk_base + c] = carry + incl - v;
         carry += __shfl_sync(RSFK_FULL, incl, 31);
     }
-    const int nL = carry, nR = nd.count - nL;
+    const int nL = carry;
+    const Children ch = decide_children(nd.start, nd.count, nL, min_children, max_children);
 
-    // children: {start, count, own segment, side, leaf}
-    int n_ch = 0;
-    int ch_start[2], ch_count[2], ch_pstart[2], ch_pcount[2], ch_side[2], ch_leaf[2];
+    // a child's points are final (copied to perm_final by the scatter) when it
+    // is a leaf or small enough to be finished inside one CTA
     int flags = 0;
-    if (nL > 0 && nR > 0 && nL >= min_children && nR >= min_children) {
-        n_ch = 2;
-        ch_start[0] = ch_pstart[0] = nd.start;      ch_count[0] = ch_pcount[0] = nL; ch_side[0] = 0;
-        ch_start[1] = ch_pstart[1] = nd.start + nL; ch_count[1] = ch_pcount[1] = nR; ch_side[1] = 1;
-        ch_leaf[0] = nL <= max_children - 2;
-        ch_leaf[1] = nR <= max_children - 2;
-        flags = (ch_leaf[0] ? 1 : 0) | (ch_leaf[1] ? 2 : 0);
-    } else if (nL > 0 && nR > 0) {
-        // the side with fewer than min_children points dissolves into the other,
-        // which keeps the split pair drawn from its own segment
-        int keep = (nL < min_children) ? 1 : 0;
-        if (nL < min_children && nR < min_children) keep = 0;
-        n_ch = 1;
-        ch_start[0] = nd.start; ch_count[0] = nd.count;
-        ch_pstart[0] = keep ? nd.start + nL : nd.start;
-        ch_pcount[0] = keep ? nR : nL;
-        ch_side[0] = keep;
-        ch_leaf[0] = nd.count <= max_children;
-        flags = ch_leaf[0] ? 3 : 0;
-    } else {
-        n_ch = 1;
-        ch_start[0] = ch_pstart[0] = nd.start; ch_count[0] = ch_pcount[0] = nd.count;
-        ch_side[0] = nL > 0 ? 0 : 1;
-        ch_leaf[0] = nd.count <= max_children - 2;
-        flags = ch_leaf[0] ? 3 : 0;
-    }
-    if (lane == 0) {
-        split[node].n_left = nL;
-        split[node].flags = flags;
-    }
-    for (int k = 0; k < n_ch; ++k) {
-        if (ch_leaf[k]) {
-            if (lane == 0) emit_leaf(ch_start[k], ch_count[k], leaf_start, leaf_count, leaf_cap, cnt);
+    for (int k = 0; k < ch.n; ++k) {
+        const bool small = !ch.leaf[k] && ch.count[k] <= small_limit;
+        const bool fin = ch.leaf[k] || small;
+        if (fin) flags |= (ch.n == 2) ? (1 << k) : 3;
+        if (ch.leaf[k]) {
+            if (lane == 0) emit_leaf(ch.start[k], ch.count[k], leaf_start, leaf_count, leaf_cap, cnt);
             continue;
         }
-        const int nch = (ch_count[k] + CHUNK - 1) / CHUNK;
+        Node o;
+        o.start = ch.start[k];   o.count = ch.count[k];
+        o.pstart = ch.pstart[k]; o.pcount = ch.pcount[k];
+        o.tbl = child_table_row(table, n_table, nd.tbl, ch.side[k]);
+        o.chunk_base = 0;
+        o.level = child_level;
+        o.pad1 = 0;
+        if (small) {
+            if (lane == 0) {
+                const int slot = atomicAdd(&cnt->n_small, 1);
+                if (slot < small_cap) small_nodes[slot] = o;
+                else cnt->error = RSFK_ERR_OVERFLOW;
+            }
+            continue;
+        }
+        const int nch = (ch.count[k] + CHUNK - 1) / CHUNK;
         int slot = 0, cb = 0;
         if (lane == 0) {
             slot = atomicAdd(&cnt->n_nodes_next, 1);
             cb = atomicAdd(&cnt->n_chunks_next, nch);
-            atomicAdd(&cnt->active_next, ch_count[k]);
+            atomicAdd(&cnt->active_next, ch.count[k]);
         }
         slot = __shfl_sync(RSFK_FULL, slot, 0);
         cb = __shfl_sync(RSFK_FULL, cb, 0);
@@ -307,19 +425,14 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
             continue;
         }
         if (lane == 0) {
-            Node o;
-            o.start = ch_start[k];   o.count = ch_count[k];
-            o.pstart = ch_pstart[k]; o.pcount = ch_pcount[k];
-            o.tbl = -1;
-            if (table != nullptr && nd.tbl >= 0 && nd.tbl < n_table) {
-                int4 t = table[nd.tbl];
-                o.tbl = ch_side[k] ? t.w : t.z;
-            }
             o.chunk_base = cb;
-            o.pad0 = o.pad1 = 0;
             nodes_out[slot] = o;
         }
         for (int c = lane; c < nch; c += 32) chunk_node_out[cb + c] = slot;
+    }
+    if (lane == 0) {
+        split[node].n_left = nL;
+        split[node].flags = flags;
     }
 }
 
@@ -373,6 +486,201 @@ k_scatter(const int* __restrict__ perm_in, int* __restrict__ perm_out, int* __re
     }
 }
 
+// ---------------------------------------------------------------------------
+// subtree: one CTA finishes a node of at most SUB_MAX points, all its levels,
+// without leaving the SM: ids ping-pong in shared memory, rows are read from
+// global memory (L2 after the first level).  Same rules and arithmetic as the
+// level kernels, so the buckets are identical to a level-synchronous build.
+// ---------------------------------------------------------------------------
+constexpr int SUB_MAX = 2048;        // largest node a CTA takes
+constexpr int SUB_NODES = 128;       // open nodes a CTA can hold per level
+constexpr int SUB_GROUPS = SUB_MAX / 32 + SUB_NODES;
+
+struct SubNode {
+    int start, count;   // relative to the CTA's segment
+    int pstart, pcount; // relative
+    int tbl;
+};
+
+__global__ void __launch_bounds__(TREE_THREADS)
+k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
+          const Node* __restrict__ small_nodes, int* __restrict__ leaf_start,
+          int* __restrict__ leaf_count, int leaf_cap, LevelCounters* __restrict__ cnt,
+          const int4* __restrict__ table, int n_table, int seed, int min_children, int max_children,
+          int max_depth, int vec4)
+{
+    extern __shared__ float4 smem4[]; // per-warp normal vectors: n_warps * D floats
+    float* smem = reinterpret_cast<float*>(smem4);
+    __shared__ int sIds[2][SUB_MAX];
+    __shared__ unsigned sMask[SUB_GROUPS];
+    __shared__ int sGroupNode[SUB_GROUPS];
+    __shared__ SubNode sOpen[2][SUB_NODES];
+    __shared__ int sGroupBase[SUB_NODES];
+    __shared__ int sCount[2];          // open nodes of the next level, total groups
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    float* sN = smem + (size_t)warp * D;
+    const Node root = small_nodes[blockIdx.x];
+    int* seg = perm_final + root.start;
+
+    for (int i = threadIdx.x; i < root.count; i += blockDim.x) sIds[0][i] = seg[i];
+    if (threadIdx.x == 0) {
+        SubNode r;
+        r.start = 0; r.count = root.count;
+        r.pstart = root.pstart - root.start; r.pcount = root.pcount;
+        r.tbl = root.tbl;
+        sOpen[0][0] = r;
+    }
+    int n_open = 1, cur = 0, level = root.level;
+    unsigned long long my_active = 0, my_nodes = 0;
+    __syncthreads();
+
+    while (n_open > 0) {
+        if (level + 1 >= max_depth) {
+            // depth limit: open nodes become leaves of at most max_children points
+            for (int i = warp; i < n_open; i += n_warps) {
+                const SubNode nd = sOpen[cur][i];
+                for (int k = lane; k < nd.count; k += 32) seg[nd.start + k] = sIds[cur][nd.start + k];
+                if (lane == 0) {
+                    const int piece = max(1, max_children);
+                    const int q = (nd.count + piece - 1) / piece;
+                    for (int j = 0; j < q; ++j) {
+                        int a = (int)((long long)nd.count * j / q), b = (int)((long long)nd.count * (j + 1) / q);
+                        emit_leaf(root.start + nd.start + a, b - a, leaf_start, leaf_count, leaf_cap, cnt);
+                    }
+                }
+            }
+            break;
+        }
+        // ---- group list: 32 consecutive positions of one open node ----------
+        if (warp == 0) {
+            int carry = 0;
+            for (int i0 = 0; i0 < n_open; i0 += 32) {
+                const int i = i0 + lane;
+                const int g = i < n_open ? (sOpen[cur][i].count + 31) >> 5 : 0;
+                int incl = g;
+#pragma unroll
+                for (int s = 1; s < 32; s <<= 1) {
+                    int t = __shfl_up_sync(RSFK_FULL, incl, s);
+                    if (lane >= s) incl += t;
+                }
+                if (i < n_open) sGroupBase[i] = carry + incl - g;
+                carry += __shfl_sync(RSFK_FULL, incl, 31);
+            }
+            if (lane == 0) { sCount[0] = 0; sCount[1] = carry; }
+        }
+        __syncthreads();
+        const int n_groups = sCount[1];
+        for (int i = warp; i < n_open; i += n_warps) {
+            const int g0 = sGroupBase[i], ng = (sOpen[cur][i].count + 31) >> 5;
+            for (int g = lane; g < ng; g += 32) sGroupNode[g0 + g] = i;
+            if (lane == 0) { my_active += sOpen[cur][i].count; my_nodes += 1; }
+        }
+        __syncthreads();
+        // ---- projection: one warp per group ---------------------------------
+        for (int g = warp; g < n_groups; g += n_warps) {
+            const int i = sGroupNode[g];
+            const SubNode nd = sOpen[cur][i];
+            const int off = (g - sGroupBase[i]) * 32;
+            const int here = min(32, nd.count - off);
+            int p1, p2;
+            if (table != nullptr && nd.tbl >= 0 && nd.tbl < n_table) {
+                const int4 t = table[nd.tbl];
+                p1 = t.x; p2 = t.y;
+            } else {
+                int r1, r2;
+                sample_positions(seed, level, root.start + nd.pstart, nd.pcount, r1, r2);
+                p1 = sIds[cur][nd.pstart + r1];
+                p2 = sIds[cur][nd.pstart + r2];
+            }
+            const float* x1 = pts + (size_t)p1 * D;
+            const float* x2 = pts + (size_t)p2 * D;
+            float c = 0.0f;
+            __syncwarp();
+            if (level == 0) {
+                for (int k = lane; k < D; k += 32) sN[k] = __fsub_rn(__ldg(x1 + k), __ldg(x2 + k));
+                __syncwarp();
+                if (lane == 0)
+                    for (int k = 0; k < D; ++k)
+                        c = __fadd_rn(c, __fmul_rn(__fmul_rn(sN[k], __fadd_rn(__ldg(x1 + k), __ldg(x2 + k))), 0.5f));
+                c = __shfl_sync(RSFK_FULL, c, 0);
+            } else {
+                for (int k = lane; k < D; k += 32) {
+                    const float a = __ldg(x1 + k), b = __ldg(x2 + k);
+                    const float nk = __fsub_rn(a, b);
+                    sN[k] = nk;
+                    c = __fadd_rn(c, __fmul_rn(__fmul_rn(nk, __fadd_rn(a, b)), 0.5f));
+                }
+                c = butterfly_sum(c);
+            }
+            __syncwarp();
+            const int my_id = lane < here ? sIds[cur][nd.start + off + lane] : -1;
+            const unsigned mask = project_group(pts, D, vec4 != 0, sN, c, my_id, here, lane);
+            if (lane == 0) sMask[g] = mask;
+        }
+        __syncthreads();
+        // ---- partition + decision: one warp per open node -------------------
+        const int nxt = cur ^ 1;
+        for (int i = warp; i < n_open; i += n_warps) {
+            const SubNode nd = sOpen[cur][i];
+            const int g0 = sGroupBase[i], ng = (nd.count + 31) >> 5;
+            int nL = 0;
+            for (int g = lane; g < ng; g += 32) {
+                const int here = min(32, nd.count - g * 32);
+                const unsigned valid = here >= 32 ? 0xffffffffu : ((1u << here) - 1u);
+                nL += __popc(~sMask[g0 + g] & valid);
+            }
+#pragma unroll
+            for (int s = 16; s >= 1; s >>= 1) nL += __shfl_xor_sync(RSFK_FULL, nL, s);
+            int lefts = 0;
+            for (int g = 0; g < ng; ++g) {
+                const int here = min(32, nd.count - g * 32);
+                const unsigned valid = here >= 32 ? 0xffffffffu : ((1u << here) - 1u);
+                const unsigned m = sMask[g0 + g] & valid;
+                if (lane < here) {
+                    const bool right = (m >> lane) & 1u;
+                    const int lb = lefts + __popc(~m & ((1u << lane) - 1u));
+                    const int pos = g * 32 + lane;
+                    const int dest = right ? nL + (pos - lb) : lb;
+                    sIds[nxt][nd.start + dest] = sIds[cur][nd.start + pos];
+                }
+                lefts += __popc(~m & valid);
+            }
+            __syncwarp();
+            const Children ch = decide_children(nd.start, nd.count, nL, min_children, max_children);
+            for (int k = 0; k < ch.n; ++k) {
+                if (ch.leaf[k]) {
+                    for (int q = lane; q < ch.count[k]; q += 32)
+                        seg[ch.start[k] + q] = sIds[nxt][ch.start[k] + q];
+                    if (lane == 0)
+                        emit_leaf(root.start + ch.start[k], ch.count[k], leaf_start, leaf_count, leaf_cap, cnt);
+                } else if (lane == 0) {
+                    const int slot = atomicAdd(&sCount[0], 1);
+                    if (slot < SUB_NODES) {
+                        SubNode o;
+                        o.start = ch.start[k];   o.count = ch.count[k];
+                        o.pstart = ch.pstart[k]; o.pcount = ch.pcount[k];
+                        o.tbl = child_table_row(table, n_table, nd.tbl, ch.side[k]);
+                        sOpen[nxt][slot] = o;
+                    } else {
+                        cnt->error = RSFK_ERR_OVERFLOW;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        n_open = min(sCount[0], SUB_NODES);
+        cur = nxt;
+        level++;
+        __syncthreads();
+    }
+    if (lane == 0) {
+        if (my_active) atomicAdd(&cnt->sub_active, my_active);
+        if (my_nodes) atomicAdd(&cnt->sub_nodes, my_nodes);
+    }
+    if (threadIdx.x == 0) atomicMax(&cnt->max_level, level);
+}
+
 // Depth limit reached: every open node becomes leaves of at most max_children
 // points (consecutive pieces of its segment).
 __global__ void k_force_leaves(const Node* __restrict__ nodes, int n_nodes, const int* __restrict__ perm,
@@ -407,10 +715,11 @@ __global__ void k_tree_init(Node* nodes, int* chunk_node, int n_chunks, int N, i
         Node r;
         r.start = 0; r.count = N; r.pstart = 0; r.pcount = N;
         r.tbl = has_table ? 0 : -1;
-        r.chunk_base = 0; r.pad0 = r.pad1 = 0;
+        r.chunk_base = 0; r.level = 0; r.pad1 = 0;
         nodes[0] = r;
         cnt->n_nodes_next = 0; cnt->n_chunks_next = 0; cnt->n_leaves = 0;
         cnt->max_leaf = 0; cnt->min_leaf = 0x7fffffff; cnt->error = 0; cnt->active_next = 0;
+        cnt->n_small = 0; cnt->max_level = 0; cnt->sub_active = 0; cnt->sub_nodes = 0;
     }
     for (int c = t; c < n_chunks; c += gridDim.x * blockDim.x) chunk_node[c] = 0;
 }
@@ -428,6 +737,7 @@ __global__ void k_single_leaf(int* leaf_start, int* leaf_count, int N, LevelCoun
     leaf_count[0] = N;
     cnt->n_leaves = 1; cnt->max_leaf = N; cnt->min_leaf = N; cnt->error = 0;
     cnt->n_nodes_next = 0; cnt->n_chunks_next = 0;
+    cnt->n_small = 0; cnt->max_level = 0; cnt->sub_active = 0; cnt->sub_nodes = 0; cnt->active_next = 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -446,7 +756,8 @@ static void launch_project(Context& ctx, const float* pts, int D, const int* per
     else if (D <= 16) RSFK_SMALL(16);
     else
         k_project_wide<<<n_chunks, TREE_THREADS, (size_t)D * sizeof(float), st>>>(
-            pts, D, perm, nodes, chunk_node, side_bits, chunk_left, table, n_table, seed, level);
+            pts, D, perm, nodes, chunk_node, side_bits, chunk_left, table, n_table, seed, level,
+            (D % 4 == 0 && ((uintptr_t)pts & 15) == 0) ? 1 : 0);
 #undef RSFK_SMALL
     count_launches(1);
 }
@@ -483,6 +794,16 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     nodes[0] = (Node*)ctx.scratch(Context::NODES_A, sizeof(Node) * (size_t)node_cap);
     nodes[1] = (Node*)ctx.scratch(Context::NODES_B, sizeof(Node) * (size_t)node_cap);
     NodeSplit* split = (NodeSplit*)ctx.scratch(Context::NODE_SPLIT, sizeof(NodeSplit) * (size_t)node_cap);
+    // nodes at or below small_limit points are finished inside one CTA each
+    int small_limit = 262144 / D;
+    if (small_limit > SUB_MAX) small_limit = SUB_MAX;
+    const long long node_room = (long long)SUB_NODES * open_min;
+    if (small_limit > node_room) small_limit = (int)node_room;
+    const size_t sub_smem = sizeof(float) * (size_t)(TREE_THREADS / 32) * D;
+    if (small_limit < max_children - 1 || sub_smem > 64 * 1024) small_limit = 0; // nothing would qualify
+    if (const char* e = getenv("RSFK_SUBTREE_LIMIT")) small_limit = atoi(e) < small_limit ? atoi(e) : small_limit;
+    const int small_cap = node_cap;
+    Node* small_nodes = (Node*)ctx.scratch(Context::SMALL_NODES, sizeof(Node) * (size_t)small_cap);
     int* leaf_start = (int*)ctx.scratch(Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
     int* leaf_count = (int*)ctx.scratch(Context::LEAF_COUNT, sizeof(int) * (size_t)leaf_cap);
     LevelCounters* cnt = (LevelCounters*)ctx.scratch(Context::COUNTERS, sizeof(LevelCounters));
@@ -521,7 +842,8 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
         k_reset_level<<<1, 1, 0, st>>>(cnt);
         k_decide<<<(n_nodes * 32 + TREE_THREADS - 1) / TREE_THREADS, TREE_THREADS, 0, st>>>(
             nodes[cur], n_nodes, chunk_left, nodes[cur ^ 1], node_cap, chunk_node[cur ^ 1], chunk_cap,
-            split, leaf_start, leaf_count, leaf_cap, cnt, table, n_table, min_children, max_children);
+            split, leaf_start, leaf_count, leaf_cap, small_nodes, small_cap, small_limit, depth, cnt, table,
+            n_table, min_children, max_children);
         k_scatter<<<n_chunks, TREE_THREADS, 0, st>>>(perm[cur], perm[cur ^ 1], perm_final, nodes[cur],
                                                      chunk_node[cur], side_bits, chunk_left, split);
         count_launches(3);
@@ -542,6 +864,18 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
                                                 leaf_count, leaf_cap, cnt, max_children);
         count_launches(1);
     }
+    const int n_small = (N > 1 && levels > 0) ? ctx.host_counters->n_small : 0;
+    if (n_small > 0) {
+        if (sub_smem > 16 * 1024 &&
+            !ctx.check(cudaFuncSetAttribute(k_subtree, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sub_smem),
+                       "subtree smem attribute"))
+            return false;
+        k_subtree<<<n_small, TREE_THREADS, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
+                                                           leaf_count, leaf_cap, cnt, table, n_table, seed,
+                                                           min_children, max_children, max_depth,
+                                                           (D % 4 == 0 && ((uintptr_t)d_points & 15) == 0) ? 1 : 0);
+        count_launches(1);
+    }
     if (!ctx.check(cudaMemcpyAsync(ctx.host_counters, cnt, sizeof(LevelCounters),
                                    cudaMemcpyDeviceToHost, st), "counters D2H") ||
         !ctx.check(cudaStreamSynchronize(st), "tree end"))
@@ -550,6 +884,9 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
         return ctx.fail(ctx.host_counters->error, "tree_build: internal table overflow");
 
     ctx.stats.trees++;
+    ctx.stats.tree_active_points += (long long)ctx.host_counters->sub_active;
+    ctx.stats.tree_nodes += (long long)ctx.host_counters->sub_nodes;
+    if (ctx.host_counters->max_level > levels) levels = ctx.host_counters->max_level;
     out.perm = perm_final;
     out.leaf_start = leaf_start;
     out.leaf_count = leaf_count;
