@@ -223,6 +223,7 @@ def run_ours(args, w):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = os.environ.get("RSFK_NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     N, D, K = args.points or w["N"], w["D"], w["K"]
@@ -335,14 +336,15 @@ def run_ours(args, w):
     elif world == 1:
         r = RSFK(random_state=w["seed"])
         times = []
-        for i in range(args.e2e_steps + 1):
+        for i in range(args.e2e_steps + 2):
             r.find_nearest_neighbors(X, K, n_trees=w["trees"], min_tree_children=w["min"],
                                      max_tree_children=w["max"], nn_exploring_factor=w["sweeps"])
-            if i > 0:
+            if i > 1:          # two untimed calls: context creation, scratch growth
                 times.append(r._last_search_time)
         t_e2e = float(np.mean(times))
         e2e = dict(value=N / t_e2e, unit="points/s", h2d_bytes_per_step=4 * N * D + 8 * N * K,
                    d2h_bytes_per_step=8 * N * K, ms_per_step=t_e2e * 1e3,
+                   ms_each=[round(t * 1e3, 2) for t in times],
                    api="gpu_rsfk.RSFK.find_nearest_neighbors -> pymodule_rsfk_knn (host buffers)")
     else:
         out_i = torch.empty((rdist.row_block(N, world), K), dtype=torch.int32).pin_memory()
@@ -521,7 +523,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-worker"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--points", type=int, default=0, help="override N (debugging)")
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--recall-queries", type=int, default=10_000)
     ap.add_argument("--no-recall", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -179,17 +179,22 @@ void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TRE
         return;
     }
     const size_t pts_bytes = sizeof(float) * (size_t)N * D, list_elems = (size_t)N * K;
+    const double ta0 = now_s();
     float* d_points = nullptr;
     int* d_idx = nullptr;
     float* d_dist = nullptr;
     bool ok = c.check(cudaMalloc((void**)&d_points, pts_bytes), "cudaMalloc(points)") &&
               c.check(cudaMalloc((void**)&d_idx, sizeof(int) * list_elems), "cudaMalloc(indices)") &&
               c.check(cudaMalloc((void**)&d_dist, sizeof(float) * list_elems), "cudaMalloc(distances)");
+    if (ok && VERBOSE >= 1) printf("Device allocations take %lf seconds\n", now_s() - ta0);
     ok = ok && c.check(cudaMemcpyAsync(d_points, points, pts_bytes, cudaMemcpyHostToDevice, c.stream), "H2D points");
     ok = ok && c.check(cudaMemcpyAsync(d_idx, knn_indices, sizeof(int) * list_elems, cudaMemcpyHostToDevice, c.stream), "H2D indices");
     ok = ok && c.check(cudaMemcpyAsync(d_dist, knn_sqr_distances, sizeof(float) * list_elems, cudaMemcpyHostToDevice, c.stream), "H2D distances");
+    const double th0 = now_s();
     ok = ok && rsfk::sort_rows(c, d_idx, d_dist, N, K);
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "H2D");
     const double t0 = now_s();
+    if (ok && VERBOSE >= 1) printf("Host to device copies take %lf seconds\n", t0 - th0);
     ok = ok && run_forest(h, d_points, N, D, K, n_trees, 0, 1, MIN_TREE_CHILD, MAX_TREE_CHILD, MAX_DEPTH,
                           RANDOM_STATE, d_idx, d_dist, log_forest, VERBOSE);
     const double t1 = now_s();
@@ -204,6 +209,7 @@ void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TRE
     ok = ok && c.check(cudaMemcpyAsync(knn_indices, d_idx, sizeof(int) * list_elems, cudaMemcpyDeviceToHost, c.stream), "D2H indices");
     ok = ok && c.check(cudaMemcpyAsync(knn_sqr_distances, d_dist, sizeof(float) * list_elems, cudaMemcpyDeviceToHost, c.stream), "D2H distances");
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "D2H");
+    if (ok && VERBOSE >= 1) printf("Device to host copies take %lf seconds\n", now_s() - t2);
     cudaStreamSynchronize(c.stream);
     if (d_points) cudaFree(d_points);
     if (d_idx) cudaFree(d_idx);
