@@ -487,3 +487,91 @@ bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d
 }
 
 } // namespace rsfk
+
+// ---------------------------------------------------------------------------
+// Exploration sweep for callers that must not allocate.
+//
+// A sweep needs a frozen copy of the index lists (every point reads its
+// neighbours' OLD rows while rows are being rewritten) and an 8-byte work
+// counter.  The other entry points take that memory from the caller or from the
+// context's pool (cudaMalloc).  This one keeps it in a fixed array that is part
+// of the library image, so the call touches no allocator at all.
+// ---------------------------------------------------------------------------
+#include "../../include/rsfk_b200.h"
+
+namespace {
+
+constexpr long long STATIC_SNAPSHOT_INTS = RSFK_STATIC_SWEEP_MAX_ENTRIES;
+constexpr int STATIC_MAX_DEVICES = 64;
+
+// Snapshot of the index lists, then one 256-byte slot holding the work counter.
+// In host code this name is only a handle for cudaGetSymbolAddress; it is not a
+// device address and must never be handed to a kernel directly.
+static __device__ __align__(256) int g_static_sweep_scratch[STATIC_SNAPSHOT_INTS + 64];
+
+int* g_static_scratch_addr[STATIC_MAX_DEVICES]; // per device, filled on first use
+int g_static_sm_count[STATIC_MAX_DEVICES];
+
+int static_fail(int code, const char* msg)
+{
+    fprintf(stderr, "rsfk_explore_sweep_static: %s\n", msg);
+    return code;
+}
+
+} // namespace
+
+extern "C" int rsfk_explore_sweep_static(const float* d_points, int N, int D, int K, int* d_idx,
+                                         float* d_dist, void* stream)
+{
+    using namespace rsfk;
+    if (!d_points || !d_idx || !d_dist || N <= 0 || D <= 0 || K <= 0)
+        return static_fail(RSFK_ERR_ARG, "invalid argument");
+    if (K > list_capacity()) return static_fail(RSFK_ERR_UNSUPPORTED, "K above 256 is not supported");
+    if ((long long)N * K > STATIC_SNAPSHOT_INTS)
+        return static_fail(RSFK_ERR_ARG,
+                           "N*K exceeds RSFK_STATIC_SWEEP_MAX_ENTRIES, the capacity of the built-in snapshot "
+                           "buffer; use rsfk_dev_explore with a caller-provided snapshot instead");
+    const size_t smem = sizeof(float) * (size_t)KNN_WARPS * D + sizeof(int) * (size_t)KNN_WARPS * EXP_QUEUE;
+    if (smem > 200 * 1024) return static_fail(RSFK_ERR_UNSUPPORTED, "D too large for the sweep kernel");
+
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return static_fail(RSFK_ERR_CUDA, cudaGetErrorString(err));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) return static_fail(RSFK_ERR_ARG, "device ordinal out of range");
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // one-time set-up for this device (it is current): resolve the device
+        // address of the built-in array and read the SM count
+        int* addr = nullptr;
+        err = cudaGetSymbolAddress((void**)&addr, g_static_sweep_scratch);
+        if (err != cudaSuccess || addr == nullptr)
+            return static_fail(RSFK_ERR_CUDA, err != cudaSuccess ? cudaGetErrorString(err) : "null symbol address");
+        int sms = 0;
+        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return static_fail(RSFK_ERR_CUDA, cudaGetErrorString(err));
+        g_static_sm_count[dev] = sms > 0 ? sms : 148;
+        g_static_scratch_addr[dev] = addr;
+    }
+    int* snapshot = g_static_scratch_addr[dev];
+    unsigned long long* counter = reinterpret_cast<unsigned long long*>(snapshot + STATIC_SNAPSHOT_INTS);
+    cudaStream_t st = (cudaStream_t)stream;
+
+    // the array keeps whatever the previous call left: overwrite the part this
+    // call reads and zero the counter
+    err = cudaMemcpyAsync(snapshot, d_idx, sizeof(int) * (size_t)N * K, cudaMemcpyDeviceToDevice, st);
+    if (err == cudaSuccess) err = cudaMemsetAsync(counter, 0, sizeof(unsigned long long), st);
+    if (err != cudaSuccess) return static_fail(RSFK_ERR_CUDA, cudaGetErrorString(err));
+
+    long long blocks = ((long long)N + KNN_WARPS - 1) / KNN_WARPS;
+    if (blocks > (long long)g_static_sm_count[dev] * 8) blocks = (long long)g_static_sm_count[dev] * 8;
+    RSFK_DISPATCH_KPL(K, {
+        err = cudaFuncSetAttribute(k_explore<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess) {
+            k_explore<KPL><<<(int)blocks, KNN_THREADS, smem, st>>>(d_points, N, D, K, snapshot, d_idx, d_dist,
+                                                                  0, N, 0, counter);
+            err = cudaGetLastError();
+        }
+    });
+    if (err != cudaSuccess) return static_fail(RSFK_ERR_CUDA, cudaGetErrorString(err));
+    rsfk::count_launches(1);
+    return RSFK_OK;
+}

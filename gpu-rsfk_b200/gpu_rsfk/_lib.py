@@ -84,6 +84,8 @@ def load():
     L.rsfk_dev_explore.argtypes = [vp, vp, i, i, i, vp, vp, vp, i, i, i]
     L.rsfk_dev_merge_lists.restype = i
     L.rsfk_dev_merge_lists.argtypes = [vp, ll, i, i, vp, vp, vp, vp]
+    L.rsfk_explore_sweep_static.restype = i
+    L.rsfk_explore_sweep_static.argtypes = [vp, i, i, i, vp, vp, vp]
     _lib = L
     return L
 

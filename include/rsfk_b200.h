@@ -145,6 +145,45 @@ RSFK_EXPORT int rsfk_dev_merge_lists(rsfk_ctx* ctx, long long rows, int K, int G
                          const int* const* d_idx_lists, const float* const* d_dist_lists,
                          int* d_out_idx, float* d_out_dist);
 
+/* ---------------------------------------------------------------- part 4 -- */
+
+/* Capacity, in K-list entries (N*K), of the snapshot buffer built into the
+ * library for rsfk_explore_sweep_static: 4 Mi entries = 16 MiB of device memory
+ * that every GPU using the library holds from load until the process exits. */
+#define RSFK_STATIC_SWEEP_MAX_ENTRIES (4 * 1024 * 1024)
+
+/* One neighbour-of-neighbour sweep over all N rows, in place, WITHOUT touching
+ * any allocator.  This entry point has no counterpart in the reference.
+ *
+ * It exists for hosts that cannot call cudaMalloc where the sweep runs: an
+ * application that hands its whole device-memory budget to its own arena at
+ * start-up, a service whose latency rules forbid the device-wide
+ * synchronisation cudaMalloc/cudaFree imply, or a plug-in API that bans
+ * allocation after initialisation.  Everything else the sweep needs -- the
+ * frozen copy of the index lists and a work counter -- lives in a fixed array
+ * inside the library image, so the call makes no cudaMalloc, cudaFree or other
+ * allocating call and needs no rsfk_ctx.
+ *
+ *   d_points [N*D], d_idx / d_dist [N*K]: device pointers on the CURRENT
+ *   device; rows must be canonical (see rsfk_dev_sort_rows); they are updated
+ *   in place exactly as rsfk_dev_explore would update them from a snapshot
+ *   taken at the start of the call.  stream: cudaStream_t as void*
+ *   (NULL = legacy default stream); the work is enqueued, not awaited.
+ *
+ * Limits and rules:
+ *  - N*K <= RSFK_STATIC_SWEEP_MAX_ENTRIES, K <= rsfk_max_neighbors(); larger
+ *    problems are refused with RSFK_ERR_ARG and a message on stderr (use
+ *    rsfk_dev_explore with your own snapshot buffer).
+ *  - The first call on each device looks up the built-in array's device
+ *    address; make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous
+ *    call's contents (each call overwrites what it reads).  Two calls whose GPU
+ *    work overlaps -- different streams, or different host threads -- race on
+ *    it: serialise them.
+ * Returns 0 or an rsfk_status code. */
+RSFK_EXPORT int rsfk_explore_sweep_static(const float* d_points, int N, int D, int K,
+                                          int* d_idx, float* d_dist, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
