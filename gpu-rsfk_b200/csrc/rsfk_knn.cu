@@ -115,6 +115,33 @@ __device__ __forceinline__ void stage_rows(const float* __restrict__ pts, int D,
     }
 }
 
+// Squared distance for D <= VL <= 16, one thread per pair.  In the reference's
+// 32-lane sum every lane then holds at most one term (lanes >= D hold zero), so
+// the result is the butterfly-ordered tree sum of the D squared differences.
+template <int VL>
+__device__ __forceinline__ float small_d_dist(const float* a, const float* b, int D)
+{
+    float acc[VL];
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+        const float df = k < D ? __fsub_rn(a[k], b[k]) : 0.0f;
+        acc[k] = __fmaf_rn(df, df, 0.0f);
+    }
+#pragma unroll
+    for (int stride = 1; stride < VL; stride <<= 1)
+#pragma unroll
+        for (int k = 0; k < VL; k += 2 * stride) acc[k] = __fadd_rn(acc[k], acc[k + stride]);
+    return acc[0];
+}
+
+__device__ __forceinline__ float small_d_dist_any(const float* a, const float* b, int D)
+{
+    if (D <= 2) return small_d_dist<2>(a, b, D);
+    if (D <= 4) return small_d_dist<4>(a, b, D);
+    if (D <= 8) return small_d_dist<8>(a, b, D);
+    return small_d_dist<16>(a, b, D);
+}
+
 template <int KPL>
 __global__ void __launch_bounds__(KNN_THREADS)
 k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict__ perm,
@@ -156,6 +183,16 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
             const int* idsJc = diag ? idsI : idsJ;
             // ---- distance tile ------------------------------------------------
             const int tI = (mI + 3) >> 2, tJ = (mJ + 3) >> 2;
+            if (D <= 16) {
+                // few dimensions: one thread per pair
+                for (int e = threadIdx.x; e < mI * mJ; e += blockDim.x) {
+                    const int r = e / mJ, c = e - r * mJ;
+                    if (diag && c < r) continue;
+                    const float dsum = small_d_dist_any(XI + (size_t)r * D, XJc + (size_t)c * D, D);
+                    tile[r * TS + c] = dsum;
+                    if (diag) tile[c * TS + r] = dsum;
+                }
+            } else
             for (int t = warp; t < tI * tJ; t += KNN_WARPS) {
                 const int ti = t / tJ, tj = t - ti * tJ;
                 if (diag && tj < ti) continue;
@@ -258,8 +295,35 @@ __device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __r
     }
 }
 
+// Per-warp set of the ids seen while one point is processed (open addressing
+// in shared memory).  A candidate already in the set -- a member of the row or
+// a candidate met before -- is not fetched again.  When a probe sequence finds
+// no free slot the id is reported as new: a repeated evaluation is wasted work,
+// never a wrong result (the list itself refuses repeated indices).
+constexpr int EXP_TABLE = 2048; // slots per warp
+constexpr int EXP_PROBES = 16;
+
+__device__ __forceinline__ bool seen_before(int* table, int c)
+{
+    unsigned h = ((unsigned)c * 2654435761u) >> (32 - 11);
+    static_assert(EXP_TABLE == 1 << 11, "hash shift must match the table size");
+#pragma unroll 1
+    for (int probe = 0; probe < EXP_PROBES; ++probe) {
+        const int old = atomicCAS(&table[h], -1, c);
+        if (old == -1) return false;
+        if (old == c) return true;
+        h = (h + 1) & (EXP_TABLE - 1);
+    }
+    return false;
+}
+
+__host__ __device__ inline size_t explore_smem_bytes(int D)
+{
+    return sizeof(float) * (size_t)KNN_WARPS * D + sizeof(int) * (size_t)KNN_WARPS * (EXP_QUEUE + EXP_TABLE);
+}
+
 template <int KPL>
-__global__ void __launch_bounds__(KNN_THREADS)
+__global__ void __launch_bounds__(KNN_THREADS, 2)
 k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restrict__ old_idx,
           int* __restrict__ knn_idx, float* __restrict__ knn_dist, int row_begin, int row_end,
           int list_row0, unsigned long long* __restrict__ evaluated)
@@ -268,6 +332,7 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* xp = smem + (size_t)warp * D;
     int* queue = (int*)(smem + (size_t)KNN_WARPS * D) + warp * EXP_QUEUE;
+    int* table = (int*)(smem + (size_t)KNN_WARPS * D) + KNN_WARPS * EXP_QUEUE + warp * EXP_TABLE;
 
     const int warp0 = blockIdx.x * KNN_WARPS + warp;
     const int n_warps = gridDim.x * KNN_WARPS;
@@ -275,6 +340,7 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
     for (int p = row_begin + warp0; p < row_end; p += n_warps) {
         __syncwarp();
         for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)p * D + k);
+        for (int t = lane; t < EXP_TABLE; t += 32) table[t] = -1;
         WarpList<KPL> L;
         L.load(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
         int nb[KPL];
@@ -283,6 +349,11 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
             int e = r * 32 + lane;
             nb[r] = e < K ? old_idx[(size_t)p * K + e] : -1;
         }
+        __syncwarp();
+        // members of the row are never candidates
+#pragma unroll
+        for (int r = 0; r < KPL; ++r)
+            if (L.i[r] >= 0) seen_before(table, L.i[r]);
         __syncwarp();
         bool changed = false;
         int qn = 0;
@@ -295,20 +366,11 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
                 const int* nrow = old_idx + (size_t)nbr * K;
                 for (int e0 = 0; e0 < K; e0 += 32) {
                     const int e = e0 + lane;
-                    int c = e < K ? nrow[e] : -1;
+                    const int c = e < K ? nrow[e] : -1;
                     bool ok = c >= 0 && c < N;
-                    // not in the row being updated
-                    bool dup = false;
-#pragma unroll
-                    for (int rr = 0; rr < KPL; ++rr)
-                        for (int bb = 0; bb < 32; ++bb) {
-                            if (rr * 32 + bb >= K) break;
-                            dup |= (__shfl_sync(RSFK_FULL, L.i[rr], bb) == c);
-                        }
-                    // not already waiting in the queue
-                    for (int q = 0; q < qn; ++q) dup |= (queue[q] == c);
-                    ok = ok && !dup;
+                    if (ok) ok = !seen_before(table, c);
                     const unsigned mask = __ballot_sync(RSFK_FULL, ok);
+                    if (mask == 0) continue;
                     if (ok) queue[qn + __popc(mask & ((1u << lane) - 1u))] = c;
                     qn += __popc(mask);
                     __syncwarp();
@@ -450,7 +512,7 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
 {
     if (!check_k(ctx, K)) return false;
     if (row_end <= row_begin) return true;
-    const size_t smem = sizeof(float) * (size_t)KNN_WARPS * D + sizeof(int) * (size_t)KNN_WARPS * EXP_QUEUE;
+    const size_t smem = explore_smem_bytes(D);
     if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "explore_sweep: D too large");
     long long rows = (long long)row_end - row_begin;
     long long blocks = (rows + KNN_WARPS - 1) / KNN_WARPS;
@@ -531,7 +593,7 @@ extern "C" int rsfk_explore_sweep_static(const float* d_points, int N, int D, in
         return static_fail(RSFK_ERR_ARG,
                            "N*K exceeds RSFK_STATIC_SWEEP_MAX_ENTRIES, the capacity of the built-in snapshot "
                            "buffer; use rsfk_dev_explore with a caller-provided snapshot instead");
-    const size_t smem = sizeof(float) * (size_t)KNN_WARPS * D + sizeof(int) * (size_t)KNN_WARPS * EXP_QUEUE;
+    const size_t smem = explore_smem_bytes(D);
     if (smem > 200 * 1024) return static_fail(RSFK_ERR_UNSUPPORTED, "D too large for the sweep kernel");
 
     int dev = 0;
