@@ -148,7 +148,8 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
              const int* __restrict__ leaf_start, const int* __restrict__ leaf_count,
              int* __restrict__ knn_idx, float* __restrict__ knn_dist, int B, int two_blocks)
 {
-    extern __shared__ float smem[];
+    extern __shared__ float4 smem4[];
+    float* smem = reinterpret_cast<float*>(smem4);
     // layout: tile[B][B+1] | XI[B][D] | XJ[B][D] (only when two_blocks) | idsI[B] | idsJ[B]
     const int TS = B + 1;
     float* tile = smem;
@@ -259,12 +260,12 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
 // ---------------------------------------------------------------------------
 constexpr int EXP_QUEUE = 64;
 
-template <int KPL>
-__device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __restrict__ pts, int D,
-                                              const float* xp, int* queue, int n, int K, int lane,
-                                              bool& changed)
+// Squared distances from the point (xp, shared memory) to up to 32 queued
+// candidates; lane l returns the distance of candidate *cand (also returned).
+// Scalar form: lane l owns dimensions l, l+32, ... of all 32 rows.
+__device__ __forceinline__ float explore_dist32_scalar(const float* __restrict__ pts, int D, const float* xp,
+                                                       const int* queue, int n, int lane, int& cand)
 {
-    // n in [1,32] candidates at queue[0..n)
     float acc[32];
     const float* row[32];
 #pragma unroll
@@ -284,13 +285,71 @@ __device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __r
         }
     }
     const float dsum = transposed_sum32(acc, lane);
-    const int item = item32_of_lane(lane);
+    cand = item32_of_lane(lane);
+    return dsum;
+}
+
+// 16-byte loads (D % 4 == 0, aligned rows): eight lanes share a row; lane
+// (g = lane/8, t = lane%8) owns terms 4t..4t+3 (+32, ...) of rows 4j+g, j=0..7,
+// i.e. virtual lanes 4t..4t+3 of the reference's sum, and ends up with the
+// distance of candidate 4t+g.
+__device__ __forceinline__ float explore_dist32_vec4(const float* __restrict__ pts, int D, const float* xp,
+                                                     const int* queue, int n, int lane, int& cand)
+{
+    const int g = lane >> 3, t = lane & 7;
+    const float4* xp4 = reinterpret_cast<const float4*>(xp);
+    const int D4 = D >> 2;
+    float acc[8][4];
+    const float4* row[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        row[j] = reinterpret_cast<const float4*>(pts + (size_t)queue[min(4 * j + g, n - 1)] * D);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[j][q] = 0.0f;
+    }
+    for (int k4 = t; k4 < D4; k4 += 8) {
+        const float4 x = xp4[k4];
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __ldg(row[j] + k4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float df;
+            df = __fsub_rn(v[j].x, x.x); acc[j][0] = __fmaf_rn(df, df, acc[j][0]);
+            df = __fsub_rn(v[j].y, x.y); acc[j][1] = __fmaf_rn(df, df, acc[j][1]);
+            df = __fsub_rn(v[j].z, x.z); acc[j][2] = __fmaf_rn(df, df, acc[j][2]);
+            df = __fsub_rn(v[j].w, x.w); acc[j][3] = __fmaf_rn(df, df, acc[j][3]);
+        }
+    }
+    float mine = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float s = __fadd_rn(__fadd_rn(acc[j][0], acc[j][1]), __fadd_rn(acc[j][2], acc[j][3]));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 1));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 2));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 4));
+        if (j == t) mine = s;
+    }
+    cand = 4 * t + g;
+    return mine;
+}
+
+template <int KPL, bool VEC4>
+__device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __restrict__ pts, int D,
+                                              const float* xp, int* queue, int n, int K,
+                                              int lane, bool& changed)
+{
+    // n in [1,32] candidates at queue[0..n)
+    int item;
+    const float dsum = VEC4 ? explore_dist32_vec4(pts, D, xp, queue, n, lane, item)
+                            : explore_dist32_scalar(pts, D, xp, queue, n, lane, item);
     const int ci = item < n ? queue[item] : -1;
-    // insert in queue order so that equal candidates behave like the serial scan
-    for (int c = 0; c < n; ++c) {
-        const int src = item32_of_lane(c); // lane holding item c (bit reversal is an involution)
-        const float d = __shfl_sync(RSFK_FULL, dsum, src);
-        const int id = __shfl_sync(RSFK_FULL, ci, src);
+    unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(dsum, ci));
+    while (mask) {
+        const int b = __ffs(mask) - 1;
+        mask &= mask - 1;
+        const float d = __shfl_sync(RSFK_FULL, dsum, b);
+        const int id = __shfl_sync(RSFK_FULL, ci, b);
         changed |= L.try_insert(d, id, K, lane);
     }
 }
@@ -300,47 +359,59 @@ __device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __r
 // a candidate met before -- is not fetched again.  When a probe sequence finds
 // no free slot the id is reported as new: a repeated evaluation is wasted work,
 // never a wrong result (the list itself refuses repeated indices).
-constexpr int EXP_TABLE = 2048; // slots per warp
 constexpr int EXP_PROBES = 16;
 
-__device__ __forceinline__ bool seen_before(int* table, int c)
+__device__ __forceinline__ bool seen_before(int* table, int table_log2, int c)
 {
-    unsigned h = ((unsigned)c * 2654435761u) >> (32 - 11);
-    static_assert(EXP_TABLE == 1 << 11, "hash shift must match the table size");
+    unsigned h = ((unsigned)c * 2654435761u) >> (32 - table_log2);
+    const unsigned wrap = (1u << table_log2) - 1u;
 #pragma unroll 1
     for (int probe = 0; probe < EXP_PROBES; ++probe) {
         const int old = atomicCAS(&table[h], -1, c);
         if (old == -1) return false;
         if (old == c) return true;
-        h = (h + 1) & (EXP_TABLE - 1);
+        h = (h + 1) & wrap;
     }
     return false;
 }
 
-__host__ __device__ inline size_t explore_smem_bytes(int D)
+// Launch shape of the sweep: up to K*K candidates per point want a table of at
+// least 2*K*K slots (capped at 4096); larger tables run four warps per CTA so
+// that three CTAs still fit one SM.
+struct ExploreShape {
+    int warps, table_log2;
+    size_t smem;
+};
+inline ExploreShape explore_shape(int D, int K)
 {
-    return sizeof(float) * (size_t)KNN_WARPS * D + sizeof(int) * (size_t)KNN_WARPS * (EXP_QUEUE + EXP_TABLE);
+    ExploreShape e;
+    e.table_log2 = (K <= 32) ? 11 : 12;
+    e.warps = (K <= 32) ? KNN_WARPS : 4;
+    e.smem = sizeof(float) * (size_t)e.warps * D + sizeof(int) * (size_t)e.warps * (EXP_QUEUE + (1 << e.table_log2));
+    return e;
 }
 
-template <int KPL>
+template <int KPL, bool VEC4>
 __global__ void __launch_bounds__(KNN_THREADS, 2)
 k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restrict__ old_idx,
           int* __restrict__ knn_idx, float* __restrict__ knn_dist, int row_begin, int row_end,
-          int list_row0, unsigned long long* __restrict__ evaluated)
+          int list_row0, unsigned long long* __restrict__ evaluated, int table_log2)
 {
-    extern __shared__ float smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    extern __shared__ float4 smem4[];
+    float* smem = reinterpret_cast<float*>(smem4);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, cta_warps = blockDim.x >> 5;
+    const int table_slots = 1 << table_log2;
     float* xp = smem + (size_t)warp * D;
-    int* queue = (int*)(smem + (size_t)KNN_WARPS * D) + warp * EXP_QUEUE;
-    int* table = (int*)(smem + (size_t)KNN_WARPS * D) + KNN_WARPS * EXP_QUEUE + warp * EXP_TABLE;
+    int* queue = (int*)(smem + (size_t)cta_warps * D) + warp * EXP_QUEUE;
+    int* table = (int*)(smem + (size_t)cta_warps * D) + cta_warps * EXP_QUEUE + warp * table_slots;
 
-    const int warp0 = blockIdx.x * KNN_WARPS + warp;
-    const int n_warps = gridDim.x * KNN_WARPS;
+    const int warp0 = blockIdx.x * cta_warps + warp;
+    const int n_warps = gridDim.x * cta_warps;
     unsigned long long n_eval = 0;
     for (int p = row_begin + warp0; p < row_end; p += n_warps) {
         __syncwarp();
         for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)p * D + k);
-        for (int t = lane; t < EXP_TABLE; t += 32) table[t] = -1;
+        for (int t = lane; t < table_slots; t += 32) table[t] = -1;
         WarpList<KPL> L;
         L.load(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
         int nb[KPL];
@@ -353,7 +424,7 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
         // members of the row are never candidates
 #pragma unroll
         for (int r = 0; r < KPL; ++r)
-            if (L.i[r] >= 0) seen_before(table, L.i[r]);
+            if (L.i[r] >= 0) seen_before(table, table_log2, L.i[r]);
         __syncwarp();
         bool changed = false;
         int qn = 0;
@@ -368,7 +439,7 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
                     const int e = e0 + lane;
                     const int c = e < K ? nrow[e] : -1;
                     bool ok = c >= 0 && c < N;
-                    if (ok) ok = !seen_before(table, c);
+                    if (ok) ok = !seen_before(table, table_log2, c);
                     const unsigned mask = __ballot_sync(RSFK_FULL, ok);
                     if (mask == 0) continue;
                     if (ok) queue[qn + __popc(mask & ((1u << lane) - 1u))] = c;
@@ -376,7 +447,7 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
                     __syncwarp();
                     if (qn >= 32) {
                         n_eval += 32;
-                        explore_flush<KPL>(L, pts, D, xp, queue, 32, K, lane, changed);
+                        explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
                         __syncwarp();
                         // move the tail to the front
                         const int rest = qn - 32;
@@ -391,7 +462,7 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
         }
         if (qn > 0) {
             n_eval += qn;
-            explore_flush<KPL>(L, pts, D, xp, queue, qn, K, lane, changed);
+            explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
         }
         if (changed)
             L.store(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
@@ -512,19 +583,23 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
 {
     if (!check_k(ctx, K)) return false;
     if (row_end <= row_begin) return true;
-    const size_t smem = explore_smem_bytes(D);
+    const ExploreShape shape = explore_shape(D, K);
+    const size_t smem = shape.smem;
     if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "explore_sweep: D too large");
     long long rows = (long long)row_end - row_begin;
-    long long blocks = (rows + KNN_WARPS - 1) / KNN_WARPS;
+    long long blocks = (rows + shape.warps - 1) / shape.warps;
     if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
     unsigned long long* counter = ctx.explore_counter();
     if (!counter) return false;
+    const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
     RSFK_DISPATCH_KPL(K, {
-        if (!ctx.check(cudaFuncSetAttribute(k_explore<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+        auto kern = vec4 ? k_explore<KPL, true> : k_explore<KPL, false>;
+        if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                        "explore smem attribute"))
             return false;
-        k_explore<KPL><<<(int)blocks, KNN_THREADS, smem, ctx.stream>>>(d_points, N, D, K, d_old_idx, d_idx,
-                                                                      d_dist, row_begin, row_end, list_row0, counter);
+        kern<<<(int)blocks, shape.warps * 32, smem, ctx.stream>>>(d_points, N, D, K, d_old_idx, d_idx, d_dist,
+                                                                 row_begin, row_end, list_row0, counter,
+                                                                 shape.table_log2);
     });
     count_launches(1);
     return ctx.check(cudaGetLastError(), "explore launch");
@@ -593,7 +668,8 @@ extern "C" int rsfk_explore_sweep_static(const float* d_points, int N, int D, in
         return static_fail(RSFK_ERR_ARG,
                            "N*K exceeds RSFK_STATIC_SWEEP_MAX_ENTRIES, the capacity of the built-in snapshot "
                            "buffer; use rsfk_dev_explore with a caller-provided snapshot instead");
-    const size_t smem = explore_smem_bytes(D);
+    const ExploreShape shape = explore_shape(D, K);
+    const size_t smem = shape.smem;
     if (smem > 200 * 1024) return static_fail(RSFK_ERR_UNSUPPORTED, "D too large for the sweep kernel");
 
     int dev = 0;
@@ -623,13 +699,15 @@ extern "C" int rsfk_explore_sweep_static(const float* d_points, int N, int D, in
     if (err == cudaSuccess) err = cudaMemsetAsync(counter, 0, sizeof(unsigned long long), st);
     if (err != cudaSuccess) return static_fail(RSFK_ERR_CUDA, cudaGetErrorString(err));
 
-    long long blocks = ((long long)N + KNN_WARPS - 1) / KNN_WARPS;
+    long long blocks = ((long long)N + shape.warps - 1) / shape.warps;
     if (blocks > (long long)g_static_sm_count[dev] * 8) blocks = (long long)g_static_sm_count[dev] * 8;
+    const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
     RSFK_DISPATCH_KPL(K, {
-        err = cudaFuncSetAttribute(k_explore<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        auto kern = vec4 ? k_explore<KPL, true> : k_explore<KPL, false>;
+        err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err == cudaSuccess) {
-            k_explore<KPL><<<(int)blocks, KNN_THREADS, smem, st>>>(d_points, N, D, K, snapshot, d_idx, d_dist,
-                                                                  0, N, 0, counter);
+            kern<<<(int)blocks, shape.warps * 32, smem, st>>>(d_points, N, D, K, snapshot, d_idx, d_dist, 0, N, 0,
+                                                             counter, shape.table_log2);
             err = cudaGetLastError();
         }
     });
