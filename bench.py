@@ -51,7 +51,7 @@ WORKLOADS = {
 # DRAM bytes (read+write) per launch of the dominant kernel from the committed
 # ncu capture, per unit processed; None until a capture exists.  Filled from
 # the summaries under profiles/.
-NCU_TRAFFIC_PER_POINT = {"explore": None, "bucket_knn": None, "tree_project": None}
+NCU_TRAFFIC_PER_POINT = {"explore": None, "bucket_knn": None, "tree_levels": None, "tree_subtrees": None}
 
 
 def make_points(w, n_override=None):
@@ -285,14 +285,22 @@ def run_ours(args, w):
     rows_own = re_ - rb
     phases = {}
     knn_ms = tot.get("bucket_knn_us", 0) / 1e3
+    sub_ms = tot.get("subtree_us", 0) / 1e3
     forest_ms = engine.total_ms("forest")
+    sub_pts, sub_nodes = tot.get("sub_active_points", 0), tot.get("sub_nodes", 0)
+    lvl_pts = tot.get("tree_active_points", 0) - sub_pts
+    lvl_nodes = tot.get("tree_nodes", 0) - sub_nodes
     phases["bucket_knn"] = dict(
         launches=trees_run, ms_per_launch=knn_ms / trees_run,
         bytes_per_launch=4.0 * N * D + 4.0 * N + 2 * 8.0 * N * K)
-    phases["tree_build"] = dict(
-        launches=trees_run, ms_per_launch=(forest_ms - knn_ms) / trees_run,
-        bytes_per_launch=(4.0 * (D + 2) * tot.get("tree_active_points", 0)
-                          + 4.0 * (D + 1) * tot.get("tree_nodes", 0)) / trees_run)
+    # one "launch" of the level phase = all level kernels (project + decide + scatter) of one tree
+    phases["tree_levels"] = dict(
+        launches=trees_run, ms_per_launch=(forest_ms - knn_ms - sub_ms) / trees_run,
+        bytes_per_launch=(4.0 * (D + 2) * lvl_pts + 4.0 * (D + 1) * lvl_nodes) / trees_run)
+    if sub_ms > 0:
+        phases["tree_subtrees"] = dict(
+            launches=trees_run, ms_per_launch=sub_ms / trees_run,
+            bytes_per_launch=(4.0 * (D + 2) * sub_pts + 4.0 * (D + 1) * sub_nodes) / trees_run)
     if engine.records["explore"]:
         C = tot.get("explore_candidates", 0) / n_explore
         phases["explore"] = dict(
@@ -307,9 +315,9 @@ def run_ours(args, w):
         p["gbs"] = p["bytes_per_launch"] / (p["ms_per_launch"] * 1e-3) / 1e9 if p["ms_per_launch"] > 0 else None
         p["total_ms"] = p["ms_per_launch"] * p["launches"]
     dom = max(phases, key=lambda n: phases[n]["total_ms"])
-    kernel_of = {"bucket_knn": "k_bucket_knn", "tree_build": "k_project_wide+k_decide+k_scatter (tree levels)",
-                 "explore": "k_explore", "merge_lists": "k_merge_lists"}
-    traffic_unit = NCU_TRAFFIC_PER_POINT.get({"tree_build": "tree_project"}.get(dom, dom))
+    kernel_of = {"bucket_knn": "k_bucket_knn", "tree_levels": "k_project_wide (+k_decide, k_scatter) per tree",
+                 "tree_subtrees": "k_subtree", "explore": "k_explore", "merge_lists": "k_merge_lists"}
+    traffic_unit = NCU_TRAFFIC_PER_POINT.get(dom)
     roofline = dict(bound="hbm", kernel=kernel_of[dom], achieved=phases[dom]["gbs"], peak=peak_gbs,
                     unit="GB/s", frac=(phases[dom]["gbs"] or 0) / peak_gbs, peak_kind=peak_kind,
                     traffic=(traffic_unit * (rows_own if dom == "explore" else N)) if traffic_unit else None,

@@ -114,6 +114,7 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
                    h->tree.n_leaves, h->tree.min_leaf, h->tree.max_leaf, tb1 - tb0);
     }
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
+    ok = ok && c.check_error_flag();
     if (ok)
         for (int i = 0; i < n_trees; ++i) {
             float ms = 0.0f;
@@ -320,9 +321,10 @@ int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
             !c.check(cudaStreamSynchronize(c.stream), "stats"))
             return c.status;
     }
-    const double v[5] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
-                         c.stats.bucket_knn_us, (double)evaluated};
-    for (int i = 0; i < n && i < 5; ++i) out[i] = v[i];
+    const double v[8] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+                         c.stats.bucket_knn_us, (double)evaluated, c.stats.subtree_us,
+                         (double)c.stats.sub_active_points, (double)c.stats.sub_nodes};
+    for (int i = 0; i < n && i < 8; ++i) out[i] = v[i];
     return RSFK_OK;
 }
 
@@ -330,6 +332,7 @@ int rsfk_ctx_synchronize(rsfk_ctx* ctx)
 {
     if (!ctx) return RSFK_ERR_ARG;
     ctx->c.check(cudaStreamSynchronize(ctx->c.stream), "synchronize");
+    ctx->c.check_error_flag();
     return ctx->c.status;
 }
 

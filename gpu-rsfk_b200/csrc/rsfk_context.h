@@ -56,6 +56,9 @@ struct Stats {
     long long tree_active_points = 0; // sum over levels of the points projected
     long long tree_nodes = 0;         // nodes split (hyperplanes formed)
     double bucket_knn_us = 0.0;       // device time of the bucket-KNN kernels
+    double subtree_us = 0.0;          // device time of the subtree kernels
+    long long sub_active_points = 0;  // part of tree_active_points projected inside subtree CTAs
+    long long sub_nodes = 0;          // part of tree_nodes split inside subtree CTAs
 };
 
 struct TreeResult {
@@ -79,11 +82,12 @@ struct Context {
     enum Slot {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
-        SNAPSHOT, EXPLORE_COUNT, N_SLOTS
+        SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, N_SLOTS
     };
     Stats stats;
     Buffer slots[N_SLOTS];
     LevelCounters* host_counters = nullptr; // pinned
+    cudaEvent_t sub_ev[2] = {nullptr, nullptr};
 
     bool fail(int code, const std::string& msg)
     {
@@ -117,10 +121,33 @@ struct Context {
         if (p && fresh) cudaMemsetAsync(p, 0, sizeof(unsigned long long), stream);
         return p;
     }
+    // device word a kernel sets when one of its bounded waits gave up (zeroed once)
+    int* error_flag()
+    {
+        const bool fresh = slots[ERROR_FLAG].ptr == nullptr;
+        int* p = (int*)scratch(ERROR_FLAG, sizeof(int));
+        if (p && fresh) cudaMemsetAsync(p, 0, sizeof(int), stream);
+        return p;
+    }
+    // reads the flag back (synchronizes the stream); false and a failure status when set
+    bool check_error_flag()
+    {
+        if (!slots[ERROR_FLAG].ptr) return true;
+        int v = 0;
+        if (!check(cudaMemcpyAsync(&v, slots[ERROR_FLAG].ptr, sizeof(int), cudaMemcpyDeviceToHost, stream), "flag D2H") ||
+            !check(cudaStreamSynchronize(stream), "flag sync"))
+            return false;
+        if (v != 0) {
+            cudaMemsetAsync(slots[ERROR_FLAG].ptr, 0, sizeof(int), stream);
+            return fail(RSFK_ERR_CUDA, "a device-side wait ran out of its limit (tensor-core bucket kernel)");
+        }
+        return true;
+    }
     void release()
     {
         for (auto& b : slots) { if (b.ptr) cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
         if (host_counters) { cudaFreeHost(host_counters); host_counters = nullptr; }
+        for (auto& e : sub_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
         if (owns_stream && stream) { cudaStreamDestroy(stream); stream = nullptr; }
     }
 };

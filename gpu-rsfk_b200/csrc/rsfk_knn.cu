@@ -12,6 +12,8 @@
 //
 // Squared distances keep the reference's summation order (term i in lane i%32,
 // fused multiply-add, xor butterfly), so their bits equal the reference's.
+#include <cstdlib>
+
 #include "rsfk_context.h"
 
 namespace rsfk {
@@ -142,7 +144,7 @@ __device__ __forceinline__ float small_d_dist_any(const float* a, const float* b
     return small_d_dist<16>(a, b, D);
 }
 
-template <int KPL>
+template <int KPL, bool SMALL_D>
 __global__ void __launch_bounds__(KNN_THREADS)
 k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict__ perm,
              const int* __restrict__ leaf_start, const int* __restrict__ leaf_count,
@@ -184,8 +186,8 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
             const int* idsJc = diag ? idsI : idsJ;
             // ---- distance tile ------------------------------------------------
             const int tI = (mI + 3) >> 2, tJ = (mJ + 3) >> 2;
-            if (D <= 16) {
-                // few dimensions: one thread per pair
+            if (SMALL_D) {
+                // few dimensions (D <= 16): one thread per pair
                 for (int e = threadIdx.x; e < mI * mJ; e += blockDim.x) {
                     const int r = e / mJ, c = e - r * mJ;
                     if (diag && c < r) continue;
@@ -508,6 +510,8 @@ k_merge_lists(MergeArgs args, int G, long long rows, int K, int* __restrict__ ou
     }
 }
 
+#include "rsfk_bucket_tc.cuh"
+
 // ---------------------------------------------------------------------------
 // host launchers
 // ---------------------------------------------------------------------------
@@ -551,6 +555,26 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     (void)N;
     if (!check_k(ctx, K)) return false;
     if (tree.n_leaves <= 0) return true;
+    // D >= 64 and leaves of at most 128 points: Gram tile on the tensor cores
+    static const bool tc_enabled = [] { const char* e = getenv("RSFK_TC"); return e && e[0] == '1'; }();
+    if (tc_enabled && D >= 64 && tree.max_leaf <= tc::TC_ROWS) {
+        const tc::Layout lay = tc::layout_for(D);
+        if (lay.total <= 200 * 1024) {
+            int* flag = ctx.error_flag();
+            if (!flag) return false;
+            const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
+            RSFK_DISPATCH_KPL(K, {
+                auto kern = vec4 ? tc::k_bucket_knn_tc<KPL, true> : tc::k_bucket_knn_tc<KPL, false>;
+                if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
+                               "bucket_knn_tc smem attribute"))
+                    return false;
+                kern<<<tree.n_leaves, KNN_THREADS, lay.total, ctx.stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
+                                                                           tree.leaf_count, d_idx, d_dist, flag);
+            });
+            count_launches(1);
+            return ctx.check(cudaGetLastError(), "bucket_knn_tc launch");
+        }
+    }
     // block size: the whole leaf when it fits, else the largest that fits twice
     const size_t budget = 200 * 1024;
     auto bytes = [&](int B, int two) {
@@ -568,11 +592,12 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     }
     const size_t smem = bytes(B, two);
     RSFK_DISPATCH_KPL(K, {
-        if (!ctx.check(cudaFuncSetAttribute(k_bucket_knn<KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+        auto kern = (D <= 16) ? k_bucket_knn<KPL, true> : k_bucket_knn<KPL, false>;
+        if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                        "bucket_knn smem attribute"))
             return false;
-        k_bucket_knn<KPL><<<tree.n_leaves, KNN_THREADS, smem, ctx.stream>>>(
-            d_points, D, K, tree.perm, tree.leaf_start, tree.leaf_count, d_idx, d_dist, B, two);
+        kern<<<tree.n_leaves, KNN_THREADS, smem, ctx.stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
+                                                              tree.leaf_count, d_idx, d_dist, B, two);
     });
     count_launches(1);
     return ctx.check(cudaGetLastError(), "bucket_knn launch");

@@ -870,10 +870,13 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
             !ctx.check(cudaFuncSetAttribute(k_subtree, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sub_smem),
                        "subtree smem attribute"))
             return false;
+        if (!ctx.sub_ev[0]) { cudaEventCreate(&ctx.sub_ev[0]); cudaEventCreate(&ctx.sub_ev[1]); }
+        cudaEventRecord(ctx.sub_ev[0], st);
         k_subtree<<<n_small, TREE_THREADS, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
                                                            leaf_count, leaf_cap, cnt, table, n_table, seed,
                                                            min_children, max_children, max_depth,
                                                            (D % 4 == 0 && ((uintptr_t)d_points & 15) == 0) ? 1 : 0);
+        cudaEventRecord(ctx.sub_ev[1], st);
         count_launches(1);
     }
     if (!ctx.check(cudaMemcpyAsync(ctx.host_counters, cnt, sizeof(LevelCounters),
@@ -886,6 +889,12 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     ctx.stats.trees++;
     ctx.stats.tree_active_points += (long long)ctx.host_counters->sub_active;
     ctx.stats.tree_nodes += (long long)ctx.host_counters->sub_nodes;
+    ctx.stats.sub_active_points += (long long)ctx.host_counters->sub_active;
+    ctx.stats.sub_nodes += (long long)ctx.host_counters->sub_nodes;
+    if (n_small > 0) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, ctx.sub_ev[0], ctx.sub_ev[1]) == cudaSuccess) ctx.stats.subtree_us += ms * 1e3;
+    }
     if (ctx.host_counters->max_level > levels) levels = ctx.host_counters->max_level;
     out.perm = perm_final;
     out.leaf_start = leaf_start;

@@ -145,9 +145,10 @@ class DeviceForest(object):
 
     def stats(self):
         """Work counters of this context (synchronizes the stream)."""
-        out = (ctypes.c_double * 5)()
-        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 5), "stats")
-        names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates")
+        out = (ctypes.c_double * 8)()
+        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 8), "stats")
+        names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates",
+                 "subtree_us", "sub_active_points", "sub_nodes")
         return dict(zip(names, [float(v) for v in out]))
 
     def kernel_launches(self):

@@ -87,7 +87,8 @@ RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
  * achieved bytes/s: out[0] trees built, out[1] points projected summed over
  * tree levels, out[2] nodes split, out[3] device microseconds spent in the
  * bucket-KNN kernels, out[4] candidates whose distance the exploration sweeps
- * evaluated.  The reference's counterpart is its ForestLog of per-phase
+ * evaluated, out[5] device microseconds spent in the subtree kernels, out[6] and
+ * out[7] the part of out[1] and out[2] done inside subtree kernels.  The reference's counterpart is its ForestLog of per-phase
  * wall-clock times (src/include/rsfk.h:274-392). */
 RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
