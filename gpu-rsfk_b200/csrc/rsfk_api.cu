@@ -89,19 +89,50 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
     std::vector<cudaEvent_t> ev(2 * (size_t)n_trees);
     for (auto& e : ev) cudaEventCreate(&e);
     if (log_forest) memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
+    const bool timeline = getenv("RSFK_TIMELINE") != nullptr;
+    cudaEvent_t ev_start = nullptr;
+    std::vector<double> tl;
+    if (timeline) {
+        cudaEventCreate(&ev_start);
+        cudaStreamSynchronize(c.stream);
+        cudaEventRecord(ev_start, c.stream);
+    }
     const double t0 = now_s();
     bool ok = true;
+    // bucket KNN of tree i runs on a second stream while tree i+1 is built
+    // (off unless RSFK_OVERLAP=1: with the present kernels' register footprints the two
+    // streams do not co-reside on an SM, so nothing is gained)
+    static const bool overlap_allowed = [] { const char* e = getenv("RSFK_OVERLAP"); return e && e[0] == '1'; }();
+    const bool overlap = overlap_allowed && n_trees > 1 && c.ensure_aux() && c.error_flag() != nullptr;
+    if (overlap) {
+        cudaEventRecord(c.ev_join, c.stream); // the lists are ready on the main stream
+        cudaStreamWaitEvent(c.aux, c.ev_join, 0);
+    }
     for (int i = 0; i < n_trees && ok; ++i) {
         const int t = first_tree + i * tree_stride;
+        const int buf = overlap ? (i & 1) : 0;
+        c.result_buf = buf;
+        if (overlap && i >= 2) cudaStreamWaitEvent(c.stream, c.ev_knn[buf], 0); // buffer still being read?
         const double tb0 = now_s();
         ok = rsfk::tree_build(c, d_points, N, D, min_children, max_children, max_depth, seed + t,
                               nullptr, 0, h->tree);
         h->has_tree = ok;
         const double tb1 = now_s();
+        c.stats.tree_build_us += (tb1 - tb0) * 1e6;
+        if (timeline) { tl.push_back((tb0 - t0) * 1e3); tl.push_back((tb1 - t0) * 1e3); }
         if (!ok) break;
-        cudaEventRecord(ev[2 * i], c.stream);
-        ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist);
-        cudaEventRecord(ev[2 * i + 1], c.stream);
+        if (overlap) {
+            cudaEventRecord(c.ev_tree[buf], c.stream);
+            cudaStreamWaitEvent(c.aux, c.ev_tree[buf], 0);
+            cudaEventRecord(ev[2 * i], c.aux);
+            ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist, true);
+            cudaEventRecord(ev[2 * i + 1], c.aux);
+            cudaEventRecord(c.ev_knn[buf], c.aux);
+        } else {
+            cudaEventRecord(ev[2 * i], c.stream);
+            ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist);
+            cudaEventRecord(ev[2 * i + 1], c.stream);
+        }
         if (log_forest) {
             log_forest[0 * n_trees + i] = (float)h->tree.levels;
             log_forest[1 * n_trees + i] = (float)h->tree.max_leaf;
@@ -113,8 +144,23 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
             printf("tree %d: depth %d, leaves %d, leaf size %d..%d, build %.6f s\n", t, h->tree.levels,
                    h->tree.n_leaves, h->tree.min_leaf, h->tree.max_leaf, tb1 - tb0);
     }
+    c.result_buf = 0;
+    if (overlap) {
+        cudaEventRecord(c.ev_join, c.aux); // later work on the main stream sees the finished lists
+        cudaStreamWaitEvent(c.stream, c.ev_join, 0);
+    }
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
     ok = ok && c.check_error_flag();
+    if (ok && timeline) {
+        for (int i = 0; i < n_trees && i < 6; ++i) {
+            float a = 0, b = 0;
+            cudaEventElapsedTime(&a, ev_start, ev[2 * i]);
+            cudaEventElapsedTime(&b, ev_start, ev[2 * i + 1]);
+            fprintf(stderr, "timeline tree %d: build host %.3f..%.3f ms, knn device %.3f..%.3f ms\n", i, tl[2 * i],
+                    tl[2 * i + 1], a, b);
+        }
+    }
+    if (ev_start) cudaEventDestroy(ev_start);
     if (ok)
         for (int i = 0; i < n_trees; ++i) {
             float ms = 0.0f;
@@ -321,10 +367,10 @@ int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
             !c.check(cudaStreamSynchronize(c.stream), "stats"))
             return c.status;
     }
-    const double v[8] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+    const double v[9] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
                          c.stats.bucket_knn_us, (double)evaluated, c.stats.subtree_us,
-                         (double)c.stats.sub_active_points, (double)c.stats.sub_nodes};
-    for (int i = 0; i < n && i < 8; ++i) out[i] = v[i];
+                         (double)c.stats.sub_active_points, (double)c.stats.sub_nodes, c.stats.tree_build_us};
+    for (int i = 0; i < n && i < 9; ++i) out[i] = v[i];
     return RSFK_OK;
 }
 

@@ -57,6 +57,7 @@ struct Stats {
     long long tree_nodes = 0;         // nodes split (hyperplanes formed)
     double bucket_knn_us = 0.0;       // device time of the bucket-KNN kernels
     double subtree_us = 0.0;          // device time of the subtree kernels
+    double tree_build_us = 0.0;       // host-observed time of the tree builds (each ends with a stream sync)
     long long sub_active_points = 0;  // part of tree_active_points projected inside subtree CTAs
     long long sub_nodes = 0;          // part of tree_nodes split inside subtree CTAs
 };
@@ -82,12 +83,33 @@ struct Context {
     enum Slot {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
+        PERM_FINAL_B, LEAF_START_B, LEAF_COUNT_B,
         SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, N_SLOTS
     };
     Stats stats;
     Buffer slots[N_SLOTS];
     LevelCounters* host_counters = nullptr; // pinned
     cudaEvent_t sub_ev[2] = {nullptr, nullptr};
+    // A forest overlaps the bucket KNN of tree t (second stream) with the build
+    // of tree t+1 (main stream); trees alternate between two result buffers.
+    int result_buf = 0;
+    cudaStream_t aux = nullptr;
+    cudaEvent_t ev_tree[2] = {nullptr, nullptr}, ev_knn[2] = {nullptr, nullptr}, ev_join = nullptr;
+    bool ensure_aux()
+    {
+        if (aux) return true;
+        // lowest priority: CTAs of the (latency-bound) tree kernels on the main
+        // stream are placed before pending bucket-KNN CTAs
+        int least = 0, greatest = 0;
+        cudaDeviceGetStreamPriorityRange(&least, &greatest);
+        if (!check(cudaStreamCreateWithPriority(&aux, cudaStreamNonBlocking, least), "aux stream")) return false;
+        for (int i = 0; i < 2; ++i) {
+            cudaEventCreateWithFlags(&ev_tree[i], cudaEventDisableTiming);
+            cudaEventCreateWithFlags(&ev_knn[i], cudaEventDisableTiming);
+        }
+        cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming);
+        return true;
+    }
 
     bool fail(int code, const std::string& msg)
     {
@@ -148,6 +170,13 @@ struct Context {
         for (auto& b : slots) { if (b.ptr) cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
         if (host_counters) { cudaFreeHost(host_counters); host_counters = nullptr; }
         for (auto& e : sub_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
+        for (int i = 0; i < 2; ++i) {
+            if (ev_tree[i]) cudaEventDestroy(ev_tree[i]);
+            if (ev_knn[i]) cudaEventDestroy(ev_knn[i]);
+            ev_tree[i] = ev_knn[i] = nullptr;
+        }
+        if (ev_join) { cudaEventDestroy(ev_join); ev_join = nullptr; }
+        if (aux) { cudaStreamDestroy(aux); aux = nullptr; }
         if (owns_stream && stream) { cudaStreamDestroy(stream); stream = nullptr; }
     }
 };
@@ -161,7 +190,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
 int list_capacity();                      // largest supported K
 bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K);
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
-                int* d_idx, float* d_dist);
+                int* d_idx, float* d_dist, bool on_aux_stream = false);
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
                    int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0);
 bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,

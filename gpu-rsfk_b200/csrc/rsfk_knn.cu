@@ -550,9 +550,10 @@ bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K)
 }
 
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
-                int* d_idx, float* d_dist)
+                int* d_idx, float* d_dist, bool on_aux_stream)
 {
     (void)N;
+    cudaStream_t launch_stream = on_aux_stream ? ctx.aux : ctx.stream;
     if (!check_k(ctx, K)) return false;
     if (tree.n_leaves <= 0) return true;
     // D >= 64 and leaves of at most 128 points: Gram tile on the tensor cores
@@ -568,7 +569,7 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
                 if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
                                "bucket_knn_tc smem attribute"))
                     return false;
-                kern<<<tree.n_leaves, KNN_THREADS, lay.total, ctx.stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
+                kern<<<tree.n_leaves, KNN_THREADS, lay.total, launch_stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
                                                                            tree.leaf_count, d_idx, d_dist, flag);
             });
             count_launches(1);
@@ -596,7 +597,7 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
         if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                        "bucket_knn smem attribute"))
             return false;
-        kern<<<tree.n_leaves, KNN_THREADS, smem, ctx.stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
+        kern<<<tree.n_leaves, KNN_THREADS, smem, launch_stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
                                                               tree.leaf_count, d_idx, d_dist, B, two);
     });
     count_launches(1);

@@ -784,7 +784,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     int* perm[2];
     perm[0] = (int*)ctx.scratch(Context::PERM_A, sizeof(int) * (size_t)N);
     perm[1] = (int*)ctx.scratch(Context::PERM_B, sizeof(int) * (size_t)N);
-    int* perm_final = (int*)ctx.scratch(Context::PERM_FINAL, sizeof(int) * (size_t)N);
+    int* perm_final = (int*)ctx.scratch(ctx.result_buf ? Context::PERM_FINAL_B : Context::PERM_FINAL, sizeof(int) * (size_t)N);
     unsigned* side_bits = (unsigned*)ctx.scratch(Context::SIDE_BITS, sizeof(unsigned) * (size_t)chunk_cap * CHUNK_WORDS);
     int* chunk_node[2];
     chunk_node[0] = (int*)ctx.scratch(Context::CHUNK_NODE_A, sizeof(int) * (size_t)chunk_cap);
@@ -804,8 +804,8 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     if (const char* e = getenv("RSFK_SUBTREE_LIMIT")) small_limit = atoi(e) < small_limit ? atoi(e) : small_limit;
     const int small_cap = node_cap;
     Node* small_nodes = (Node*)ctx.scratch(Context::SMALL_NODES, sizeof(Node) * (size_t)small_cap);
-    int* leaf_start = (int*)ctx.scratch(Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
-    int* leaf_count = (int*)ctx.scratch(Context::LEAF_COUNT, sizeof(int) * (size_t)leaf_cap);
+    int* leaf_start = (int*)ctx.scratch(ctx.result_buf ? Context::LEAF_START_B : Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
+    int* leaf_count = (int*)ctx.scratch(ctx.result_buf ? Context::LEAF_COUNT_B : Context::LEAF_COUNT, sizeof(int) * (size_t)leaf_cap);
     LevelCounters* cnt = (LevelCounters*)ctx.scratch(Context::COUNTERS, sizeof(LevelCounters));
     if (ctx.status != RSFK_OK) return false;
     if (!ctx.host_counters &&
@@ -872,7 +872,12 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
             return false;
         if (!ctx.sub_ev[0]) { cudaEventCreate(&ctx.sub_ev[0]); cudaEventCreate(&ctx.sub_ev[1]); }
         cudaEventRecord(ctx.sub_ev[0], st);
-        k_subtree<<<n_small, TREE_THREADS, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
+        static const int sub_threads = [] {
+            const char* e = getenv("RSFK_SUBTREE_THREADS");
+            int v = e ? atoi(e) : 128;
+            return (v == 64 || v == 128 || v == 256) ? v : 128;
+        }();
+        k_subtree<<<n_small, sub_threads, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
                                                            leaf_count, leaf_cap, cnt, table, n_table, seed,
                                                            min_children, max_children, max_depth,
                                                            (D % 4 == 0 && ((uintptr_t)d_points & 15) == 0) ? 1 : 0);

@@ -145,10 +145,10 @@ class DeviceForest(object):
 
     def stats(self):
         """Work counters of this context (synchronizes the stream)."""
-        out = (ctypes.c_double * 8)()
-        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 8), "stats")
+        out = (ctypes.c_double * 9)()
+        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 9), "stats")
         names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates",
-                 "subtree_us", "sub_active_points", "sub_nodes")
+                 "subtree_us", "sub_active_points", "sub_nodes", "tree_build_us")
         return dict(zip(names, [float(v) for v in out]))
 
     def kernel_launches(self):

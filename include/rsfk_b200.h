@@ -88,7 +88,8 @@ RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
  * tree levels, out[2] nodes split, out[3] device microseconds spent in the
  * bucket-KNN kernels, out[4] candidates whose distance the exploration sweeps
  * evaluated, out[5] device microseconds spent in the subtree kernels, out[6] and
- * out[7] the part of out[1] and out[2] done inside subtree kernels.  The reference's counterpart is its ForestLog of per-phase
+ * out[7] the part of out[1] and out[2] done inside subtree kernels, out[8] microseconds
+ * the tree builds took as seen from the host.  The reference's counterpart is its ForestLog of per-phase
  * wall-clock times (src/include/rsfk.h:274-392). */
 RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
