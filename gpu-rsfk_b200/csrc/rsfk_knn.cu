@@ -556,11 +556,19 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     cudaStream_t launch_stream = on_aux_stream ? ctx.aux : ctx.stream;
     if (!check_k(ctx, K)) return false;
     if (tree.n_leaves <= 0) return true;
-    // D >= 64 and leaves of at most 128 points: Gram tile on the tensor cores
-    static const bool tc_enabled = [] { const char* e = getenv("RSFK_TC"); return e && e[0] == '1'; }();
-    if (tc_enabled && D >= 64 && tree.max_leaf <= tc::TC_ROWS) {
-        const tc::Layout lay = tc::layout_for(D);
-        if (lay.total <= 200 * 1024) {
+    const size_t budget = 200 * 1024;
+    auto bytes = [&](int B, int two) {
+        return sizeof(float) * ((size_t)B * (B + 1) + (size_t)(two ? 2 : 1) * B * D) + sizeof(int) * (size_t)(two ? 2 : 1) * B;
+    };
+    // D >= 64: Gram tiles on the tensor cores (RSFK_TC=1 always, =0 never; by
+    // default where a leaf no longer fits the SIMT kernel's single shared-memory
+    // block, which is where that kernel re-stages rows many times)
+    static const int tc_mode = [] { const char* e = getenv("RSFK_TC"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
+    const bool simt_single_block = bytes((tree.max_leaf + 3) & ~3, 0) <= budget;
+    const bool want_tc = tc_mode == 1 || (tc_mode == -1 && !simt_single_block);
+    if (want_tc && D >= 64 && tree.max_leaf <= tc::TC_ROWS * tc::TC_MAX_BLOCKS) {
+        const tc::Layout lay = tc::layout_for(D, tree.max_leaf);
+        if (lay.total <= 220 * 1024) {
             int* flag = ctx.error_flag();
             if (!flag) return false;
             const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
@@ -569,18 +577,14 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
                 if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
                                "bucket_knn_tc smem attribute"))
                     return false;
-                kern<<<tree.n_leaves, KNN_THREADS, lay.total, launch_stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
-                                                                           tree.leaf_count, d_idx, d_dist, flag);
+                kern<<<tree.n_leaves, KNN_THREADS, lay.total, launch_stream>>>(
+                    d_points, D, K, tree.perm, tree.leaf_start, tree.leaf_count, d_idx, d_dist, tree.max_leaf, flag);
             });
             count_launches(1);
             return ctx.check(cudaGetLastError(), "bucket_knn_tc launch");
         }
     }
     // block size: the whole leaf when it fits, else the largest that fits twice
-    const size_t budget = 200 * 1024;
-    auto bytes = [&](int B, int two) {
-        return sizeof(float) * ((size_t)B * (B + 1) + (size_t)(two ? 2 : 1) * B * D) + sizeof(int) * (size_t)(two ? 2 : 1) * B;
-    };
     int B = (tree.max_leaf + 3) & ~3;
     if (B < 4) B = 4;
     int two = 0;

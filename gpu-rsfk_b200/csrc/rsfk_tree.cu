@@ -874,8 +874,8 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
         cudaEventRecord(ctx.sub_ev[0], st);
         static const int sub_threads = [] {
             const char* e = getenv("RSFK_SUBTREE_THREADS");
-            int v = e ? atoi(e) : 128;
-            return (v == 64 || v == 128 || v == 256) ? v : 128;
+            int v = e ? atoi(e) : TREE_THREADS;
+            return (v == 64 || v == 128 || v == 256) ? v : TREE_THREADS;
         }();
         k_subtree<<<n_small, sub_threads, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
                                                            leaf_count, leaf_cap, cnt, table, n_table, seed,
