@@ -259,11 +259,12 @@ k_bucket_knn_tc(const float* __restrict__ pts, int D, int K, const int* __restri
         const int i0 = bi * TC_ROWS;
         __syncthreads(); // the previous block's row phase has finished with sIdsA / sPass
         for (int r = threadIdx.x; r < TC_ROWS; r += blockDim.x) sIdsA[r] = i0 + r < m ? ids[i0 + r] : -1;
+        for (int w = threadIdx.x; w < TC_ROWS * PW; w += blockDim.x) sPass[w] = 0u;
         __syncthreads();
-        // K-th distance of this thread's row (epilogue rows: lanes of warp%4)
+        // this thread's epilogue row: tensor-memory lane 32*(warp%4)+lane
         const int erow = 32 * (warp & 3) + lane;
         const int eid = sIdsA[erow];
-        const float thr = eid >= 0 ? knn_dist[(size_t)eid * K + (K - 1)] : -1.0f;
+        const int mI = min(TC_ROWS, m - i0);
 
         for (int bj = 0; bj < n_blocks && !failed; ++bj) {
             const int j0 = bj * TC_ROWS;
@@ -311,6 +312,8 @@ k_bucket_knn_tc(const float* __restrict__ pts, int D, int K, const int* __restri
             // ---- epilogue: pass bits of rows I against columns J ------------
             // warp w reads tensor-memory lanes 32*(w%4).. (rows) and columns 64*(w/4)..
             {
+                // current K-th distance of the row (rows flushed after earlier tiles have tightened it)
+                const float thr = eid >= 0 ? __ldcg(knn_dist + (size_t)eid * K + (K - 1)) : -1.0f;
                 const float* nJ = diag ? sNormA : sNormB;
                 const float n_row = sNormA[erow];
 #pragma unroll
@@ -334,45 +337,51 @@ k_bucket_knn_tc(const float* __restrict__ pts, int D, int K, const int* __restri
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+            // ---- rows of block I: exact distances of passing candidates ----
+            // A row is flushed as soon as 32 candidates wait (its K-th distance then
+            // tightens the filter of the following tiles) and after the last tile.
+            const bool last_tile = (bj == n_blocks - 1);
+            const int n_words = min((m + 31) >> 5, (bj + 1) * (TC_ROWS / 32));
+            for (int r = warp; r < mI; r += KNN_WARPS) {
+                int pending = 0;
+                for (int w = lane; w < n_words; w += 32) pending += __popc(sPass[r * PW + w]);
+#pragma unroll
+                for (int sft = 16; sft >= 1; sft >>= 1) pending += __shfl_xor_sync(RSFK_FULL, pending, sft);
+                if (pending == 0 || (pending < 32 && !last_tile)) continue;
+                const int self = sIdsA[r];
+                __syncwarp();
+                for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)self * D + k);
+                WarpList<KPL> L;
+                L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                __syncwarp();
+                bool changed = false;
+                int qn = 0;
+                for (int w = 0; w < n_words; ++w) {
+                    const unsigned bits = sPass[r * PW + w];
+                    if (bits == 0) continue;
+                    __syncwarp();
+                    if (lane == 0) sPass[r * PW + w] = 0u;
+                    const bool ok = (bits >> lane) & 1u;
+                    if (ok) queue[qn + __popc(bits & ((1u << lane) - 1u))] = ids[32 * w + lane];
+                    qn += __popc(bits);
+                    __syncwarp();
+                    if (qn >= 32) {
+                        explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
+                        __syncwarp();
+                        const int rest = qn - 32;
+                        const int tmp = lane < rest ? queue[32 + lane] : -1;
+                        __syncwarp();
+                        if (lane < rest) queue[lane] = tmp;
+                        qn = rest;
+                        __syncwarp();
+                    }
+                }
+                if (qn > 0) explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
+                if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+            }
         }
         if (failed) break;
-
-        // ---- rows of block I: exact distances of passing candidates -------
-        const int mI = min(TC_ROWS, m - i0);
-        const int n_words = (m + 31) >> 5;
-        for (int r = warp; r < mI; r += KNN_WARPS) {
-            const int self = sIdsA[r];
-            unsigned any = 0;
-            for (int w = lane; w < n_words; w += 32) any |= sPass[r * PW + w];
-            if (__ballot_sync(RSFK_FULL, any != 0) == 0) continue;
-            __syncwarp();
-            for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)self * D + k);
-            WarpList<KPL> L;
-            L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
-            __syncwarp();
-            bool changed = false;
-            int qn = 0;
-            for (int w = 0; w < n_words; ++w) {
-                const unsigned bits = sPass[r * PW + w];
-                if (bits == 0) continue;
-                const bool ok = (bits >> lane) & 1u;
-                if (ok) queue[qn + __popc(bits & ((1u << lane) - 1u))] = ids[32 * w + lane];
-                qn += __popc(bits);
-                __syncwarp();
-                if (qn >= 32) {
-                    explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
-                    __syncwarp();
-                    const int rest = qn - 32;
-                    const int tmp = lane < rest ? queue[32 + lane] : -1;
-                    __syncwarp();
-                    if (lane < rest) queue[lane] = tmp;
-                    qn = rest;
-                    __syncwarp();
-                }
-            }
-            if (qn > 0) explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
-            if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
-        }
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
