@@ -26,8 +26,9 @@
 
 namespace rsfk {
 
-constexpr int CHUNK = 1024;          // positions per work chunk
+constexpr int CHUNK = 512;           // positions per work chunk
 constexpr int CHUNK_WORDS = CHUNK / 32;
+static_assert(CHUNK % 32 == 0 && CHUNK_WORDS <= 32, "one warp scans the words of a chunk");
 constexpr int TREE_THREADS = 256;
 
 struct NodeSplit {
@@ -468,8 +469,10 @@ k_scatter(const int* __restrict__ perm_in, int* __restrict__ perm_out, int* __re
             int t = __shfl_up_sync(RSFK_FULL, incl, s);
             if (w >= s) incl += t;
         }
-        sMask[w] = m;
-        sWordLeft[w] = incl - lefts;
+        if (w < CHUNK_WORDS) { // the scan runs on all 32 lanes; a chunk has CHUNK_WORDS words
+            sMask[w] = m;
+            sWordLeft[w] = incl - lefts;
+        }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
