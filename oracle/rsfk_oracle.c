@@ -13,9 +13,11 @@
  * compiler emits (nvcc contracts a*b+c by default) is written here as an
  * explicit fmaf(), and nothing else may be fused.
  *
- * Parity status: the distance function, the bucket update rule and the
- * exploration sweep are pinned against outputs of the reference binary itself
- * (fixtures under tests/golden/, produced by tests/golden/make_ref_golden.py).
+ * Parity status: pinned.  The distance function, the bucket update rule, the
+ * exploration sweep, and the tree rules (split side with the root's serial and
+ * the other nodes' lane-strided offset, minimum side size, leaf sizes) are all
+ * checked against outputs of the reference binary itself (fixtures under
+ * tests/golden/, produced by tests/golden/make_ref_golden.py).
  */
 #include <float.h>
 #include <math.h>
@@ -675,4 +677,60 @@ ORC_API double orc_recall(const int* truth, const int* approx, int rows, int K)
         }
     }
     return (double)hit / ((double)rows * K);
+}
+
+/* ------------------------------------------------------------------------- */
+/* Recovering split pairs of a reference tree from its leaves (tests only)    */
+/* ------------------------------------------------------------------------- */
+
+/* The reference does not report which pairs it sampled.  Given the points of a
+ * node (ids[0..n)) and the leaf each point finally landed in (leaf[0..n), small
+ * non-negative labels < n_leaves <= 64), this enumerates the distinct ways a
+ * pair (p1, p2) of the node's own points can separate the node's LEAVES with the
+ * restated split rule (n.x < c goes right; offset summed serially when is_root,
+ * lane-strided otherwise): every leaf entirely on one side, both sides non-empty.
+ * Each separation is returned once as the 64-bit mask of the leaves that go
+ * right, with the first pair found for it.  Returns the number of separations
+ * (at most cap). */
+ORC_API int orc_find_leaf_separations(const float* points, int D, const int* ids, const int* leaf, int n,
+                                      int n_leaves, int is_root, int min_side, uint64_t* masks_out,
+                                      int* pairs_out, int cap)
+{
+    int found = 0;
+    #pragma omp parallel
+    {
+        float* nrm = (float*)malloc(sizeof(float) * (size_t)D);
+        #pragma omp for schedule(dynamic, 4)
+        for (int a = 0; a < n; ++a) {
+            for (int b = 0; b < n; ++b) {
+                if (a == b || leaf[a] == leaf[b]) continue;
+                const float* x1 = points + (size_t)ids[a] * D;
+                const float* x2 = points + (size_t)ids[b] * D;
+                float c = orc_hyperplane(x1, x2, D, is_root, nrm);
+                uint64_t right = 0, left = 0;
+                int n_right = 0, ok = 1;
+                for (int q = 0; q < n && ok; ++q) {
+                    int r = orc_project(nrm, points + (size_t)ids[q] * D, D) < c;
+                    if (r) { right |= 1ull << leaf[q]; n_right++; } else left |= 1ull << leaf[q];
+                    if (right & left) ok = 0;
+                }
+                if (!ok || right == 0 || left == 0) continue;
+                if (n_right < min_side || n - n_right < min_side) continue;
+                #pragma omp critical
+                {
+                    int known = 0;
+                    for (int k = 0; k < found; ++k) if (masks_out[k] == right) { known = 1; break; }
+                    if (!known && found < cap) {
+                        masks_out[found] = right;
+                        pairs_out[2 * found] = ids[a];
+                        pairs_out[2 * found + 1] = ids[b];
+                        found++;
+                    }
+                }
+            }
+        }
+        free(nrm);
+    }
+    (void)n_leaves;
+    return found;
 }

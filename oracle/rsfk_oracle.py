@@ -230,3 +230,21 @@ def init_lists(N, K, self_in_row=True):
 def leaf_sets(perm, leaf_start, leaf_count):
     """Partition as a set of frozensets, independent of leaf and slot order."""
     return {frozenset(perm[s:s + c].tolist()) for s, c in zip(leaf_start, leaf_count)}
+
+
+def find_leaf_separations(points, ids, leaf, is_root, min_side, cap=64):
+    """Distinct leaf separations a pair of the node's points can produce
+    (see orc_find_leaf_separations); returns [(right_mask, (p1, p2)), ...]."""
+    points = _pts(points)
+    L = lib()
+    L.orc_find_leaf_separations.restype = ctypes.c_int
+    L.orc_find_leaf_separations.argtypes = [_f32, ctypes.c_int, _i32, _i32, ctypes.c_int, ctypes.c_int,
+                                            ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                            ctypes.c_int]
+    ids = np.ascontiguousarray(ids, np.int32)
+    leaf = np.ascontiguousarray(leaf, np.int32)
+    masks = np.zeros(cap, np.uint64)
+    pairs = np.zeros(2 * cap, np.int32)
+    n = L.orc_find_leaf_separations(points, points.shape[1], ids, leaf, len(ids), int(leaf.max()) + 1,
+                                    int(is_root), int(min_side), masks.ctypes.data, pairs.ctypes.data, cap)
+    return [(int(masks[k]), (int(pairs[2 * k]), int(pairs[2 * k + 1]))) for k in range(n)]

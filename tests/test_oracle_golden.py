@@ -127,3 +127,41 @@ def test_reference_root_split_is_reproduced_by_some_pair(oracle, path):
         if found:
             break
     assert found is not None
+
+
+def _reconstruct(oracle, X, ids, label, MIN, MAX, is_root, depth=0):
+    """True when the leaves below this node (label per point) can be produced by
+    the restated rules from SOME split pair at every internal node."""
+    n = len(ids)
+    labels = np.unique(label)
+    if len(labels) == 1:
+        return (not is_root) and n <= MAX           # a leaf: at most MAX-2 points, or MAX-1..MAX after a merge
+    if not is_root and n <= MAX - 2:
+        return False                                # such a node would have been a leaf
+    local = np.searchsorted(labels, label).astype(np.int32)
+    if len(labels) > 64:
+        return False
+    for mask, _pair in oracle.find_leaf_separations(X, ids, local, is_root, MIN):
+        right = np.array([(mask >> int(l)) & 1 for l in local], bool)
+        if _reconstruct(oracle, X, ids[~right], label[~right], MIN, MAX, False, depth + 1) and \
+           _reconstruct(oracle, X, ids[right], label[right], MIN, MAX, False, depth + 1):
+            return True
+    return False
+
+
+@pytest.mark.parametrize("path", _load("ref_buckets_*.npz"))
+def test_reference_tree_is_reproduced_by_the_restated_rules(oracle, path):
+    """Whole reference trees (20-60 leaves, several levels): at every internal
+    node some pair of the node's own points separates its leaves under the
+    restated split rule (lane-strided offset below the root), both sides keep at
+    least MIN points, and every group of at most MAX-2 points is a single leaf.
+    This pins the non-root hyperplane arithmetic and the leaf/merge rule to the
+    reference binary without knowing which pairs it sampled."""
+    z = np.load(path)
+    X, idx = z["X"], z["idx"]
+    N, D, MIN, MAX, K = [int(v) for v in z["params"]]
+    buckets = sorted({frozenset(r[r >= 0].tolist()) for r in idx}, key=min)
+    label = np.empty(N, np.int32)
+    for b, members in enumerate(buckets):
+        label[list(members)] = b
+    assert _reconstruct(oracle, X, np.arange(N, dtype=np.int32), label, MIN, MAX, True)
