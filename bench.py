@@ -51,7 +51,10 @@ WORKLOADS = {
 # DRAM bytes (read+write) per launch of the dominant kernel from the committed
 # ncu capture, per unit processed; None until a capture exists.  Filled from
 # the summaries under profiles/.
-NCU_TRAFFIC_PER_POINT = {"explore": None, "bucket_knn": None, "tree_levels": None, "tree_subtrees": None}
+# (ncu --set full captures of a 400 000-point case of c2, summaries under profiles/; traffic grows
+# in proportion to the points a launch processes)
+NCU_TRAFFIC_PER_POINT = {"explore": 58.81e9 / 400_000, "bucket_knn": 359.7e6 / 400_000,
+                         "tree_project": 174.1e6 / 400_000, "tree_subtrees": 702.5e6 / 400_000}
 
 
 def make_points(w, n_override=None):
@@ -293,10 +296,16 @@ def run_ours(args, w):
     phases["bucket_knn"] = dict(
         launches=trees_run, ms_per_launch=knn_ms / trees_run,
         bytes_per_launch=4.0 * N * D + 4.0 * N + 2 * 8.0 * N * K)
-    # one "launch" of the level phase = all level kernels (project + decide + scatter) of one tree
-    phases["tree_levels"] = dict(
-        launches=trees_run, ms_per_launch=(forest_ms - knn_ms - sub_ms) / trees_run,
-        bytes_per_launch=(4.0 * (D + 2) * lvl_pts + 4.0 * (D + 1) * lvl_nodes) / trees_run)
+    # tree levels: the projection kernel (one launch per level) and the rest of the level work
+    # (decide + scatter kernels, counter read-back by the host)
+    proj_ms = tot.get("project_us", 0) / 1e3
+    proj_n = max(1, tot.get("project_launches", 0))
+    phases["tree_project"] = dict(
+        launches=proj_n, ms_per_launch=proj_ms / proj_n,
+        bytes_per_launch=(4.0 * (D + 1) * lvl_pts + 4.0 * (D + 1) * lvl_nodes) / proj_n)
+    phases["tree_level_rest"] = dict(
+        launches=proj_n, ms_per_launch=(forest_ms - knn_ms - sub_ms - proj_ms) / proj_n,
+        bytes_per_launch=4.0 * 3 * lvl_pts / proj_n)
     if sub_ms > 0:
         phases["tree_subtrees"] = dict(
             launches=trees_run, ms_per_launch=sub_ms / trees_run,
@@ -314,13 +323,15 @@ def run_ours(args, w):
     for p in phases.values():
         p["gbs"] = p["bytes_per_launch"] / (p["ms_per_launch"] * 1e-3) / 1e9 if p["ms_per_launch"] > 0 else None
         p["total_ms"] = p["ms_per_launch"] * p["launches"]
-    dom = max(phases, key=lambda n: phases[n]["total_ms"])
-    kernel_of = {"bucket_knn": "k_bucket_knn", "tree_levels": "k_project_wide (+k_decide, k_scatter) per tree",
+    dom = max((n for n in phases if n != "tree_level_rest"), key=lambda n: phases[n]["total_ms"])
+    kernel_of = {"bucket_knn": "k_bucket_knn (k_bucket_knn_tc where leaves exceed one shared-memory block)",
+                 "tree_project": "k_project_wide", "tree_level_rest": "k_decide + k_scatter + host read-back",
                  "tree_subtrees": "k_subtree", "explore": "k_explore", "merge_lists": "k_merge_lists"}
     traffic_unit = NCU_TRAFFIC_PER_POINT.get(dom)
     roofline = dict(bound="hbm", kernel=kernel_of[dom], achieved=phases[dom]["gbs"], peak=peak_gbs,
                     unit="GB/s", frac=(phases[dom]["gbs"] or 0) / peak_gbs, peak_kind=peak_kind,
-                    traffic=(traffic_unit * (rows_own if dom == "explore" else N)) if traffic_unit else None,
+                    traffic=(traffic_unit * {"explore": rows_own, "tree_project": lvl_pts / proj_n}.get(dom, N))
+                    if traffic_unit and args.workload == "c2" else None,
                     algorithmic_bytes_per_launch=phases[dom]["bytes_per_launch"],
                     ms_per_launch=phases[dom]["ms_per_launch"])
 

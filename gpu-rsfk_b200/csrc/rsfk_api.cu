@@ -278,6 +278,20 @@ const char* rsfk_last_message(void) { return g_last_message.c_str(); }
 void rsfk_free(void* p) { free(p); }
 int rsfk_max_neighbors(void) { return rsfk::list_capacity(); }
 
+void rsfk_release_memory(void)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_default) return;
+    cudaSetDevice(g_default->c.device);
+    cudaStreamSynchronize(g_default->c.stream);
+    for (auto& b : g_default->c.slots) {
+        if (b.ptr) cudaFree(b.ptr);
+        b.ptr = nullptr;
+        b.bytes = 0;
+    }
+    g_default->has_tree = false;
+}
+
 long long rsfk_kernel_launches(void) { return rsfk::g_kernel_launches.load(); }
 
 void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TREE_CHILD,
@@ -309,9 +323,12 @@ void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TRE
     float* d_points = nullptr;
     int* d_idx = nullptr;
     float* d_dist = nullptr;
-    bool ok = c.check(cudaMalloc((void**)&d_points, pts_bytes), "cudaMalloc(points)") &&
-              c.check(cudaMalloc((void**)&d_idx, sizeof(int) * list_elems), "cudaMalloc(indices)") &&
-              c.check(cudaMalloc((void**)&d_dist, sizeof(float) * list_elems), "cudaMalloc(distances)");
+    // device copies live in the context's grow-only pool: no cudaMalloc/cudaFree per call
+    // (rsfk_release_memory() returns the pool to the driver)
+    d_points = (float*)c.scratch(Context::HOST_POINTS, pts_bytes);
+    d_idx = (int*)c.scratch(Context::HOST_IDX, sizeof(int) * list_elems);
+    d_dist = (float*)c.scratch(Context::HOST_DIST, sizeof(float) * list_elems);
+    bool ok = d_points && d_idx && d_dist;
     if (ok && VERBOSE >= 1) printf("Device allocations take %lf seconds\n", now_s() - ta0);
     const int dev_id = c.device;
     auto h2d = [&](void* d, void* h, size_t n, const char* what) {
@@ -346,9 +363,6 @@ void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TRE
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "D2H");
     if (ok && VERBOSE >= 1) printf("Device to host copies take %lf seconds\n", now_s() - t2);
     cudaStreamSynchronize(c.stream);
-    if (d_points) cudaFree(d_points);
-    if (d_idx) cudaFree(d_idx);
-    if (d_dist) cudaFree(d_dist);
     publish(c);
 }
 
@@ -372,7 +386,8 @@ void pymodule_cluster_by_sample_tree(int N, int D, int MIN_TREE_CHILD, int MAX_T
     }
     const double t0 = now_s();
     float* d_points = nullptr;
-    bool ok = c.check(cudaMalloc((void**)&d_points, sizeof(float) * (size_t)N * D), "cudaMalloc(points)");
+    d_points = (float*)c.scratch(Context::HOST_POINTS, sizeof(float) * (size_t)N * D);
+    bool ok = d_points != nullptr;
     ok = ok && c.check(cudaMemcpyAsync(d_points, points, sizeof(float) * (size_t)N * D, cudaMemcpyHostToDevice, c.stream), "H2D points");
     ok = ok && rsfk::tree_build(c, d_points, N, D, MIN_TREE_CHILD, MAX_TREE_CHILD, MAX_DEPTH, RANDOM_STATE,
                                 nullptr, 0, h->tree);
@@ -415,7 +430,6 @@ void pymodule_cluster_by_sample_tree(int N, int D, int MIN_TREE_CHILD, int MAX_T
         }
     }
     cudaStreamSynchronize(c.stream);
-    if (d_points) cudaFree(d_points);
     publish(c);
 }
 
@@ -455,10 +469,11 @@ int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
             !c.check(cudaStreamSynchronize(c.stream), "stats"))
             return c.status;
     }
-    const double v[9] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+    const double v[11] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
                          c.stats.bucket_knn_us, (double)evaluated, c.stats.subtree_us,
-                         (double)c.stats.sub_active_points, (double)c.stats.sub_nodes, c.stats.tree_build_us};
-    for (int i = 0; i < n && i < 9; ++i) out[i] = v[i];
+                         (double)c.stats.sub_active_points, (double)c.stats.sub_nodes, c.stats.tree_build_us,
+                         c.stats.project_us, (double)c.stats.project_launches};
+    for (int i = 0; i < n && i < 11; ++i) out[i] = v[i];
     return RSFK_OK;
 }
 

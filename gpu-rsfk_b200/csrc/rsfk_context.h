@@ -57,6 +57,8 @@ struct Stats {
     long long tree_nodes = 0;         // nodes split (hyperplanes formed)
     double bucket_knn_us = 0.0;       // device time of the bucket-KNN kernels
     double subtree_us = 0.0;          // device time of the subtree kernels
+    double project_us = 0.0;          // device time of the projection kernels of the tree levels
+    long long project_launches = 0;
     double tree_build_us = 0.0;       // host-observed time of the tree builds (each ends with a stream sync)
     long long sub_active_points = 0;  // part of tree_active_points projected inside subtree CTAs
     long long sub_nodes = 0;          // part of tree_nodes split inside subtree CTAs
@@ -84,12 +86,13 @@ struct Context {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
         PERM_FINAL_B, LEAF_START_B, LEAF_COUNT_B,
-        SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, N_SLOTS
+        SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST, N_SLOTS
     };
     Stats stats;
     Buffer slots[N_SLOTS];
     LevelCounters* host_counters = nullptr; // pinned
     cudaEvent_t sub_ev[2] = {nullptr, nullptr};
+    std::vector<cudaEvent_t> level_ev; // two per tree level, reused by every tree
     // A forest overlaps the bucket KNN of tree t (second stream) with the build
     // of tree t+1 (main stream); trees alternate between two result buffers.
     int result_buf = 0;
@@ -170,6 +173,8 @@ struct Context {
         for (auto& b : slots) { if (b.ptr) cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
         if (host_counters) { cudaFreeHost(host_counters); host_counters = nullptr; }
         for (auto& e : sub_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
+        for (auto& e : level_ev) cudaEventDestroy(e);
+        level_ev.clear();
         for (int i = 0; i < 2; ++i) {
             if (ev_tree[i]) cudaEventDestroy(ev_tree[i]);
             if (ev_knn[i]) cudaEventDestroy(ev_knn[i]);

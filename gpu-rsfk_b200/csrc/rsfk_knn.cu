@@ -144,8 +144,8 @@ __device__ __forceinline__ float small_d_dist_any(const float* a, const float* b
     return small_d_dist<16>(a, b, D);
 }
 
-template <int KPL, bool SMALL_D>
-__global__ void __launch_bounds__(KNN_THREADS)
+template <int KPL, bool SMALL_D, bool VEC4>
+__global__ void __launch_bounds__(KNN_THREADS, 3)
 k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict__ perm,
              const int* __restrict__ leaf_start, const int* __restrict__ leaf_count,
              int* __restrict__ knn_idx, float* __restrict__ knn_dist, int B, int two_blocks)
@@ -194,6 +194,62 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
                     const float dsum = small_d_dist_any(XI + (size_t)r * D, XJc + (size_t)c * D, D);
                     tile[r * TS + c] = dsum;
                     if (diag) tile[c * TS + r] = dsum;
+                }
+            } else if (VEC4) {
+                // 16-byte shared-memory loads: eight lanes share a 4x2 sub-tile of pairs, lane t
+                // of the eight owns dimensions 4t..4t+3 (+32, ...), i.e. virtual lanes 4t..4t+3 of
+                // the reference's sum; a warp covers an 8x4 tile.
+                const int g = lane >> 3, t8 = lane & 7;
+                const int D4 = D >> 2;
+                const int sI = (mI + 7) >> 3, sJ = (mJ + 3) >> 2;
+                const float4* XI4 = reinterpret_cast<const float4*>(XI);
+                const float4* XJ4 = reinterpret_cast<const float4*>(XJc);
+                for (int st = warp; st < sI * sJ; st += KNN_WARPS) {
+                    const int ti = st / sJ, tj = st - ti * sJ;
+                    if (diag && 4 * tj + 3 < 8 * ti) continue; // wholly below the diagonal
+                    const int r0 = 8 * ti + 4 * (g >> 1), c0 = 4 * tj + 2 * (g & 1);
+                    const float4* xi[4];
+                    const float4* xj[2];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) xi[u] = XI4 + (size_t)min(r0 + u, mI - 1) * D4;
+#pragma unroll
+                    for (int v = 0; v < 2; ++v) xj[v] = XJ4 + (size_t)min(c0 + v, mJ - 1) * D4;
+                    float acc[8][4];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+#pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) acc[q][cc] = 0.0f;
+                    for (int k4 = t8; k4 < D4; k4 += 8) {
+                        float4 a[4], b[2];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) a[u] = xi[u][k4];
+#pragma unroll
+                        for (int v = 0; v < 2; ++v) b[v] = xj[v][k4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int v = 0; v < 2; ++v) {
+                                float df;
+                                df = __fsub_rn(a[u].x, b[v].x); acc[u * 2 + v][0] = __fmaf_rn(df, df, acc[u * 2 + v][0]);
+                                df = __fsub_rn(a[u].y, b[v].y); acc[u * 2 + v][1] = __fmaf_rn(df, df, acc[u * 2 + v][1]);
+                                df = __fsub_rn(a[u].z, b[v].z); acc[u * 2 + v][2] = __fmaf_rn(df, df, acc[u * 2 + v][2]);
+                                df = __fsub_rn(a[u].w, b[v].w); acc[u * 2 + v][3] = __fmaf_rn(df, df, acc[u * 2 + v][3]);
+                            }
+                    }
+                    float part[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        part[q] = __fadd_rn(__fadd_rn(acc[q][0], acc[q][1]), __fadd_rn(acc[q][2], acc[q][3]));
+                    halve_step<4, 1>(part, lane);
+                    halve_step<2, 2>(part, lane);
+                    halve_step<1, 4>(part, lane);
+                    // lane t8 of the group now holds pair 4*bit0 + 2*bit1 + bit2 of its 4x2 sub-tile
+                    const int item = ((t8 & 1) << 2) | (t8 & 2) | ((t8 & 4) >> 2);
+                    const int r = r0 + (item >> 1), c = c0 + (item & 1);
+                    if (r < mI && c < mJ) {
+                        tile[r * TS + c] = part[0];
+                        if (diag) tile[c * TS + r] = part[0];
+                    }
                 }
             } else
             for (int t = warp; t < tI * tJ; t += KNN_WARPS) {
@@ -597,7 +653,9 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     }
     const size_t smem = bytes(B, two);
     RSFK_DISPATCH_KPL(K, {
-        auto kern = (D <= 16) ? k_bucket_knn<KPL, true> : k_bucket_knn<KPL, false>;
+        const bool v4 = (D % 4 == 0) && (B % 4 == 0);
+        auto kern = (D <= 16) ? k_bucket_knn<KPL, true, false>
+                              : (v4 ? k_bucket_knn<KPL, false, true> : k_bucket_knn<KPL, false, false>);
         if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                        "bucket_knn smem attribute"))
             return false;

@@ -835,13 +835,22 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     }
 
     int depth = 1;
+    int timed_levels = 0;
     long long active = N;
     for (; depth < max_depth && n_nodes > 0; ++depth) {
         const int level = depth - 1; // level of the nodes being split
         ctx.stats.tree_active_points += active;
         ctx.stats.tree_nodes += n_nodes;
+        while ((int)ctx.level_ev.size() < 2 * (timed_levels + 1)) {
+            cudaEvent_t e;
+            cudaEventCreate(&e);
+            ctx.level_ev.push_back(e);
+        }
+        cudaEventRecord(ctx.level_ev[2 * timed_levels], st);
         launch_project(ctx, d_points, D, perm[cur], nodes[cur], chunk_node[cur], n_chunks, side_bits,
                        chunk_left, table, n_table, seed, level);
+        cudaEventRecord(ctx.level_ev[2 * timed_levels + 1], st);
+        timed_levels++;
         k_reset_level<<<1, 1, 0, st>>>(cnt);
         k_decide<<<(n_nodes * 32 + TREE_THREADS - 1) / TREE_THREADS, TREE_THREADS, 0, st>>>(
             nodes[cur], n_nodes, chunk_left, nodes[cur ^ 1], node_cap, chunk_node[cur ^ 1], chunk_cap,
@@ -894,6 +903,12 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     if (ctx.host_counters->error)
         return ctx.fail(ctx.host_counters->error, "tree_build: internal table overflow");
 
+    for (int l = 0; l < timed_levels; ++l) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, ctx.level_ev[2 * l], ctx.level_ev[2 * l + 1]) == cudaSuccess)
+            ctx.stats.project_us += ms * 1e3;
+    }
+    ctx.stats.project_launches += timed_levels;
     ctx.stats.trees++;
     ctx.stats.tree_active_points += (long long)ctx.host_counters->sub_active;
     ctx.stats.tree_nodes += (long long)ctx.host_counters->sub_nodes;

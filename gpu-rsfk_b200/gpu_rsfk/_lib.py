@@ -55,6 +55,8 @@ def load():
     L.rsfk_free.argtypes = [vp]
     L.rsfk_kernel_launches.restype = ll
     L.rsfk_kernel_launches.argtypes = []
+    L.rsfk_release_memory.restype = None
+    L.rsfk_release_memory.argtypes = []
     L.rsfk_max_neighbors.restype = i
     L.rsfk_max_neighbors.argtypes = []
 

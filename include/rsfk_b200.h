@@ -68,6 +68,11 @@ RSFK_EXPORT const char* rsfk_last_message(void);
 RSFK_EXPORT void rsfk_free(void* p);
 /* Number of this library's kernels launched so far in this process. */
 RSFK_EXPORT long long rsfk_kernel_launches(void);
+/* The host-pointer entry points keep their device buffers (points, lists, tree
+ * scratch) between calls, so repeated calls do not pay cudaMalloc/cudaFree (the
+ * reference allocates and frees per call, src/rsfk.cu:2039-2067,2175-2181).
+ * This returns that memory to the driver. */
+RSFK_EXPORT void rsfk_release_memory(void);
 /* Largest K the K-list kernels support. */
 RSFK_EXPORT int rsfk_max_neighbors(void);
 
@@ -89,7 +94,8 @@ RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
  * bucket-KNN kernels, out[4] candidates whose distance the exploration sweeps
  * evaluated, out[5] device microseconds spent in the subtree kernels, out[6] and
  * out[7] the part of out[1] and out[2] done inside subtree kernels, out[8] microseconds
- * the tree builds took as seen from the host.  The reference's counterpart is its ForestLog of per-phase
+ * the tree builds took as seen from the host, out[9] device microseconds spent in the
+ * projection kernels of the tree levels and out[10] their launch count.  The reference's counterpart is its ForestLog of per-phase
  * wall-clock times (src/include/rsfk.h:274-392). */
 RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
