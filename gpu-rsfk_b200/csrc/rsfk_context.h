@@ -50,6 +50,15 @@ struct LevelCounters {
     unsigned long long sub_nodes;  // nodes split inside subtree CTAs
 };
 
+// Per-level mailbox in pinned, device-mapped host memory: the scatter kernel of a
+// level posts the next level's sizes here and the host picks them up by polling
+// `seq`, without a copy or a stream synchronisation.
+struct LevelMail {
+    int n_nodes, n_chunks, active, n_small, error;
+    int seq; // written last: the loop depth these numbers belong to
+    int pad0, pad1;
+};
+
 // Work counters a benchmark reads to turn kernel times into achieved bytes/s.
 struct Stats {
     long long trees = 0;              // trees built
@@ -91,6 +100,7 @@ struct Context {
     Stats stats;
     Buffer slots[N_SLOTS];
     LevelCounters* host_counters = nullptr; // pinned
+    LevelMail* mail = nullptr;              // pinned + mapped
     cudaEvent_t sub_ev[2] = {nullptr, nullptr};
     std::vector<cudaEvent_t> level_ev; // two per tree level, reused by every tree
     // A forest overlaps the bucket KNN of tree t (second stream) with the build
@@ -172,6 +182,7 @@ struct Context {
     {
         for (auto& b : slots) { if (b.ptr) cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
         if (host_counters) { cudaFreeHost(host_counters); host_counters = nullptr; }
+        if (mail) { cudaFreeHost(mail); mail = nullptr; }
         for (auto& e : sub_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
         for (auto& e : level_ev) cudaEventDestroy(e);
         level_ev.clear();

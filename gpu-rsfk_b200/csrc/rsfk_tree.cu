@@ -20,7 +20,9 @@
 // src/kernels/build_tree_create_nodes.cu:88-104, src/kernels/create_node.cu:60-66,120-134.
 // The arithmetic keeps the reference's summation order so that the side of
 // every point is bit-for-bit the reference's for the same split pair.
+#include <chrono>
 #include <cstdlib>
+#include <cstring>
 
 #include "rsfk_context.h"
 
@@ -444,10 +446,25 @@ __global__ void __launch_bounds__(TREE_THREADS)
 k_scatter(const int* __restrict__ perm_in, int* __restrict__ perm_out, int* __restrict__ perm_final,
           const Node* __restrict__ nodes, const int* __restrict__ chunk_node,
           const unsigned* __restrict__ side_bits, const int* __restrict__ chunk_lprefix,
-          const NodeSplit* __restrict__ split)
+          const NodeSplit* __restrict__ split, LevelCounters* counters, volatile LevelMail* mail, int seq)
 {
     __shared__ unsigned sMask[CHUNK_WORDS];
     __shared__ int sWordLeft[CHUNK_WORDS];
+
+    // The decide kernel has finished (stream order): post the next level's sizes to
+    // the host mailbox and clear the per-level counters for the next decide kernel.
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        mail->n_nodes = counters->n_nodes_next;
+        mail->n_chunks = counters->n_chunks_next;
+        mail->active = counters->active_next;
+        mail->n_small = counters->n_small;
+        mail->error = counters->error;
+        __threadfence_system();
+        mail->seq = seq;
+        counters->n_nodes_next = 0;
+        counters->n_chunks_next = 0;
+        counters->active_next = 0;
+    }
 
     const int chunk = blockIdx.x;
     const int node = chunk_node[chunk];
@@ -727,13 +744,6 @@ __global__ void k_tree_init(Node* nodes, int* chunk_node, int n_chunks, int N, i
     for (int c = t; c < n_chunks; c += gridDim.x * blockDim.x) chunk_node[c] = 0;
 }
 
-__global__ void k_reset_level(LevelCounters* cnt)
-{
-    cnt->n_nodes_next = 0;
-    cnt->n_chunks_next = 0;
-    cnt->active_next = 0;
-}
-
 __global__ void k_single_leaf(int* leaf_start, int* leaf_count, int N, LevelCounters* cnt)
 {
     leaf_start[0] = 0;
@@ -814,6 +824,11 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     if (!ctx.host_counters &&
         !ctx.check(cudaMallocHost((void**)&ctx.host_counters, sizeof(LevelCounters)), "cudaMallocHost"))
         return false;
+    if (!ctx.mail) {
+        if (!ctx.check(cudaHostAlloc((void**)&ctx.mail, sizeof(LevelMail), cudaHostAllocMapped), "cudaHostAlloc(mail)"))
+            return false;
+    }
+    memset(ctx.mail, 0, sizeof(LevelMail)); // seq 0 is never a loop depth
     const int4* table = (const int4*)d_table;
 
     const int grid_n = (int)(((long long)N + 255) / 256 < 4096 ? ((long long)N + 255) / 256 : 4096);
@@ -836,6 +851,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
 
     int depth = 1;
     int timed_levels = 0;
+    int n_small_seen = 0;
     long long active = N;
     for (; depth < max_depth && n_nodes > 0; ++depth) {
         const int level = depth - 1; // level of the nodes being split
@@ -851,23 +867,45 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
                        chunk_left, table, n_table, seed, level);
         cudaEventRecord(ctx.level_ev[2 * timed_levels + 1], st);
         timed_levels++;
-        k_reset_level<<<1, 1, 0, st>>>(cnt);
         k_decide<<<(n_nodes * 32 + TREE_THREADS - 1) / TREE_THREADS, TREE_THREADS, 0, st>>>(
             nodes[cur], n_nodes, chunk_left, nodes[cur ^ 1], node_cap, chunk_node[cur ^ 1], chunk_cap,
             split, leaf_start, leaf_count, leaf_cap, small_nodes, small_cap, small_limit, depth, cnt, table,
             n_table, min_children, max_children);
         k_scatter<<<n_chunks, TREE_THREADS, 0, st>>>(perm[cur], perm[cur ^ 1], perm_final, nodes[cur],
-                                                     chunk_node[cur], side_bits, chunk_left, split);
-        count_launches(3);
-        if (!ctx.check(cudaMemcpyAsync(ctx.host_counters, cnt, sizeof(LevelCounters),
-                                       cudaMemcpyDeviceToHost, st), "counters D2H") ||
-            !ctx.check(cudaStreamSynchronize(st), "tree level"))
-            return false;
-        if (ctx.host_counters->error)
-            return ctx.fail(ctx.host_counters->error, "tree_build: internal table overflow");
-        n_nodes = ctx.host_counters->n_nodes_next;
-        n_chunks = ctx.host_counters->n_chunks_next;
-        active = ctx.host_counters->active_next;
+                                                     chunk_node[cur], side_bits, chunk_left, split, cnt,
+                                                     ctx.mail, depth);
+        count_launches(2);
+        // wait for the mailbox (bounded): the scatter kernel posts it when it starts
+        {
+            volatile LevelMail* mail = ctx.mail;
+            const auto t_start = std::chrono::steady_clock::now();
+            unsigned spins = 0;
+            bool got = false;
+            while (!(got = (mail->seq == depth))) {
+                if ((++spins & 0x3ff) == 0) {
+                    const cudaError_t q = cudaStreamQuery(st);
+                    if (q != cudaErrorNotReady) { // finished or failed: the mail is there now or never
+                        got = (mail->seq == depth);
+                        if (!got) ctx.check(q == cudaSuccess ? cudaErrorUnknown : q, "tree level");
+                        break;
+                    }
+                    if (std::chrono::steady_clock::now() - t_start > std::chrono::seconds(30)) break;
+                }
+            }
+            std::atomic_thread_fence(std::memory_order_acquire);
+            if (!got) {
+                cudaStreamSynchronize(st);
+                return ctx.fail(RSFK_ERR_CUDA, "tree_build: level mailbox never arrived");
+            }
+        }
+        if (ctx.mail->error) {
+            cudaStreamSynchronize(st);
+            return ctx.fail(ctx.mail->error, "tree_build: internal table overflow");
+        }
+        n_nodes = ctx.mail->n_nodes;
+        n_chunks = ctx.mail->n_chunks;
+        active = ctx.mail->active;
+        n_small_seen = ctx.mail->n_small;
         cur ^= 1;
         levels = depth;
     }
@@ -876,7 +914,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
                                                 leaf_count, leaf_cap, cnt, max_children);
         count_launches(1);
     }
-    const int n_small = (N > 1 && levels > 0) ? ctx.host_counters->n_small : 0;
+    const int n_small = (N > 1 && levels > 0) ? n_small_seen : 0;
     if (n_small > 0) {
         if (sub_smem > 16 * 1024 &&
             !ctx.check(cudaFuncSetAttribute(k_subtree, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sub_smem),
