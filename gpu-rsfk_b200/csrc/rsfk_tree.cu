@@ -522,7 +522,7 @@ struct SubNode {
     int tbl;
 };
 
-__global__ void __launch_bounds__(TREE_THREADS)
+__global__ void __launch_bounds__(TREE_THREADS, 4)
 k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
           const Node* __restrict__ small_nodes, int* __restrict__ leaf_start,
           int* __restrict__ leaf_count, int leaf_cap, LevelCounters* __restrict__ cnt,
