@@ -302,3 +302,55 @@ def test_bucket_knn_tensor_core_shapes_bit_exact(forest, oracle, N, D, K, MIN, M
         forest.synchronize()
         np.testing.assert_array_equal(d_idx.cpu().numpy(), idx)
         np.testing.assert_array_equal(d_dist.cpu().numpy(), dist)
+
+
+def test_maximum_list_length_and_refusal_beyond_it(forest, oracle):
+    """K = 256 is the largest list the kernels hold; 257 is refused with a status,
+    not computed wrongly."""
+    import torch
+    from gpu_rsfk import _lib
+    N, D, K = 1500, 24, 256
+    X = _uniform(N, D, 31)
+    idx, dist = oracle.init_lists(N, K)
+    tr = oracle.build_tree(X, 300, 700, seed=1)
+    ridx, rdist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+    d_idx, d_dist = _dev(idx), _dev(dist)
+    forest.bucket_knn_table(_dev(X), _dev(tr["perm"]), _dev(tr["leaf_start"]), _dev(tr["leaf_count"]),
+                            int(tr["leaf_count"].max()), d_idx, d_dist)
+    np.testing.assert_array_equal(d_idx.cpu().numpy(), ridx)
+    np.testing.assert_array_equal(d_dist.cpu().numpy(), rdist)
+    eidx, edist = oracle.explore(X, ridx, ridx, rdist)
+    forest.explore(_dev(X), d_idx.clone(), d_idx, d_dist)
+    np.testing.assert_array_equal(d_idx.cpu().numpy(), eidx)
+    np.testing.assert_array_equal(d_dist.cpu().numpy(), edist)
+    big_i = torch.full((N, 257), -1, dtype=torch.int32, device="cuda")
+    big_d = torch.full((N, 257), float("inf"), dtype=torch.float32, device="cuda")
+    with pytest.raises(_lib.RSFKLibraryError):
+        forest.sort_rows(big_i, big_d)
+
+
+def test_one_dimension_and_no_trees_through_the_host_entry_point(oracle):
+    """D = 1 and n_trees = 0 (sweeps only, on caller-provided lists) through the
+    drop-in C ABI with host buffers."""
+    from gpu_rsfk import _lib
+    L = _lib.load()
+    N, D, K = 4000, 1, 6
+    X = _uniform(N, D, 33)
+    idx, dist = oracle.init_lists(N, K)
+    for t in range(2):
+        tr = oracle.build_tree(X, K + 1, 2 * K + 2, seed=t)
+        idx, dist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+    shuffled_i, shuffled_d = idx[:, ::-1].copy(), dist[:, ::-1].copy()      # caller's rows are unordered
+    ei, ed = oracle.explore(X, idx, idx, dist)
+    ei, ed = oracle.explore(X, ei, ei, ed)
+    log = np.zeros(2, np.float32)
+    L.pymodule_rsfk_knn(0, K, N, D, K + 1, 2 * K + 2, 5000, 0, 0, 2, X, shuffled_i, shuffled_d, log)
+    _lib.check_last("pymodule_rsfk_knn")
+    np.testing.assert_array_equal(shuffled_i, ei)
+    np.testing.assert_array_equal(shuffled_d, ed)
+    # invalid arguments leave the outputs untouched and set a status
+    before = shuffled_i.copy()
+    L.pymodule_rsfk_knn(1, 0, N, D, 7, 14, 5000, 0, 0, 0, X, shuffled_i, shuffled_d, log)
+    assert L.rsfk_last_status() == 2
+    np.testing.assert_array_equal(shuffled_i, before)
+    L.rsfk_release_memory()
