@@ -15,7 +15,7 @@
 //
 // One CTA per leaf.  The leaf's rows are cut into blocks of 128; for a block
 // pair (I, J) the 128 x 128 Gram tile accumulates in tensor memory over K-chunks
-// of 64 dimensions.  Operands are staged by the threads themselves (rows are
+// of 32 dimensions.  Operands are staged by the threads themselves (rows are
 // gathered through the permutation, so no 2-D TMA tile exists): a chunk is split
 // into big/small TF32 and stored in the K-major, no-swizzle core-matrix layout
 // the UMMA shared-memory descriptor addresses (8 rows x 16 bytes per core
@@ -25,7 +25,7 @@
 namespace tc {
 
 constexpr int TC_ROWS = 128;            // MMA M and N: rows of one leaf block
-constexpr int TC_KC = 64;               // dimensions staged per chunk
+constexpr int TC_KC = 32;               // dimensions staged per chunk
 constexpr int TC_LBO = 128;             // bytes between K-adjacent core matrices
 constexpr int TC_SBO = (TC_KC / 4) * 128; // bytes between 8-row groups
 constexpr int TC_OPERAND_BYTES = TC_ROWS * TC_KC * 4; // one of big / small
@@ -130,7 +130,12 @@ __host__ __device__ inline Layout layout_for(int D, int max_leaf)
     l.off_norm = o;  o += 2 * TC_ROWS * 4;
     l.off_ids = o;   o += 2 * TC_ROWS * 4;
     l.off_pass = o;  o += TC_ROWS * l.pass_words * 4;
-    l.off_xp = o;    o += KNN_WARPS * ((D + 3) & ~3) * 4;
+    // the per-warp copy of a row (exact distances, row phase) reuses the operand
+    // area, which is idle then, when it fits there
+    const int xp_bytes = KNN_WARPS * ((D + 3) & ~3) * 4;
+    const int operand_area = (l.two_operands ? 4 : 2) * TC_OPERAND_BYTES;
+    if (xp_bytes <= operand_area) l.off_xp = 0;
+    else { l.off_xp = o; o += xp_bytes; }
     l.off_queue = o; o += KNN_WARPS * EXP_QUEUE * 4;
     l.off_misc = o;  o += 64;
     l.total = o;
@@ -269,6 +274,7 @@ k_bucket_knn_tc(const float* __restrict__ pts, int D, int K, const int* __restri
         for (int bj = 0; bj < n_blocks && !failed; ++bj) {
             const int j0 = bj * TC_ROWS;
             const bool diag = (bj == bi);
+            __syncthreads(); // the previous tile's row phase used the operand area for its row copies
             if (!diag) {
                 for (int r = threadIdx.x; r < TC_ROWS; r += blockDim.x) sIdsB[r] = j0 + r < m ? ids[j0 + r] : -1;
                 __syncthreads();
