@@ -231,7 +231,8 @@ def run_ours(args, w):
 
     N, D, K = args.points or w["N"], w["D"], w["K"]
     X = make_points(w, args.points)
-    X_host = torch.from_numpy(X).pin_memory()
+    # pinned copy only where the end-to-end leg needs it (N > 1: every step uploads the points)
+    X_host = torch.from_numpy(X).pin_memory() if (world > 1 and not args.no_e2e) else torch.from_numpy(X)
     X_dev = X_host.to(dev, non_blocking=True)
     torch.cuda.synchronize()
 
