@@ -138,6 +138,7 @@ ORC_API void orc_sample_positions(int seed, int depth, int start, int count, int
 
 typedef struct {
     int start, count, p1, p2, tbl;
+    int qs, qc; /* segment of the query permutation routed to this node */
 } orc_node;
 
 typedef struct {
@@ -215,15 +216,29 @@ static int table_child(const int* table, int n_table, int tbl, int side)
  *
  * Outputs: perm[N]; leaf_start/leaf_count (caller frees with orc_free), leaves
  * ordered by segment start; returns the number of levels processed.
+ *
+ * Query routing (the ANN path, src/rsfk.cu:270-347): queries[NQ][D] descend the
+ * tree level by level beside the base points.  A query takes the side the
+ * split rule gives it (the same kernel as for base points,
+ * build_tree_check_points_side.cu:131-151, run over the query array); where
+ * that side holds no node of its own -- it was empty or it dissolved into its
+ * sibling -- the query follows to the sibling
+ * (build_tree_update_parents_ann.cu:150-160).  q_start[q]/q_count[q] receive
+ * the segment of `perm` that is the leaf bucket query q ends in.
  */
-ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, int MAX_DEPTH,
+static int build_tree_impl(const float* points, int N, int D, int MIN, int MAX, int MAX_DEPTH,
                            int seed, const int* table, int n_table, int* perm,
                            int** leaf_start_out, int** leaf_count_out, int* n_leaves_out,
-                           int* table_out, int table_out_cap, int* n_table_out)
+                           int* table_out, int table_out_cap, int* n_table_out,
+                           const float* queries, int NQ, int* q_start, int* q_count)
 {
     ivec ls = {0, 0, 0}, lc = {0, 0, 0};
     int n_rec = 0;
     for (int i = 0; i < N; ++i) perm[i] = i;
+    if (!queries) NQ = 0;
+    int* qperm = (int*)malloc(sizeof(int) * (size_t)(NQ > 0 ? NQ : 1));
+    int* qtmp = (int*)malloc(sizeof(int) * (size_t)(NQ > 0 ? NQ : 1));
+    for (int i = 0; i < NQ; ++i) { qperm[i] = i; q_start[i] = -1; q_count[i] = 0; }
     int* tmp = (int*)malloc(sizeof(int) * (size_t)(N > 0 ? N : 1));
     unsigned char* side = (unsigned char*)malloc((size_t)(N > 0 ? N : 1));
     float* nrm = (float*)malloc(sizeof(float) * (size_t)(D > 0 ? D : 1));
@@ -237,9 +252,14 @@ ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, 
     int depth = 0;
 
     if (N <= 0) goto done;
-    if (N == 1) { emit_leaf(&ls, &lc, 0, 1, 0); goto done; }
+    if (N == 1) {
+        emit_leaf(&ls, &lc, 0, 1, 0);
+        for (int i = 0; i < NQ; ++i) { q_start[i] = 0; q_count[i] = 1; }
+        goto done;
+    }
 
     act[0].start = 0; act[0].count = N; act[0].tbl = table ? 0 : -1;
+    act[0].qs = 0; act[0].qc = NQ;
     pick_pair(&act[0], perm, seed, 0, table, n_table);
     n_act = 1;
     if (table_out && n_rec < table_out_cap) {
@@ -270,6 +290,23 @@ ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, 
                 }
                 memcpy(perm + nd.start, tmp, sizeof(int) * (size_t)nd.count);
             }
+            int nQL = 0;
+            if (nd.qc > 0) { /* the queries of this node, same rule, same stable order */
+                int l = 0, r = 0;
+                for (int i = 0; i < nd.qc; ++i) {
+                    int q = qperm[nd.qs + i];
+                    float pr = orc_project(nrm, queries + (size_t)q * D, D);
+                    nQL += !(pr < c);
+                }
+                r = nQL;
+                for (int i = 0; i < nd.qc; ++i) {
+                    int q = qperm[nd.qs + i];
+                    float pr = orc_project(nrm, queries + (size_t)q * D, D);
+                    if (pr < c) qtmp[r++] = q;
+                    else qtmp[l++] = q;
+                }
+                memcpy(qperm + nd.qs, qtmp, sizeof(int) * (size_t)nd.qc);
+            }
             orc_node ch[2];
             int n_ch = 0, leaf[2] = {0, 0}, chside[2] = {0, 0};
             if (nL > 0 && nR > 0 && nL >= MIN && nR >= MIN) {
@@ -277,6 +314,8 @@ ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, 
                 ch[1].start = nd.start + nL; ch[1].count = nR; chside[1] = 1;
                 leaf[0] = nL <= MAX - 2;
                 leaf[1] = nR <= MAX - 2;
+                ch[0].qs = nd.qs;       ch[0].qc = nQL;
+                ch[1].qs = nd.qs + nQL; ch[1].qc = nd.qc - nQL;
                 n_ch = 2;
             } else if (nL > 0 && nR > 0) {
                 /* the side with fewer than MIN points dissolves into the other */
@@ -287,11 +326,13 @@ ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, 
                 ch[0].count = keep ? nR : nL;
                 chside[0] = keep;
                 leaf[0] = nd.count <= MAX;
+                ch[0].qs = nd.qs; ch[0].qc = nd.qc;
                 n_ch = 1;
             } else {
                 ch[0].start = nd.start; ch[0].count = nd.count;
                 chside[0] = (nL > 0) ? 0 : 1;
                 leaf[0] = nd.count <= MAX - 2;
+                ch[0].qs = nd.qs; ch[0].qc = nd.qc;
                 n_ch = 1;
             }
             for (int k = 0; k < n_ch; ++k) {
@@ -311,6 +352,10 @@ ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, 
                 if (merged) { ch[k].start = nd.start; ch[k].count = nd.count; }
                 if (leaf[k]) {
                     emit_leaf(&ls, &lc, ch[k].start, ch[k].count, 0);
+                    for (int i = 0; i < ch[k].qc; ++i) {
+                        q_start[qperm[ch[k].qs + i]] = ch[k].start;
+                        q_count[qperm[ch[k].qs + i]] = ch[k].count;
+                    }
                 } else {
                     if (n_nxt == cap) {
                         cap *= 2;
@@ -329,7 +374,14 @@ ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, 
         n_act = n_nxt;
     }
     /* depth limit: whatever is still open becomes leaves, cut to <= MAX */
-    for (int a = 0; a < n_act; ++a) emit_leaf(&ls, &lc, act[a].start, act[a].count, MAX);
+    for (int a = 0; a < n_act; ++a) {
+        int before = ls.n;
+        emit_leaf(&ls, &lc, act[a].start, act[a].count, MAX);
+        for (int i = 0; i < act[a].qc; ++i) { /* queries of a cut node go to its first piece */
+            q_start[qperm[act[a].qs + i]] = ls.data[before];
+            q_count[qperm[act[a].qs + i]] = lc.data[before];
+        }
+    }
 
 done:
     {   /* order leaves by segment start (insertion order is level order) */
@@ -348,8 +400,30 @@ done:
     }
     if (n_table_out) *n_table_out = n_rec;
     free(ls.data); free(lc.data); free(tmp); free(side); free(nrm); free(act); free(nxt);
-    free(rec_of); free(rec_nxt);
+    free(rec_of); free(rec_nxt); free(qperm); free(qtmp);
     return depth;
+}
+
+ORC_API int orc_build_tree(const float* points, int N, int D, int MIN, int MAX, int MAX_DEPTH,
+                           int seed, const int* table, int n_table, int* perm,
+                           int** leaf_start_out, int** leaf_count_out, int* n_leaves_out,
+                           int* table_out, int table_out_cap, int* n_table_out)
+{
+    return build_tree_impl(points, N, D, MIN, MAX, MAX_DEPTH, seed, table, n_table, perm,
+                           leaf_start_out, leaf_count_out, n_leaves_out, table_out, table_out_cap,
+                           n_table_out, NULL, 0, NULL, NULL);
+}
+
+/* The same tree, with queries[NQ][D] routed to their leaf buckets:
+ * q_start[q], q_count[q] = the bucket's segment of perm. */
+ORC_API int orc_build_tree_route(const float* points, int N, int D, int MIN, int MAX, int MAX_DEPTH,
+                                 int seed, const int* table, int n_table, int* perm,
+                                 int** leaf_start_out, int** leaf_count_out, int* n_leaves_out,
+                                 const float* queries, int NQ, int* q_start, int* q_count)
+{
+    return build_tree_impl(points, N, D, MIN, MAX, MAX_DEPTH, seed, table, n_table, perm,
+                           leaf_start_out, leaf_count_out, n_leaves_out, NULL, 0, NULL,
+                           queries, NQ, q_start, q_count);
 }
 
 ORC_API void orc_free(void* p) { free(p); }
@@ -509,6 +583,94 @@ ORC_API void orc_bucket_knn(const float* points, int N, int D, int K, const int*
             canonical_row(idx + (size_t)ids[i] * K, dist + (size_t)ids[i] * K, K, cands, n_c);
         }
         free(cands);
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Query (ANN) bucket update                                                  */
+/* ------------------------------------------------------------------------- */
+
+/* Reference-order update of the query lists: one warp per query, its bucket's
+ * base points taken 32 at a time in bucket order; a candidate already in the
+ * row when its batch starts is dropped, the batch's distances are computed,
+ * then the candidates replace the row's worst slot, one after another, when
+ * strictly closer (src/kernels/build_tree_update_parents_ann.cu:271-513).
+ * The distance is Sum (q_i - b_i)^2 in the order of orc_dist_sqr
+ * (:205-228: term i on lane i%32, xor butterfly).  List indices are indices of
+ * base points. */
+ORC_API void orc_ann_bucket_knn_ref(const float* points, const float* queries, int NQ, int D, int K,
+                                    const int* perm, const int* q_start, const int* q_count,
+                                    int* idx, float* dist)
+{
+    #pragma omp parallel for schedule(dynamic, 64)
+    for (int q = 0; q < NQ; ++q) {
+        int* ridx = idx + (size_t)q * K;
+        float* rdist = dist + (size_t)q * K;
+        const int* ids = perm + q_start[q];
+        const int m = q_count[q];
+        float maxv;
+        int maxp = argmax_warp(rdist, K, &maxv);
+        for (int b0 = 0; b0 < m; b0 += 32) {
+            int cand[32];
+            float cd[32];
+            const int nb = m - b0 < 32 ? m - b0 : 32;
+            for (int j = 0; j < nb; ++j) {
+                cand[j] = row_has(ridx, K, ids[b0 + j]) ? -1 : ids[b0 + j];
+                if (cand[j] >= 0)
+                    cd[j] = orc_dist_sqr(queries + (size_t)q * D, points + (size_t)cand[j] * D, D);
+            }
+            for (int j = 0; j < nb; ++j) {
+                if (cand[j] < 0) continue;
+                if (cd[j] < maxv) {
+                    ridx[maxp] = cand[j];
+                    rdist[maxp] = cd[j];
+                    maxp = argmax_warp(rdist, K, &maxv);
+                }
+            }
+        }
+    }
+}
+
+/* Tie-free statement of the same update: every query row becomes the K
+ * smallest distinct of (row united with its bucket's base points) by
+ * (distance, index). */
+ORC_API void orc_ann_bucket_knn(const float* points, const float* queries, int NQ, int D, int K,
+                                const int* perm, const int* q_start, const int* q_count,
+                                int* idx, float* dist)
+{
+    #pragma omp parallel for schedule(dynamic, 64)
+    for (int q = 0; q < NQ; ++q) {
+        const int* ids = perm + q_start[q];
+        const int m = q_count[q];
+        orc_entry* cands = (orc_entry*)malloc(sizeof(orc_entry) * (size_t)(m > 0 ? m : 1));
+        for (int j = 0; j < m; ++j) {
+            cands[j].i = ids[j];
+            cands[j].d = orc_dist_sqr(queries + (size_t)q * D, points + (size_t)ids[j] * D, D);
+        }
+        canonical_row(idx + (size_t)q * K, dist + (size_t)q * K, K, cands, m);
+        free(cands);
+    }
+}
+
+/* Exact K nearest base points of every query row (distance in the order of
+ * orc_dist_sqr), ordered by (distance, index): the recall denominator of the
+ * query path. */
+ORC_API void orc_bruteforce_ann(const float* points, int N, const float* queries, int NQ, int D,
+                                int K, int* idx, float* dist)
+{
+    #pragma omp parallel for schedule(dynamic, 8)
+    for (int q = 0; q < NQ; ++q) {
+        orc_entry* all = (orc_entry*)malloc(sizeof(orc_entry) * (size_t)(N > 0 ? N : 1));
+        for (int p = 0; p < N; ++p) {
+            all[p].i = p;
+            all[p].d = orc_dist_sqr(queries + (size_t)q * D, points + (size_t)p * D, D);
+        }
+        qsort(all, (size_t)N, sizeof(orc_entry), entry_cmp);
+        for (int k = 0; k < K; ++k) {
+            idx[(size_t)q * K + k] = k < N ? all[k].i : -1;
+            dist[(size_t)q * K + k] = k < N ? all[k].d : INFINITY;
+        }
+        free(all);
     }
 }
 

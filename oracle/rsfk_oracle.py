@@ -81,6 +81,19 @@ def lib():
                                          ctypes.c_int, _i32, _f32]
         L.orc_recall.restype = ctypes.c_double
         L.orc_recall.argtypes = [_i32, _i32, ctypes.c_int, ctypes.c_int]
+        L.orc_build_tree_route.restype = ctypes.c_int
+        L.orc_build_tree_route.argtypes = [
+            _f32, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+            ctypes.c_void_p, ctypes.c_int, _i32,
+            ctypes.POINTER(_c_int_p), ctypes.POINTER(_c_int_p), _c_int_p,
+            _f32, ctypes.c_int, _i32, _i32]
+        for fn in (L.orc_ann_bucket_knn_ref, L.orc_ann_bucket_knn):
+            fn.restype = None
+            fn.argtypes = [_f32, _f32, ctypes.c_int, ctypes.c_int, ctypes.c_int, _i32, _i32, _i32,
+                           _i32, _f32]
+        L.orc_bruteforce_ann.restype = None
+        L.orc_bruteforce_ann.argtypes = [_f32, ctypes.c_int, _f32, ctypes.c_int, ctypes.c_int,
+                                         ctypes.c_int, _i32, _f32]
         _lib = L
     return _lib
 
@@ -141,6 +154,77 @@ def build_tree(points, min_children, max_children, max_depth=5000, seed=0, table
     if record:
         out["table"] = rec[:n_rec.value].copy()
     return out
+
+
+def build_tree_route(points, queries, min_children, max_children, max_depth=5000, seed=0,
+                     table=None):
+    """The tree of build_tree plus, per query row, the leaf bucket it is routed
+    to: dict(perm, leaf_start, leaf_count, depth, q_start, q_count)."""
+    points, queries = _pts(points), _pts(queries)
+    N, D = points.shape
+    NQ = queries.shape[0]
+    perm = np.empty(N, np.int32)
+    ls, lc, nl = _c_int_p(), _c_int_p(), ctypes.c_int()
+    tbl_ptr, n_tbl = None, 0
+    if table is not None:
+        table = np.ascontiguousarray(table, np.int32).reshape(-1, 4)
+        tbl_ptr, n_tbl = table.ctypes.data, table.shape[0]
+    q_start = np.full(max(NQ, 1), -1, np.int32)
+    q_count = np.zeros(max(NQ, 1), np.int32)
+    depth = lib().orc_build_tree_route(points, N, D, min_children, max_children, max_depth, seed,
+                                       tbl_ptr, n_tbl, perm, ctypes.byref(ls), ctypes.byref(lc),
+                                       ctypes.byref(nl), queries, NQ, q_start, q_count)
+    n = nl.value
+    out = dict(perm=perm,
+               leaf_start=np.ctypeslib.as_array(ls, shape=(max(n, 1),))[:n].copy(),
+               leaf_count=np.ctypeslib.as_array(lc, shape=(max(n, 1),))[:n].copy(),
+               depth=depth, q_start=q_start[:NQ], q_count=q_count[:NQ])
+    lib().orc_free(ls)
+    lib().orc_free(lc)
+    return out
+
+
+def _ann(fn, points, queries, K, perm, q_start, q_count, idx, dist):
+    points, queries = _pts(points), _pts(queries)
+    NQ, D = queries.shape
+    idx = np.ascontiguousarray(idx, np.int32).copy()
+    dist = np.ascontiguousarray(dist, np.float32).copy()
+    fn(points, queries, NQ, D, K, np.ascontiguousarray(perm, np.int32),
+       np.ascontiguousarray(q_start, np.int32), np.ascontiguousarray(q_count, np.int32), idx, dist)
+    return idx, dist
+
+
+def ann_bucket_knn_ref(points, queries, K, perm, q_start, q_count, idx, dist):
+    return _ann(lib().orc_ann_bucket_knn_ref, points, queries, K, perm, q_start, q_count, idx, dist)
+
+
+def ann_bucket_knn(points, queries, K, perm, q_start, q_count, idx, dist):
+    return _ann(lib().orc_ann_bucket_knn, points, queries, K, perm, q_start, q_count, idx, dist)
+
+
+def ann_forest(points, queries, K, n_trees, min_children, max_children, max_depth=5000, seed=0,
+               idx=None, dist=None):
+    """The whole query path: tree t (seed+t) over the base points, queries
+    routed, their lists merged with the bucket they land in."""
+    queries = _pts(queries)
+    if idx is None:
+        idx, dist = init_lists(queries.shape[0], K, self_in_row=False)
+    idx, dist = sort_rows(idx, dist)
+    for t in range(n_trees):
+        tr = build_tree_route(points, queries, min_children, max_children, max_depth, seed + t)
+        idx, dist = ann_bucket_knn(points, queries, K, tr["perm"], tr["q_start"], tr["q_count"],
+                                   idx, dist)
+    return idx, dist
+
+
+def bruteforce_ann(points, queries, K):
+    """Exact K nearest base points of every query row."""
+    points, queries = _pts(points), _pts(queries)
+    oi = np.empty((queries.shape[0], K), np.int32)
+    od = np.empty((queries.shape[0], K), np.float32)
+    lib().orc_bruteforce_ann(points, points.shape[0], queries, queries.shape[0], points.shape[1],
+                             K, oi, od)
+    return oi, od
 
 
 def _bucket(fn, points, K, perm, leaf_start, leaf_count, idx, dist):
