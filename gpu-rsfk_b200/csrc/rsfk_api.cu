@@ -253,6 +253,36 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
     return ok;
 }
 
+// Query path: every tree is built over the base points with its index kept, the
+// queries descend it and their lists take in the bucket they land in.
+bool run_forest_ann(rsfk_ctx* h, const float* d_points, int N, const float* d_queries, int NQ, int D,
+                    int K, int n_trees, int first_tree, int tree_stride, int min_children,
+                    int max_children, int max_depth, int seed, int* d_idx, float* d_dist, int verbose)
+{
+    Context& c = h->c;
+    const bool keep_before = c.keep_index;
+    c.keep_index = true;
+    c.result_buf = 0;
+    bool ok = true;
+    for (int i = 0; i < n_trees && ok; ++i) {
+        const int t = first_tree + i * tree_stride;
+        const double tb0 = now_s();
+        ok = rsfk::tree_build(c, d_points, N, D, min_children, max_children, max_depth, seed + t,
+                              nullptr, 0, h->tree);
+        h->has_tree = ok;
+        c.stats.tree_build_us += (now_s() - tb0) * 1e6;
+        if (!ok) break;
+        ok = rsfk::ann_bucket_knn(c, d_points, N, d_queries, NQ, D, K, h->tree, d_idx, d_dist);
+        if (verbose >= 2)
+            printf("tree %d: depth %d, leaves %d, leaf size %d..%d, index rows %d\n", t, h->tree.levels,
+                   h->tree.n_leaves, h->tree.min_leaf, h->tree.max_leaf, h->tree.n_records);
+    }
+    c.keep_index = keep_before;
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "query forest");
+    ok = ok && c.check_error_flag();
+    return ok;
+}
+
 bool run_sweeps(rsfk_ctx* h, const float* d_points, int N, int D, int K, int sweeps, int* d_idx,
                 float* d_dist)
 {
@@ -433,13 +463,69 @@ void pymodule_cluster_by_sample_tree(int N, int D, int MIN_TREE_CHILD, int MAX_T
     publish(c);
 }
 
-void pymodule_rsfk_knn_ann(int, int, int, int, int, int, int, int, int, int, int, float*, float*, int*,
-                           float*, float*)
+void pymodule_rsfk_knn_ann(int n_trees, int num_neighbors, int N, int NQ, int D, int MIN_TREE_CHILD,
+                           int MAX_TREE_CHILD, int MAX_DEPTH, int VERBOSE, int RANDOM_STATE,
+                           int nn_exploring_factor, float* points, float* query_points,
+                           int* knn_indices, float* knn_sqr_distances, float* log_forest)
 {
+    (void)nn_exploring_factor; // the reference's query path runs no exploration (src/rsfk.cu:98-152)
+    (void)log_forest;          // nor does it write the log (its ForestLog is a local, src/rsfk.cu:169)
     std::lock_guard<std::mutex> lock(g_mutex);
-    g_last_status = RSFK_ERR_UNSUPPORTED;
-    g_last_message = "pymodule_rsfk_knn_ann: the base/query path is not part of this library";
-    fprintf(stderr, "rsfk: %s\n", g_last_message.c_str());
+    rsfk_ctx* h = default_ctx();
+    if (!h) {
+        g_last_status = RSFK_ERR_CUDA;
+        g_last_message = "no usable CUDA device";
+        return;
+    }
+    Context& c = h->c;
+    const int K = num_neighbors;
+    if (N <= 0 || NQ <= 0 || D <= 0 || K <= 0 || n_trees < 0 || !points || !query_points || !knn_indices ||
+        !knn_sqr_distances) {
+        c.fail(RSFK_ERR_ARG, "pymodule_rsfk_knn_ann: invalid argument");
+        publish(c);
+        return;
+    }
+    if (K > rsfk::list_capacity()) {
+        c.fail(RSFK_ERR_UNSUPPORTED, "pymodule_rsfk_knn_ann: K above 256 is not supported");
+        publish(c);
+        return;
+    }
+    const size_t pts_bytes = sizeof(float) * (size_t)N * D, q_bytes = sizeof(float) * (size_t)NQ * D;
+    const size_t list_elems = (size_t)NQ * K;
+    float* d_points = (float*)c.scratch(Context::HOST_POINTS, pts_bytes);
+    float* d_queries = (float*)c.scratch(Context::HOST_QUERIES, q_bytes);
+    int* d_idx = (int*)c.scratch(Context::HOST_IDX, sizeof(int) * list_elems);
+    float* d_dist = (float*)c.scratch(Context::HOST_DIST, sizeof(float) * list_elems);
+    bool ok = d_points && d_queries && d_idx && d_dist;
+    const int dev_id = c.device;
+    auto h2d = [&](void* d, void* hp, size_t n, const char* what) {
+        if (g_copier.copy(d, hp, n, true, dev_id)) return true;
+        return c.fail(RSFK_ERR_CUDA, std::string(what) + " failed");
+    };
+    auto d2h = [&](void* d, void* hp, size_t n, const char* what) {
+        if (g_copier.copy(d, hp, n, false, dev_id)) return true;
+        return c.fail(RSFK_ERR_CUDA, std::string(what) + " failed");
+    };
+    const double t0 = now_s();
+    ok = ok && h2d(d_points, points, pts_bytes, "H2D points");
+    ok = ok && h2d(d_queries, query_points, q_bytes, "H2D query points");
+    ok = ok && h2d(d_idx, knn_indices, sizeof(int) * list_elems, "H2D indices");
+    ok = ok && h2d(d_dist, knn_sqr_distances, sizeof(float) * list_elems, "H2D distances");
+    ok = ok && rsfk::sort_rows(c, d_idx, d_dist, NQ, K);
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "H2D");
+    const double t1 = now_s();
+    if (ok && VERBOSE >= 2) printf("Allocate+copy points and KNN takes: %lf seconds\n", t1 - t0);
+    ok = ok && run_forest_ann(h, d_points, N, d_queries, NQ, D, K, n_trees, 0, 1, MIN_TREE_CHILD,
+                              MAX_TREE_CHILD, MAX_DEPTH, RANDOM_STATE, d_idx, d_dist, VERBOSE);
+    const double t2 = now_s();
+    if (ok && VERBOSE >= 1) printf("Creating RSFK forest and updating the query lists takes %lf seconds\n", t2 - t1);
+    // outputs are written only when every step succeeded
+    ok = ok && d2h(d_idx, knn_indices, sizeof(int) * list_elems, "D2H indices");
+    ok = ok && d2h(d_dist, knn_sqr_distances, sizeof(float) * list_elems, "D2H distances");
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "D2H");
+    if (ok && VERBOSE >= 2) printf("Copy KNN takes: %lf seconds\n", now_s() - t2);
+    cudaStreamSynchronize(c.stream);
+    publish(c);
 }
 
 // ------------------------------------------------------------------ part 3 --
@@ -564,6 +650,68 @@ int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, int N, int D
     t.n_leaves = n_leaves;
     t.max_leaf = max_leaf;
     rsfk::bucket_knn(ctx->c, d_points, N, D, K, t, d_idx, d_dist);
+    return ctx->c.status;
+}
+
+int rsfk_ctx_keep_index(rsfk_ctx* ctx, int on)
+{
+    if (!ctx) return RSFK_ERR_ARG;
+    ctx->c.keep_index = on != 0;
+    return RSFK_OK;
+}
+
+int rsfk_dev_route_queries(rsfk_ctx* ctx, const float* d_points, int N, int D, const float* d_queries,
+                           int NQ, int* q_start, int* q_count)
+{
+    RSFK_ENTER(ctx);
+    Context& c = ctx->c;
+    (void)N;
+    if (!ctx->has_tree || ctx->tree.records == nullptr) {
+        c.fail(RSFK_ERR_ARG, "rsfk_dev_route_queries: build a tree with rsfk_ctx_keep_index(ctx, 1) first");
+        return c.status;
+    }
+    if (NQ <= 0) return c.status;
+    const TreeResult& t = ctx->tree;
+    int* q_leaf = (int*)c.scratch(Context::QUERY_LEAF, sizeof(int) * (size_t)NQ);
+    if (!q_leaf || !rsfk::tree_route(c, d_points, D, t, d_queries, NQ, q_leaf, nullptr)) return c.status;
+    std::vector<int> leaf(NQ), ls(t.n_leaves), lc(t.n_leaves);
+    bool ok = c.check(cudaMemcpyAsync(leaf.data(), q_leaf, sizeof(int) * (size_t)NQ, cudaMemcpyDeviceToHost, c.stream), "D2H query leaves") &&
+              c.check(cudaMemcpyAsync(ls.data(), t.leaf_start, sizeof(int) * (size_t)t.n_leaves, cudaMemcpyDeviceToHost, c.stream), "D2H leaves") &&
+              c.check(cudaMemcpyAsync(lc.data(), t.leaf_count, sizeof(int) * (size_t)t.n_leaves, cudaMemcpyDeviceToHost, c.stream), "D2H leaves") &&
+              c.check(cudaStreamSynchronize(c.stream), "D2H route");
+    ok = ok && c.check_error_flag();
+    if (ok)
+        for (int q = 0; q < NQ; ++q) {
+            const int l = leaf[q];
+            q_start[q] = (l >= 0 && l < t.n_leaves) ? ls[l] : -1;
+            q_count[q] = (l >= 0 && l < t.n_leaves) ? lc[l] : 0;
+        }
+    return c.status;
+}
+
+int rsfk_dev_ann_bucket_knn(rsfk_ctx* ctx, const float* d_points, int N, const float* d_queries, int NQ,
+                            int D, int K, int* d_idx, float* d_dist)
+{
+    RSFK_ENTER(ctx);
+    if (!ctx->has_tree || ctx->tree.records == nullptr) {
+        ctx->c.fail(RSFK_ERR_ARG, "rsfk_dev_ann_bucket_knn: build a tree with rsfk_ctx_keep_index(ctx, 1) first");
+        return ctx->c.status;
+    }
+    rsfk::ann_bucket_knn(ctx->c, d_points, N, d_queries, NQ, D, K, ctx->tree, d_idx, d_dist);
+    return ctx->c.status;
+}
+
+int rsfk_dev_forest_ann(rsfk_ctx* ctx, const float* d_points, int N, const float* d_queries, int NQ, int D,
+                        int K, int n_trees, int first_tree, int tree_stride, int min_children,
+                        int max_children, int max_depth, int seed, int* d_idx, float* d_dist)
+{
+    RSFK_ENTER(ctx);
+    if (N <= 0 || NQ < 0 || D <= 0 || K <= 0 || n_trees < 0 || tree_stride < 1) {
+        ctx->c.fail(RSFK_ERR_ARG, "rsfk_dev_forest_ann: invalid argument");
+        return ctx->c.status;
+    }
+    run_forest_ann(ctx, d_points, N, d_queries, NQ, D, K, n_trees, first_tree, tree_stride, min_children,
+                   max_children, max_depth, seed, d_idx, d_dist, 0);
     return ctx->c.status;
 }
 

@@ -32,7 +32,7 @@ struct Node {
     int tbl;        // row of the replay table, or -1
     int chunk_base; // first work chunk of this node in the level's chunk list
     int level;      // depth of the node (root = 0)
-    int pad1;
+    int rec;        // row of the node in the tree index (when one is kept)
 };
 
 struct LevelCounters {
@@ -45,7 +45,7 @@ struct LevelCounters {
     int active_next; // points of the next level's open nodes
     int n_small;     // nodes handed to the in-CTA subtree kernel
     int max_level;   // deepest level any subtree reached
-    int pad0;
+    int n_recs;      // rows of the tree index handed out so far
     unsigned long long sub_active; // points projected inside subtree CTAs (all levels)
     unsigned long long sub_nodes;  // nodes split inside subtree CTAs
 };
@@ -81,6 +81,11 @@ struct TreeResult {
     int max_leaf = 0;
     int min_leaf = 0;
     int levels = 0;
+    // Tree index (kept on request): row r = {p1, p2, left ref, right ref}; the split
+    // pair is (p1, p2) (p1 < 0: no split, follow the left ref); a ref >= 0 is a row,
+    // a ref < 0 names the leaf slot -1-ref.  Row 0 is the root.
+    const int4* records = nullptr;
+    int n_records = 0;
 };
 
 struct Context {
@@ -95,8 +100,14 @@ struct Context {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
         PERM_FINAL_B, LEAF_START_B, LEAF_COUNT_B,
-        SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST, N_SLOTS
+        SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
+        RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
+        N_SLOTS
     };
+    // When set, tree_build keeps the tree index (TreeResult::records) that the
+    // query path descends.
+    bool keep_index = false;
+    bool planes_ready = false; // hyperplanes of the current tree index are materialised
     Stats stats;
     Buffer slots[N_SLOTS];
     LevelCounters* host_counters = nullptr; // pinned
@@ -174,7 +185,8 @@ struct Context {
             return false;
         if (v != 0) {
             cudaMemsetAsync(slots[ERROR_FLAG].ptr, 0, sizeof(int), stream);
-            return fail(RSFK_ERR_CUDA, "a device-side wait ran out of its limit (tensor-core bucket kernel)");
+            return fail(RSFK_ERR_CUDA, "a device-side check failed (a bounded wait of the tensor-core bucket "
+                                       "kernel ran out, or a query reached no leaf)");
         }
         return true;
     }
@@ -201,12 +213,20 @@ struct Context {
 bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_children,
                 int max_children, int max_depth, int seed, const int* d_table, int n_table,
                 TreeResult& out);
+// Leaf slot of every query row (d_q_leaf[NQ], -1 on failure) by descending the tree
+// index; d_leaf_queries[n_leaves], when given, is incremented once per query.
+bool tree_route(Context& ctx, const float* d_points, int D, const TreeResult& tree,
+                const float* d_queries, int NQ, int* d_q_leaf, int* d_leaf_queries);
 
 // rsfk_knn.cu
 int list_capacity();                      // largest supported K
 bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K);
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
                 int* d_idx, float* d_dist, bool on_aux_stream = false);
+// Query lists (rows of d_idx/d_dist, NQ x K, indices of base points) merged with the
+// bucket of base points each query is routed to.
+bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_queries, int NQ, int D,
+                    int K, const TreeResult& tree, int* d_idx, float* d_dist);
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
                    int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0);
 bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,

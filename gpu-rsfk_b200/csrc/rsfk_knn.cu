@@ -394,7 +394,7 @@ __device__ __forceinline__ float explore_dist32_vec4(const float* __restrict__ p
 
 template <int KPL, bool VEC4>
 __device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __restrict__ pts, int D,
-                                              const float* xp, int* queue, int n, int K,
+                                              const float* xp, const int* queue, int n, int K,
                                               int lane, bool& changed)
 {
     // n in [1,32] candidates at queue[0..n)
@@ -526,6 +526,95 @@ k_explore(const float* __restrict__ pts, int N, int D, int K, const int* __restr
             L.store(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
     }
     if (lane == 0 && n_eval) atomicAdd(evaluated, n_eval);
+}
+
+// ---------------------------------------------------------------------------
+// Query (ANN) bucket update (reference:
+// compute_knn_from_buckets_perwarp_coalesced_ann,
+// src/kernels/build_tree_update_parents_ann.cu:232-513): one warp per query,
+// the base points of the bucket it was routed to are taken 32 at a time and
+// merged into the query's list.  Queries are visited in leaf order
+// (q_order), so the warps of a CTA read the same bucket rows.
+// ---------------------------------------------------------------------------
+
+// Exclusive prefix sum of counts[n] in place (one CTA); counts[n] = total.
+__global__ void __launch_bounds__(1024)
+k_leaf_offsets(int* __restrict__ counts, int n)
+{
+    __shared__ int sWarp[32];
+    const int per = (n + blockDim.x - 1) / blockDim.x;
+    const int lo = min(n, (int)threadIdx.x * per), hi = min(n, lo + per);
+    int sum = 0;
+    for (int i = lo; i < hi; ++i) sum += counts[i];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = sum;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        const int t = __shfl_up_sync(RSFK_FULL, incl, s);
+        if (lane >= s) incl += t;
+    }
+    if (lane == 31) sWarp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = sWarp[lane], wi = w;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+            const int t = __shfl_up_sync(RSFK_FULL, wi, s);
+            if (lane >= s) wi += t;
+        }
+        sWarp[lane] = wi - w;
+    }
+    __syncthreads();
+    int run = sWarp[warp] + incl - sum;
+    for (int i = lo; i < hi; ++i) {
+        const int c = counts[i];
+        counts[i] = run;
+        run += c;
+    }
+    if (threadIdx.x == blockDim.x - 1) counts[n] = run;
+}
+
+// q_order: queries grouped by leaf (any order inside a leaf: every query is
+// independent of the others).  cursor = the offsets of k_leaf_offsets.
+__global__ void k_place_queries(const int* __restrict__ q_leaf, int NQ, int* __restrict__ cursor,
+                                int* __restrict__ q_order)
+{
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < NQ; q += gridDim.x * blockDim.x) {
+        const int leaf = q_leaf[q];
+        if (leaf < 0) continue;
+        q_order[atomicAdd(&cursor[leaf], 1)] = q;
+    }
+}
+
+template <int KPL, bool VEC4>
+__global__ void __launch_bounds__(KNN_THREADS, 2)
+k_ann_bucket(const float* __restrict__ pts, const float* __restrict__ queries, int D, int K,
+             const int* __restrict__ perm, const int* __restrict__ leaf_start,
+             const int* __restrict__ leaf_count, const int* __restrict__ q_leaf,
+             const int* __restrict__ q_order, const int* __restrict__ n_order_ptr,
+             int* __restrict__ knn_idx, float* __restrict__ knn_dist)
+{
+    extern __shared__ float4 smem4[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, cta_warps = blockDim.x >> 5;
+    float* xq = reinterpret_cast<float*>(smem4) + (size_t)warp * D;
+    const int warp0 = blockIdx.x * cta_warps + warp;
+    const int n_warps = gridDim.x * cta_warps;
+    const int n_order = *n_order_ptr; // queries that reached a leaf (all, unless the error flag is up)
+    for (int o = warp0; o < n_order; o += n_warps) {
+        const int q = q_order[o];
+        const int leaf = q_leaf[q];
+        const int* ids = perm + leaf_start[leaf];
+        const int m = leaf_count[leaf];
+        __syncwarp();
+        for (int k = lane; k < D; k += 32) xq[k] = __ldg(queries + (size_t)q * D + k);
+        WarpList<KPL> L;
+        L.load(knn_idx + (size_t)q * K, knn_dist + (size_t)q * K, K, lane);
+        __syncwarp();
+        bool changed = false;
+        for (int b0 = 0; b0 < m; b0 += 32)
+            explore_flush<KPL, VEC4>(L, pts, D, xq, ids + b0, min(32, m - b0), K, lane, changed);
+        if (changed) L.store(knn_idx + (size_t)q * K, knn_dist + (size_t)q * K, K, lane);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -691,6 +780,47 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
     });
     count_launches(1);
     return ctx.check(cudaGetLastError(), "explore launch");
+}
+
+bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_queries, int NQ, int D,
+                    int K, const TreeResult& tree, int* d_idx, float* d_dist)
+{
+    (void)N;
+    if (!check_k(ctx, K)) return false;
+    if (NQ <= 0) return true;
+    if (tree.n_leaves < 1) return ctx.fail(RSFK_ERR_ARG, "ann_bucket_knn: no tree");
+    cudaStream_t st = ctx.stream;
+    int* q_leaf = (int*)ctx.scratch(Context::QUERY_LEAF, sizeof(int) * (size_t)NQ);
+    int* q_order = (int*)ctx.scratch(Context::QUERY_ORDER, sizeof(int) * (size_t)NQ);
+    int* leaf_queries = (int*)ctx.scratch(Context::LEAF_QUERIES, sizeof(int) * (size_t)(tree.n_leaves + 1));
+    if (ctx.status != RSFK_OK) return false;
+    if (!ctx.check(cudaMemsetAsync(leaf_queries, 0, sizeof(int) * (size_t)(tree.n_leaves + 1), st),
+                   "clear leaf counts"))
+        return false;
+    if (!tree_route(ctx, d_points, D, tree, d_queries, NQ, q_leaf, leaf_queries)) return false;
+    k_leaf_offsets<<<1, 1024, 0, st>>>(leaf_queries, tree.n_leaves);
+    int grid = (NQ + 255) / 256;
+    if (grid > ctx.sm_count * 16) grid = ctx.sm_count * 16;
+    k_place_queries<<<grid, 256, 0, st>>>(q_leaf, NQ, leaf_queries, q_order);
+    count_launches(2);
+    // leaf_queries[n_leaves] = number of queries that reached a leaf = entries of q_order
+    const size_t smem = sizeof(float) * (size_t)KNN_WARPS * D;
+    if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "ann_bucket_knn: D too large");
+    long long blocks = ((long long)NQ + KNN_WARPS - 1) / KNN_WARPS;
+    if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
+    const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
+    RSFK_DISPATCH_KPL(K, {
+        auto kern = vec4 ? k_ann_bucket<KPL, true> : k_ann_bucket<KPL, false>;
+        if (smem > 48 * 1024 &&
+            !ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                       "query bucket smem attribute"))
+            return false;
+        kern<<<(int)blocks, KNN_THREADS, smem, st>>>(d_points, d_queries, D, K, tree.perm, tree.leaf_start,
+                                                     tree.leaf_count, q_leaf, q_order,
+                                                     leaf_queries + tree.n_leaves, d_idx, d_dist);
+    });
+    count_launches(1);
+    return ctx.check(cudaGetLastError(), "query bucket launch");
 }
 
 bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,

@@ -189,7 +189,8 @@ __global__ void __launch_bounds__(TREE_THREADS)
 k_project_wide(const float* __restrict__ pts, int D, const int* __restrict__ perm,
                const Node* __restrict__ nodes, const int* __restrict__ chunk_node,
                unsigned* __restrict__ side_bits, int* __restrict__ chunk_left,
-               const int4* __restrict__ table, int n_table, int seed, int level, int vec4)
+               const int4* __restrict__ table, int n_table, int seed, int level, int vec4,
+               int4* __restrict__ records)
 {
     extern __shared__ float4 smem4[];
     float* sN = reinterpret_cast<float*>(smem4);
@@ -207,6 +208,10 @@ k_project_wide(const float* __restrict__ pts, int D, const int* __restrict__ per
         sPair[0] = p1;
         sPair[1] = p2;
         sLeft = 0;
+        if (records != nullptr && off == 0) { // the node's first chunk files the split pair
+            records[nd.rec].x = p1;
+            records[nd.rec].y = p2;
+        }
     }
     __syncthreads();
     const float c = load_hyperplane(pts, D, sPair[0], sPair[1], level == 0, sN, &sC);
@@ -240,7 +245,8 @@ __global__ void __launch_bounds__(TREE_THREADS)
 k_project_small(const float* __restrict__ pts, int D, const int* __restrict__ perm,
                 const Node* __restrict__ nodes, const int* __restrict__ chunk_node,
                 unsigned* __restrict__ side_bits, int* __restrict__ chunk_left,
-                const int4* __restrict__ table, int n_table, int seed, int level)
+                const int4* __restrict__ table, int n_table, int seed, int level,
+                int4* __restrict__ records)
 {
     __shared__ float sN[VL];
     __shared__ float sC;
@@ -257,6 +263,10 @@ k_project_small(const float* __restrict__ pts, int D, const int* __restrict__ pe
         sPair[0] = p1;
         sPair[1] = p2;
         sLeft = 0;
+        if (records != nullptr && off == 0) { // the node's first chunk files the split pair
+            records[nd.rec].x = p1;
+            records[nd.rec].y = p2;
+        }
     }
     __syncthreads();
     const float c = load_hyperplane(pts, D, sPair[0], sPair[1], level == 0, sN, &sC);
@@ -292,8 +302,8 @@ k_project_small(const float* __restrict__ pts, int D, const int* __restrict__ pe
 // ---------------------------------------------------------------------------
 // decide: one warp per node.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void emit_leaf(int start, int count, int* leaf_start, int* leaf_count,
-                                          int leaf_cap, LevelCounters* cnt)
+__device__ __forceinline__ int emit_leaf(int start, int count, int* leaf_start, int* leaf_count,
+                                         int leaf_cap, LevelCounters* cnt)
 {
     int slot = atomicAdd(&cnt->n_leaves, 1);
     if (slot < leaf_cap) {
@@ -304,6 +314,27 @@ __device__ __forceinline__ void emit_leaf(int start, int count, int* leaf_start,
     }
     atomicMax(&cnt->max_leaf, count);
     atomicMin(&cnt->min_leaf, count);
+    return slot;
+}
+
+// A new row of the tree index (lane 0 only), or 0 when no index is kept.
+__device__ __forceinline__ int new_record(int4* records, int rec_cap, LevelCounters* cnt)
+{
+    if (records == nullptr) return 0;
+    const int r = atomicAdd(&cnt->n_recs, 1);
+    if (r >= rec_cap) {
+        cnt->error = RSFK_ERR_OVERFLOW;
+        return 0;
+    }
+    return r;
+}
+
+// Child refs of a row: a node with one child sends both sides to it.
+__device__ __forceinline__ void file_refs(int4* records, int rec, int n_children, const int* ref)
+{
+    if (records == nullptr) return;
+    records[rec].z = ref[0];
+    records[rec].w = n_children == 2 ? ref[1] : ref[0];
 }
 
 // Children of a node whose stable partition put n_left points on the left.
@@ -363,7 +394,7 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
          NodeSplit* __restrict__ split, int* __restrict__ leaf_start, int* __restrict__ leaf_count,
          int leaf_cap, Node* __restrict__ small_nodes, int small_cap, int small_limit, int child_level,
          LevelCounters* __restrict__ cnt, const int4* __restrict__ table, int n_table,
-         int min_children, int max_children)
+         int min_children, int max_children, int4* __restrict__ records, int rec_cap)
 {
     const int lane = threadIdx.x & 31;
     const int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -391,12 +422,14 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
     // a child's points are final (copied to perm_final by the scatter) when it
     // is a leaf or small enough to be finished inside one CTA
     int flags = 0;
+    int ref[2] = {0, 0}; // lane 0: where each child went (row, or -1-leaf slot)
     for (int k = 0; k < ch.n; ++k) {
         const bool small = !ch.leaf[k] && ch.count[k] <= small_limit;
         const bool fin = ch.leaf[k] || small;
         if (fin) flags |= (ch.n == 2) ? (1 << k) : 3;
         if (ch.leaf[k]) {
-            if (lane == 0) emit_leaf(ch.start[k], ch.count[k], leaf_start, leaf_count, leaf_cap, cnt);
+            if (lane == 0)
+                ref[k] = -1 - emit_leaf(ch.start[k], ch.count[k], leaf_start, leaf_count, leaf_cap, cnt);
             continue;
         }
         Node o;
@@ -405,7 +438,8 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
         o.tbl = child_table_row(table, n_table, nd.tbl, ch.side[k]);
         o.chunk_base = 0;
         o.level = child_level;
-        o.pad1 = 0;
+        o.rec = 0;
+        if (lane == 0) ref[k] = o.rec = new_record(records, rec_cap, cnt);
         if (small) {
             if (lane == 0) {
                 const int slot = atomicAdd(&cnt->n_small, 1);
@@ -436,6 +470,7 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
     if (lane == 0) {
         split[node].n_left = nL;
         split[node].flags = flags;
+        file_refs(records, nd.rec, ch.n, ref);
     }
 }
 
@@ -520,6 +555,7 @@ struct SubNode {
     int start, count;   // relative to the CTA's segment
     int pstart, pcount; // relative
     int tbl;
+    int rec;            // row of the tree index
 };
 
 __global__ void __launch_bounds__(TREE_THREADS, 4)
@@ -527,7 +563,7 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
           const Node* __restrict__ small_nodes, int* __restrict__ leaf_start,
           int* __restrict__ leaf_count, int leaf_cap, LevelCounters* __restrict__ cnt,
           const int4* __restrict__ table, int n_table, int seed, int min_children, int max_children,
-          int max_depth, int vec4)
+          int max_depth, int vec4, int4* __restrict__ records, int rec_cap)
 {
     extern __shared__ float4 smem4[]; // per-warp normal vectors: n_warps * D floats
     float* smem = reinterpret_cast<float*>(smem4);
@@ -549,6 +585,7 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
         r.start = 0; r.count = root.count;
         r.pstart = root.pstart - root.start; r.pcount = root.pcount;
         r.tbl = root.tbl;
+        r.rec = root.rec;
         sOpen[0][0] = r;
     }
     int n_open = 1, cur = 0, level = root.level;
@@ -564,10 +601,14 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
                 if (lane == 0) {
                     const int piece = max(1, max_children);
                     const int q = (nd.count + piece - 1) / piece;
+                    int first = 0;
                     for (int j = 0; j < q; ++j) {
                         int a = (int)((long long)nd.count * j / q), b = (int)((long long)nd.count * (j + 1) / q);
-                        emit_leaf(root.start + nd.start + a, b - a, leaf_start, leaf_count, leaf_cap, cnt);
+                        const int slot = emit_leaf(root.start + nd.start + a, b - a, leaf_start, leaf_count, leaf_cap, cnt);
+                        if (j == 0) first = slot;
                     }
+                    if (records != nullptr) // no split: queries go to the first piece
+                        records[nd.rec] = make_int4(-1, -1, -1 - first, -1 - first);
                 }
             }
             break;
@@ -612,6 +653,10 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
                 sample_positions(seed, level, root.start + nd.pstart, nd.pcount, r1, r2);
                 p1 = sIds[cur][nd.pstart + r1];
                 p2 = sIds[cur][nd.pstart + r2];
+            }
+            if (records != nullptr && off == 0 && lane == 0) {
+                records[nd.rec].x = p1;
+                records[nd.rec].y = p2;
             }
             const float* x1 = pts + (size_t)p1 * D;
             const float* x2 = pts + (size_t)p2 * D;
@@ -668,12 +713,13 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
             }
             __syncwarp();
             const Children ch = decide_children(nd.start, nd.count, nL, min_children, max_children);
+            int ref[2] = {0, 0};
             for (int k = 0; k < ch.n; ++k) {
                 if (ch.leaf[k]) {
                     for (int q = lane; q < ch.count[k]; q += 32)
                         seg[ch.start[k] + q] = sIds[nxt][ch.start[k] + q];
                     if (lane == 0)
-                        emit_leaf(root.start + ch.start[k], ch.count[k], leaf_start, leaf_count, leaf_cap, cnt);
+                        ref[k] = -1 - emit_leaf(root.start + ch.start[k], ch.count[k], leaf_start, leaf_count, leaf_cap, cnt);
                 } else if (lane == 0) {
                     const int slot = atomicAdd(&sCount[0], 1);
                     if (slot < SUB_NODES) {
@@ -681,12 +727,14 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
                         o.start = ch.start[k];   o.count = ch.count[k];
                         o.pstart = ch.pstart[k]; o.pcount = ch.pcount[k];
                         o.tbl = child_table_row(table, n_table, nd.tbl, ch.side[k]);
+                        ref[k] = o.rec = new_record(records, rec_cap, cnt);
                         sOpen[nxt][slot] = o;
                     } else {
                         cnt->error = RSFK_ERR_OVERFLOW;
                     }
                 }
             }
+            if (lane == 0) file_refs(records, nd.rec, ch.n, ref);
         }
         __syncthreads();
         n_open = min(sCount[0], SUB_NODES);
@@ -706,7 +754,7 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
 __global__ void k_force_leaves(const Node* __restrict__ nodes, int n_nodes, const int* __restrict__ perm,
                                int* __restrict__ perm_final, int* __restrict__ leaf_start,
                                int* __restrict__ leaf_count, int leaf_cap, LevelCounters* cnt,
-                               int max_children)
+                               int max_children, int4* __restrict__ records)
 {
     const int node = blockIdx.x;
     if (node >= n_nodes) return;
@@ -715,10 +763,14 @@ __global__ void k_force_leaves(const Node* __restrict__ nodes, int n_nodes, cons
     if (threadIdx.x == 0) {
         const int piece = max(1, max_children);
         const int q = (nd.count + piece - 1) / piece;
+        int first = 0;
         for (int i = 0; i < q; ++i) {
             int a = (int)((long long)nd.count * i / q), b = (int)((long long)nd.count * (i + 1) / q);
-            emit_leaf(nd.start + a, b - a, leaf_start, leaf_count, leaf_cap, cnt);
+            const int slot = emit_leaf(nd.start + a, b - a, leaf_start, leaf_count, leaf_cap, cnt);
+            if (i == 0) first = slot;
         }
+        if (records != nullptr) // no split: queries go to the first piece
+            records[nd.rec] = make_int4(-1, -1, -1 - first, -1 - first);
     }
 }
 
@@ -735,8 +787,9 @@ __global__ void k_tree_init(Node* nodes, int* chunk_node, int n_chunks, int N, i
         Node r;
         r.start = 0; r.count = N; r.pstart = 0; r.pcount = N;
         r.tbl = has_table ? 0 : -1;
-        r.chunk_base = 0; r.level = 0; r.pad1 = 0;
+        r.chunk_base = 0; r.level = 0; r.rec = 0;
         nodes[0] = r;
+        cnt->n_recs = 1; // row 0 is the root
         cnt->n_nodes_next = 0; cnt->n_chunks_next = 0; cnt->n_leaves = 0;
         cnt->max_leaf = 0; cnt->min_leaf = 0x7fffffff; cnt->error = 0; cnt->active_next = 0;
         cnt->n_small = 0; cnt->max_level = 0; cnt->sub_active = 0; cnt->sub_nodes = 0;
@@ -744,10 +797,12 @@ __global__ void k_tree_init(Node* nodes, int* chunk_node, int n_chunks, int N, i
     for (int c = t; c < n_chunks; c += gridDim.x * blockDim.x) chunk_node[c] = 0;
 }
 
-__global__ void k_single_leaf(int* leaf_start, int* leaf_count, int N, LevelCounters* cnt)
+__global__ void k_single_leaf(int* leaf_start, int* leaf_count, int N, LevelCounters* cnt, int4* records)
 {
     leaf_start[0] = 0;
     leaf_count[0] = N;
+    cnt->n_recs = 1;
+    if (records != nullptr) records[0] = make_int4(-1, -1, -1, -1); // every query: leaf slot 0
     cnt->n_leaves = 1; cnt->max_leaf = N; cnt->min_leaf = N; cnt->error = 0;
     cnt->n_nodes_next = 0; cnt->n_chunks_next = 0;
     cnt->n_small = 0; cnt->max_level = 0; cnt->sub_active = 0; cnt->sub_nodes = 0; cnt->active_next = 0;
@@ -756,13 +811,13 @@ __global__ void k_single_leaf(int* leaf_start, int* leaf_count, int N, LevelCoun
 // ---------------------------------------------------------------------------
 static void launch_project(Context& ctx, const float* pts, int D, const int* perm, const Node* nodes,
                            const int* chunk_node, int n_chunks, unsigned* side_bits, int* chunk_left,
-                           const int4* table, int n_table, int seed, int level)
+                           const int4* table, int n_table, int seed, int level, int4* records)
 {
     cudaStream_t st = ctx.stream;
 #define RSFK_SMALL(VL)                                                                              \
     k_project_small<VL><<<n_chunks, TREE_THREADS, 0, st>>>(pts, D, perm, nodes, chunk_node,         \
                                                            side_bits, chunk_left, table, n_table,   \
-                                                           seed, level)
+                                                           seed, level, records)
     if (D <= 2) RSFK_SMALL(2);
     else if (D <= 4) RSFK_SMALL(4);
     else if (D <= 8) RSFK_SMALL(8);
@@ -770,7 +825,7 @@ static void launch_project(Context& ctx, const float* pts, int D, const int* per
     else
         k_project_wide<<<n_chunks, TREE_THREADS, (size_t)D * sizeof(float), st>>>(
             pts, D, perm, nodes, chunk_node, side_bits, chunk_left, table, n_table, seed, level,
-            (D % 4 == 0 && ((uintptr_t)pts & 15) == 0) ? 1 : 0);
+            (D % 4 == 0 && ((uintptr_t)pts & 15) == 0) ? 1 : 0, records);
 #undef RSFK_SMALL
     count_launches(1);
 }
@@ -820,6 +875,11 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     int* leaf_start = (int*)ctx.scratch(ctx.result_buf ? Context::LEAF_START_B : Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
     int* leaf_count = (int*)ctx.scratch(ctx.result_buf ? Context::LEAF_COUNT_B : Context::LEAF_COUNT, sizeof(int) * (size_t)leaf_cap);
     LevelCounters* cnt = (LevelCounters*)ctx.scratch(Context::COUNTERS, sizeof(LevelCounters));
+    // tree index: a row per node that is split; with no side ever dissolving that is one
+    // row less than there are leaves, dissolving sides add chain rows
+    const int rec_cap = ctx.keep_index ? 4 * leaf_cap + 64 : 0;
+    int4* records = ctx.keep_index ? (int4*)ctx.scratch(Context::RECORDS, sizeof(int4) * (size_t)rec_cap) : nullptr;
+    ctx.planes_ready = false;
     if (ctx.status != RSFK_OK) return false;
     if (!ctx.host_counters &&
         !ctx.check(cudaMallocHost((void**)&ctx.host_counters, sizeof(LevelCounters)), "cudaMallocHost"))
@@ -840,7 +900,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     int cur = 0;
     if (N == 1) {
         k_iota<<<1, 32, 0, st>>>(perm_final, 1);
-        k_single_leaf<<<1, 1, 0, st>>>(leaf_start, leaf_count, N, cnt);
+        k_single_leaf<<<1, 1, 0, st>>>(leaf_start, leaf_count, N, cnt, records);
         count_launches(2);
         n_nodes = 0;
     } else {
@@ -864,13 +924,13 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
         }
         cudaEventRecord(ctx.level_ev[2 * timed_levels], st);
         launch_project(ctx, d_points, D, perm[cur], nodes[cur], chunk_node[cur], n_chunks, side_bits,
-                       chunk_left, table, n_table, seed, level);
+                       chunk_left, table, n_table, seed, level, records);
         cudaEventRecord(ctx.level_ev[2 * timed_levels + 1], st);
         timed_levels++;
         k_decide<<<(n_nodes * 32 + TREE_THREADS - 1) / TREE_THREADS, TREE_THREADS, 0, st>>>(
             nodes[cur], n_nodes, chunk_left, nodes[cur ^ 1], node_cap, chunk_node[cur ^ 1], chunk_cap,
             split, leaf_start, leaf_count, leaf_cap, small_nodes, small_cap, small_limit, depth, cnt, table,
-            n_table, min_children, max_children);
+            n_table, min_children, max_children, records, rec_cap);
         k_scatter<<<n_chunks, TREE_THREADS, 0, st>>>(perm[cur], perm[cur ^ 1], perm_final, nodes[cur],
                                                      chunk_node[cur], side_bits, chunk_left, split, cnt,
                                                      ctx.mail, depth);
@@ -911,7 +971,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     }
     if (n_nodes > 0) {
         k_force_leaves<<<n_nodes, 256, 0, st>>>(nodes[cur], n_nodes, perm[cur], perm_final, leaf_start,
-                                                leaf_count, leaf_cap, cnt, max_children);
+                                                leaf_count, leaf_cap, cnt, max_children, records);
         count_launches(1);
     }
     const int n_small = (N > 1 && levels > 0) ? n_small_seen : 0;
@@ -930,7 +990,8 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
         k_subtree<<<n_small, sub_threads, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
                                                            leaf_count, leaf_cap, cnt, table, n_table, seed,
                                                            min_children, max_children, max_depth,
-                                                           (D % 4 == 0 && ((uintptr_t)d_points & 15) == 0) ? 1 : 0);
+                                                           (D % 4 == 0 && ((uintptr_t)d_points & 15) == 0) ? 1 : 0,
+                                                           records, rec_cap);
         cudaEventRecord(ctx.sub_ev[1], st);
         count_launches(1);
     }
@@ -964,7 +1025,136 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     out.max_leaf = ctx.host_counters->max_leaf;
     out.min_leaf = ctx.host_counters->min_leaf;
     out.levels = N == 1 ? 0 : levels + 1;
+    out.records = records;
+    out.n_records = records ? ctx.host_counters->n_recs : 0;
     return true;
+}
+
+// ---------------------------------------------------------------------------
+// Query routing over the tree index (reference: the query descent of
+// RSFK::knn_gpu_rsfk_forest_ann_tree, src/rsfk.cu:270-347, which runs
+// build_tree_check_points_side over the query array level by level and
+// build_tree_update_parents_ann.cu:150-160 to step to the child, or to its
+// sibling when the side a query falls on holds no node).
+// ---------------------------------------------------------------------------
+
+// Hyperplane of every row: normal n = x[p1]-x[p2] and offset c, in the
+// arithmetic of load_hyperplane (row 0, the root, sums serially).
+__global__ void __launch_bounds__(TREE_THREADS)
+k_planes(const float* __restrict__ pts, int D, const int4* __restrict__ records, int n_recs,
+         float* __restrict__ normals, float* __restrict__ offsets)
+{
+    const int lane = threadIdx.x & 31;
+    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (r >= n_recs) return;
+    const int4 rec = records[r];
+    if (rec.x < 0 || rec.y < 0) {
+        if (lane == 0) offsets[r] = 0.0f;
+        return;
+    }
+    const float* x1 = pts + (size_t)rec.x * D;
+    const float* x2 = pts + (size_t)rec.y * D;
+    float* nrm = normals + (size_t)r * D;
+    float c = 0.0f;
+    if (r == 0) {
+        for (int k = lane; k < D; k += 32) nrm[k] = __fsub_rn(__ldg(x1 + k), __ldg(x2 + k));
+        if (lane == 0)
+            for (int k = 0; k < D; ++k) {
+                const float a = __ldg(x1 + k), b = __ldg(x2 + k);
+                c = __fadd_rn(c, __fmul_rn(__fmul_rn(__fsub_rn(a, b), __fadd_rn(a, b)), 0.5f));
+            }
+    } else {
+        for (int k = lane; k < D; k += 32) {
+            const float a = __ldg(x1 + k), b = __ldg(x2 + k);
+            const float nk = __fsub_rn(a, b);
+            nrm[k] = nk;
+            c = __fadd_rn(c, __fmul_rn(__fmul_rn(nk, __fadd_rn(a, b)), 0.5f));
+        }
+        c = butterfly_sum(c);
+    }
+    if (lane == 0) offsets[r] = c;
+}
+
+// One warp per query: descend from row 0 to a leaf slot.  The projection is the
+// reference's warp sum (term k on lane k%32, fused multiply-add, xor butterfly),
+// the comparison `n.x < c` sends the query right.  The descent is bounded by
+// max_steps; a query that does not reach a leaf raises the error flag.
+constexpr int ROUTE_WARPS = 8;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+k_route(const float* __restrict__ queries, int NQ, int D, const int4* __restrict__ records, int n_recs,
+        const float* __restrict__ normals, const float* __restrict__ offsets, int max_steps,
+        int n_leaves, int* __restrict__ q_leaf, int* __restrict__ leaf_queries, int* __restrict__ error_flag)
+{
+    extern __shared__ float4 smem4[];
+    float* xq = reinterpret_cast<float*>(smem4) + (size_t)(threadIdx.x >> 5) * D;
+    const int lane = threadIdx.x & 31;
+    const int warp0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    for (int q = warp0; q < NQ; q += n_warps) {
+        __syncwarp();
+        for (int k = lane; k < D; k += 32) xq[k] = __ldg(queries + (size_t)q * D + k);
+        __syncwarp();
+        int cur = 0, leaf = -1;
+        for (int step = 0; step < max_steps; ++step) {
+            const int4 rec = records[cur];
+            int ref = rec.z;
+            if (rec.x >= 0) {
+                const float* nrm = normals + (size_t)cur * D;
+                float acc = 0.0f;
+                for (int k = lane; k < D; k += 32) acc = __fmaf_rn(__ldg(nrm + k), xq[k], acc);
+                if (butterfly_sum(acc) < offsets[cur]) ref = rec.w;
+            }
+            if (ref < 0) {
+                leaf = -1 - ref;
+                break;
+            }
+            if (ref >= n_recs) break;
+            cur = ref;
+        }
+        if (lane == 0) {
+            if (leaf < 0 || leaf >= n_leaves) {
+                q_leaf[q] = -1;
+                atomicExch(error_flag, RSFK_ERR_OVERFLOW);
+            } else {
+                q_leaf[q] = leaf;
+                if (leaf_queries != nullptr) atomicAdd(&leaf_queries[leaf], 1);
+            }
+        }
+    }
+}
+
+bool tree_route(Context& ctx, const float* d_points, int D, const TreeResult& tree,
+                const float* d_queries, int NQ, int* d_q_leaf, int* d_leaf_queries)
+{
+    if (tree.records == nullptr || tree.n_records < 1)
+        return ctx.fail(RSFK_ERR_ARG, "tree_route: the tree was built without its index");
+    if (NQ <= 0) return true;
+    cudaStream_t st = ctx.stream;
+    const int n_recs = tree.n_records;
+    float* normals = (float*)ctx.scratch(Context::PLANE_NORMALS, sizeof(float) * (size_t)n_recs * D);
+    float* offsets = (float*)ctx.scratch(Context::PLANE_OFFSETS, sizeof(float) * (size_t)n_recs);
+    int* error_flag = ctx.error_flag();
+    if (ctx.status != RSFK_OK || !error_flag) return false;
+    if (!ctx.planes_ready) {
+        k_planes<<<(n_recs * 32 + TREE_THREADS - 1) / TREE_THREADS, TREE_THREADS, 0, st>>>(
+            d_points, D, tree.records, n_recs, normals, offsets);
+        count_launches(1);
+        ctx.planes_ready = true;
+    }
+    const size_t smem = sizeof(float) * (size_t)ROUTE_WARPS * D;
+    if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "tree_route: D too large");
+    if (smem > 48 * 1024 &&
+        !ctx.check(cudaFuncSetAttribute(k_route, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                   "route smem attribute"))
+        return false;
+    long long blocks = ((long long)NQ + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
+    k_route<<<(int)blocks, ROUTE_WARPS * 32, smem, st>>>(d_queries, NQ, D, tree.records, n_recs, normals,
+                                                          offsets, tree.levels + 8, tree.n_leaves, d_q_leaf,
+                                                          d_leaf_queries, error_flag);
+    count_launches(1);
+    return ctx.check(cudaGetLastError(), "route launch");
 }
 
 } // namespace rsfk

@@ -155,9 +155,73 @@ class RSFK(object):
         self._last_search_time = time.time() - t_init
         return knn_indices, knn_squared_dist
 
-    def find_nearest_neighbors_ann(self, *args, **kwargs):
-        """The base/query search of the reference is not part of this library."""
-        raise Exception('find_nearest_neighbors_ann is not available in the sm_100a build')
+    def _ann_call(self, n_trees, K, min_children, max_children, max_depth, verbose, sweeps,
+                  points, query_points, indices, sq_dist):
+        N, D = points.shape
+        log = np.zeros(n_trees * 16 + 2, np.float32)
+        self._lib.pymodule_rsfk_knn_ann(n_trees, K, N, query_points.shape[0], D, min_children,
+                                        max_children, max_depth, verbose, self.random_state, sweeps,
+                                        points, query_points, indices, sq_dist, log)
+        _lib.check_last("pymodule_rsfk_knn_ann")
+
+    def find_nearest_neighbors_ann(self, points, query_points, num_nearest_neighbors,
+                                   n_trees=-1, max_tree_depth=5000,
+                                   verbose=0, min_tree_children=-1,
+                                   max_tree_children=-1,
+                                   ensure_valid_indices=True,
+                                   add_bit_random_motion=False,
+                                   random_motion_force=1.0,
+                                   nn_exploring_factor=-1):
+        """Approximate K nearest ``points`` (base set, ``[n_points, n_dimensions]``)
+        of every row of ``query_points`` (``[n_queries, n_dimensions]``).
+
+        Every tree is built over the base points; a query descends it to a leaf
+        and is compared with the base points of that leaf.  Returns
+        ``(knn_indices int32 [NQ, K], knn_squared_dist float32 [NQ, K])``,
+        indices into ``points``, rows ordered by distance.  Parameters and
+        defaults as ``find_nearest_neighbors``; the exploration sweeps do not
+        apply to this search (``nn_exploring_factor`` is accepted and passed on,
+        as in the reference, but has no effect).
+        """
+        points = np.require(points, np.float32, ['CONTIGUOUS', 'ALIGNED'])
+        query_points = np.require(query_points, np.float32, ['CONTIGUOUS', 'ALIGNED'])
+        if points.ndim != 2 or query_points.ndim != 2 or points.shape[1] != query_points.shape[1]:
+            raise Exception('points and query_points must be 2-D arrays with the same number of dimensions')
+        max_tree_depth, verbose = int(max_tree_depth), int(verbose)
+        max_tree_children, n_trees = int(max_tree_children), int(n_trees)
+        N, D = points.shape
+        NQ = query_points.shape[0]
+        K = int(num_nearest_neighbors)
+
+        if nn_exploring_factor == -1:
+            nn_exploring_factor = 1 if K <= 32 else 0
+        if min_tree_children == -1:
+            min_tree_children = K + 1
+        if max_tree_children == -1 and min_tree_children >= 0:
+            max_tree_children = 2 * min_tree_children
+        _check_children(min_tree_children, max_tree_children)
+
+        if n_trees == -1:
+            mean_bucket = (min_tree_children + max_tree_children) / 2
+            n_trees = int(max(math.ceil((N * D) / (mean_bucket * 24913)), 50))
+            if verbose > 0:
+                print("Automatically setting n_trees to {}".format(n_trees))
+
+        if add_bit_random_motion:
+            random_motion(points, random_motion_force)
+            random_motion(query_points, random_motion_force)
+
+        knn_indices = np.full((NQ, K), -1, np.int32)
+        knn_squared_dist = np.full((NQ, K), np.inf, np.float32)
+
+        t_init = time.time()
+        self._ann_call(n_trees, K, int(min_tree_children), max_tree_children, max_tree_depth, verbose,
+                       int(nn_exploring_factor), points, query_points, knn_indices, knn_squared_dist)
+        if ensure_valid_indices and min_tree_children < K + 1:
+            self._ann_call(1, K, K + 1, 3 * (K + 1), max_tree_depth, verbose,
+                           int(nn_exploring_factor), points, query_points, knn_indices, knn_squared_dist)
+        self._last_search_time = time.time() - t_init
+        return knn_indices, knn_squared_dist
 
     # -------------------------------------------------------------- cluster
     def cluster_by_sample_tree(self, points, max_tree_depth=5000,

@@ -45,7 +45,12 @@ def load():
         np.ctypeslib.ndpointer(np.float32, ndim=2, flags="ALIGNED, CONTIGUOUS"),
         ctypes.POINTER(_c_int_p), ctypes.POINTER(_c_int_p), _c_int_p, _c_int_p]
     L.pymodule_rsfk_knn_ann.restype = None
-    L.pymodule_rsfk_knn_ann.argtypes = [i] * 11 + [vp] * 5
+    L.pymodule_rsfk_knn_ann.argtypes = [i] * 11 + [
+        np.ctypeslib.ndpointer(np.float32, ndim=2, flags="ALIGNED, CONTIGUOUS"),
+        np.ctypeslib.ndpointer(np.float32, ndim=2, flags="ALIGNED, CONTIGUOUS"),
+        np.ctypeslib.ndpointer(np.int32, ndim=2, flags="ALIGNED, CONTIGUOUS, WRITEABLE"),
+        np.ctypeslib.ndpointer(np.float32, ndim=2, flags="ALIGNED, CONTIGUOUS, WRITEABLE"),
+        np.ctypeslib.ndpointer(np.float32, ndim=1, flags="ALIGNED, CONTIGUOUS, WRITEABLE")]
 
     L.rsfk_last_status.restype = i
     L.rsfk_last_status.argtypes = []
@@ -86,6 +91,14 @@ def load():
     L.rsfk_dev_explore.argtypes = [vp, vp, i, i, i, vp, vp, vp, i, i, i]
     L.rsfk_dev_merge_lists.restype = i
     L.rsfk_dev_merge_lists.argtypes = [vp, ll, i, i, vp, vp, vp, vp]
+    L.rsfk_ctx_keep_index.restype = i
+    L.rsfk_ctx_keep_index.argtypes = [vp, i]
+    L.rsfk_dev_route_queries.restype = i
+    L.rsfk_dev_route_queries.argtypes = [vp, vp, i, i, vp, i, vp, vp]
+    L.rsfk_dev_ann_bucket_knn.restype = i
+    L.rsfk_dev_ann_bucket_knn.argtypes = [vp, vp, i, vp, i, i, i, vp, vp]
+    L.rsfk_dev_forest_ann.restype = i
+    L.rsfk_dev_forest_ann.argtypes = [vp, vp, i, vp, i, i, i, i, i, i, i, i, i, i, vp, vp]
     L.rsfk_explore_sweep_static.restype = i
     L.rsfk_explore_sweep_static.argtypes = [vp, i, i, i, vp, vp, vp]
     _lib = L

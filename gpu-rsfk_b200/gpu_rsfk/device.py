@@ -118,6 +118,52 @@ class DeviceForest(object):
         _lib.raise_on_status(code, "forest")
         return log
 
+    # ------------------------------------------------------------------ query path
+    def keep_index(self, on=True):
+        """Later tree builds keep the tree index that queries descend."""
+        _lib.raise_on_status(self._lib.rsfk_ctx_keep_index(self._ctx, 1 if on else 0), "keep_index")
+
+    def route_queries(self, points, queries):
+        """(q_start, q_count) numpy arrays: the segment of ``perm`` (``tree_export``)
+        that is the leaf bucket each query row ends in under the last tree."""
+        _want(points, torch.float32, "points"); _want(queries, torch.float32, "queries")
+        N, D = points.shape
+        NQ = queries.shape[0]
+        if queries.shape[1] != D:
+            raise ValueError("points and queries differ in dimension")
+        qs, qc = np.empty(NQ, np.int32), np.empty(NQ, np.int32)
+        code = self._lib.rsfk_dev_route_queries(self._ctx, _ptr(points), N, D, _ptr(queries), NQ,
+                                                qs.ctypes.data, qc.ctypes.data)
+        _lib.raise_on_status(code, "route_queries")
+        return qs, qc
+
+    def ann_bucket_knn(self, points, queries, idx, dist):
+        """Query lists (rows of ``idx``/``dist``, indices of base points) take in the
+        base points of the bucket each query is routed to under the last tree."""
+        _want(points, torch.float32, "points"); _want(queries, torch.float32, "queries")
+        _want(idx, torch.int32, "idx"); _want(dist, torch.float32, "dist")
+        N, D = points.shape
+        NQ = queries.shape[0]
+        if queries.shape[1] != D or idx.shape[0] != NQ or dist.shape != idx.shape:
+            raise ValueError("shapes of queries and lists do not agree")
+        code = self._lib.rsfk_dev_ann_bucket_knn(self._ctx, _ptr(points), N, _ptr(queries), NQ, D,
+                                                 idx.shape[1], _ptr(idx), _ptr(dist))
+        _lib.raise_on_status(code, "ann_bucket_knn")
+
+    def forest_ann(self, points, queries, idx, dist, n_trees, min_children, max_children,
+                   max_depth=5000, seed=0, first_tree=0, tree_stride=1):
+        """Trees over the base points, each followed by the query update."""
+        _want(points, torch.float32, "points"); _want(queries, torch.float32, "queries")
+        _want(idx, torch.int32, "idx"); _want(dist, torch.float32, "dist")
+        N, D = points.shape
+        NQ = queries.shape[0]
+        if queries.shape[1] != D or idx.shape[0] != NQ or dist.shape != idx.shape:
+            raise ValueError("shapes of queries and lists do not agree")
+        code = self._lib.rsfk_dev_forest_ann(self._ctx, _ptr(points), N, _ptr(queries), NQ, D, idx.shape[1],
+                                             n_trees, first_tree, tree_stride, min_children, max_children,
+                                             max_depth, seed, _ptr(idx), _ptr(dist))
+        _lib.raise_on_status(code, "forest_ann")
+
     def explore(self, points, old_idx, idx, dist, row_begin=0, row_end=None, list_row0=0):
         """One sweep over rows [row_begin,row_end); ``idx``/``dist`` start at row ``list_row0``."""
         _want(points, torch.float32, "points"); _want(old_idx, torch.int32, "old_idx")

@@ -49,9 +49,14 @@ RSFK_EXPORT void pymodule_cluster_by_sample_tree(int N, int D, int MIN_TREE_CHIL
                                      float* points, int** nodes_buckets, int** bucket_sizes,
                                      int* total_leaves, int* max_child);
 
-/* Same symbol as the reference's base/query entry point (src/python/pymodule_ext.cu:61-77,
- * 149-181).  That path is outside this library's scope: the call leaves its
- * outputs untouched and sets status RSFK_ERR_UNSUPPORTED. */
+/* Replaces pymodule_rsfk_knn_ann (reference: src/python/pymodule_ext.cu:61-77, 149-181;
+ * bound at python/gpu_rsfk/RSFK.py:134-152, called at :498-514; driver
+ * RSFK::knn_gpu_rsfk_forest_ann, src/rsfk.cu:98-498).  n_trees trees over the N base
+ * points (tree t seeded RANDOM_STATE+t); every query row descends each tree to a leaf
+ * and its list -- knn_indices/knn_sqr_distances[NQ*K], IN/OUT, indices of BASE points,
+ * -1 / +inf (or FLT_MAX) = empty -- takes in the base points of that leaf.  As in the
+ * reference, nn_exploring_factor is not used and log_forest is not written on this
+ * path.  Rows come back ordered by (distance, index). */
 RSFK_EXPORT void pymodule_rsfk_knn_ann(int n_trees, int num_neighbors, int N, int NQ, int D,
                            int MIN_TREE_CHILD, int MAX_TREE_CHILD, int MAX_DEPTH, int VERBOSE,
                            int RANDOM_STATE, int nn_exploring_factor,
@@ -144,6 +149,37 @@ RSFK_EXPORT int rsfk_dev_forest(rsfk_ctx* ctx, const float* d_points, int N, int
 RSFK_EXPORT int rsfk_dev_explore(rsfk_ctx* ctx, const float* d_points, int N, int D, int K,
                      const int* d_old_idx, int* d_idx, float* d_dist,
                      int row_begin, int row_end, int list_row0);
+
+/* Query (base/query) path on device memory.
+ *
+ * rsfk_ctx_keep_index(ctx, 1) makes every later tree build of the context keep its
+ * tree index (one row per split: the pair of sample points and where each side
+ * leads), which the two calls below descend; 0 (the default) turns that off.
+ * Reference: the per-level arrays the reference keeps in RSFKIndexTree when
+ * create_bucket_from_sample_tree runs with free_index=false
+ * (src/include/rsfk.h:92-160, src/rsfk.cu:176-178). */
+RSFK_EXPORT int rsfk_ctx_keep_index(rsfk_ctx* ctx, int on);
+/* Leaf bucket of every query row under the context's tree: q_start/q_count (HOST,
+ * [NQ]) receive the segment of perm (rsfk_dev_tree_export) that is the bucket
+ * (reference: the query descent, src/rsfk.cu:270-347, ending in
+ * compute_bucket_for_query_points, build_tree_update_parents_ann.cu:76-91). */
+RSFK_EXPORT int rsfk_dev_route_queries(rsfk_ctx* ctx, const float* d_points, int N, int D,
+                           const float* d_queries, int NQ, int* q_start, int* q_count);
+/* Routes the queries and merges each query's list (d_idx/d_dist, [NQ*K], canonical,
+ * indices of base points) with the base points of its bucket (reference:
+ * compute_knn_from_buckets_perwarp_coalesced_ann,
+ * src/kernels/build_tree_update_parents_ann.cu:232-513). */
+RSFK_EXPORT int rsfk_dev_ann_bucket_knn(rsfk_ctx* ctx, const float* d_points, int N,
+                            const float* d_queries, int NQ, int D, int K,
+                            int* d_idx, float* d_dist);
+/* Trees first_tree, first_tree+tree_stride, ... (n_trees of them, tree t seeded
+ * seed+t) over the base points, each followed by the query update (reference: the
+ * tree loop of RSFK::knn_gpu_rsfk_forest_ann, src/rsfk.cu:116-126). */
+RSFK_EXPORT int rsfk_dev_forest_ann(rsfk_ctx* ctx, const float* d_points, int N,
+                        const float* d_queries, int NQ, int D, int K,
+                        int n_trees, int first_tree, int tree_stride,
+                        int min_children, int max_children, int max_depth, int seed,
+                        int* d_idx, float* d_dist);
 
 /* out = the K smallest distinct entries of G canonical lists per row.
  * d_idx_lists/d_dist_lists are HOST arrays of G device pointers (G <= 16).

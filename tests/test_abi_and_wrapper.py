@@ -42,13 +42,23 @@ def test_status_entry_points_without_a_gpu():
     L.rsfk_free(None)
 
 
-def test_ann_entry_point_reports_unsupported():
-    from gpu_rsfk import _lib, RSFK
-    L = _lib.load()
-    L.pymodule_rsfk_knn_ann(*([0] * 11 + [None] * 5))
-    assert L.rsfk_last_status() == 3
-    with pytest.raises(Exception):
-        RSFK().find_nearest_neighbors_ann(np.zeros((4, 2), np.float32), np.zeros((1, 2), np.float32), 2)
+def test_ann_entry_point_refuses_null_buffers():
+    from gpu_rsfk import _lib
+    _lib.load()
+    raw = ctypes.CDLL(_lib.LIB_PATH)  # no prototypes: NULL buffers reach the library
+    raw.pymodule_rsfk_knn_ann(*([ctypes.c_int(0)] * 11 + [None] * 5))
+    # 2 = invalid argument; 1 = no CUDA device, which a box without a GPU reports first
+    assert raw.rsfk_last_status() in (1, 2)
+
+
+def test_ann_wrapper_argument_validation():
+    from gpu_rsfk import RSFK
+    r = RSFK()
+    X, Q = np.zeros((10, 3), np.float32), np.zeros((4, 3), np.float32)
+    with pytest.raises(Exception, match="max_tree_children must be at least 2\\*min_tree_children"):
+        r.find_nearest_neighbors_ann(X, Q, 4, min_tree_children=8, max_tree_children=9)
+    with pytest.raises(Exception, match="same number of dimensions"):
+        r.find_nearest_neighbors_ann(X, np.zeros((4, 5), np.float32), 4)
 
 
 def test_wrapper_argument_validation_matches_reference():
@@ -92,6 +102,9 @@ def test_no_gpu_means_loud_failure():
     from gpu_rsfk import RSFK, RSFKLibraryError
     with pytest.raises(RSFKLibraryError):
         RSFK().find_nearest_neighbors(np.random.rand(50, 4).astype(np.float32), 3, n_trees=1)
+    with pytest.raises(RSFKLibraryError):
+        RSFK().find_nearest_neighbors_ann(np.random.rand(50, 4).astype(np.float32),
+                                          np.random.rand(5, 4).astype(np.float32), 3, n_trees=1)
     from gpu_rsfk.device import DeviceForest
     with pytest.raises(RSFKLibraryError):
         DeviceForest()

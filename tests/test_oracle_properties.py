@@ -161,3 +161,69 @@ def test_bruteforce_and_recall(oracle):
     assert oracle.recall(bi, shuffled) == 1.0
     wrong = np.full_like(bi, -1)
     assert oracle.recall(bi, wrong) == 0.0
+
+
+# ---------------------------------------------------------------- query path
+@pytest.mark.parametrize("N,D,MIN,MAX", [(3000, 17, 8, 24), (5000, 32, 33, 66), (2000, 3, 4, 12),
+                                         (4000, 100, 10, 40), (100, 16, 33, 66), (1, 4, 2, 4)])
+def test_routing_sends_a_base_point_to_its_own_bucket(oracle, N, D, MIN, MAX):
+    """A query equal to base point p takes p's side at every split, and follows p
+    when p's side dissolves: it must end in p's bucket.  The tree itself is the
+    one build_tree gives."""
+    X = _uniform(N, D, 3)
+    t0 = oracle.build_tree(X, MIN, MAX, seed=3)
+    t = oracle.build_tree_route(X, X, MIN, MAX, seed=3)
+    np.testing.assert_array_equal(t["perm"], t0["perm"])
+    np.testing.assert_array_equal(t["leaf_start"], t0["leaf_start"])
+    np.testing.assert_array_equal(t["leaf_count"], t0["leaf_count"])
+    start_of, count_of = np.empty(N, np.int32), np.empty(N, np.int32)
+    for s, c in zip(t["leaf_start"], t["leaf_count"]):
+        start_of[t["perm"][s:s + c]] = s
+        count_of[t["perm"][s:s + c]] = c
+    np.testing.assert_array_equal(t["q_start"], start_of)
+    np.testing.assert_array_equal(t["q_count"], count_of)
+
+
+def test_routing_follows_the_split_rule_of_the_recorded_tree(oracle):
+    """Walk the recorded tree by hand: at row r the query goes right iff n.q < c;
+    a side without a row of its own leads to a leaf or to the sibling's row."""
+    N, NQ, D, MIN, MAX = 3000, 400, 9, 6, 14
+    X, Q = _uniform(N, D, 5), _uniform(NQ, D, 6)
+    rec = oracle.build_tree(X, MIN, MAX, seed=8, record=True)
+    t = oracle.build_tree_route(X, Q, MIN, MAX, seed=8)
+    table = rec["table"]
+    starts = set(int(s) for s in t["leaf_start"])
+    assert set(int(s) for s in t["q_start"]) <= starts
+    # every query's bucket must be on the query's side of the ROOT hyperplane
+    n, c = oracle.hyperplane(X[table[0, 0]], X[table[0, 1]], True)
+    root_right = np.array([oracle.project(n, q) < c for q in Q])
+    base_right = np.array([oracle.project(n, x) < c for x in X])
+    n_left = int((~base_right).sum())
+    if n_left >= MIN and N - n_left >= MIN:       # neither side dissolved
+        assert ((t["q_start"] >= n_left) == root_right).all()
+
+
+def test_query_update_reference_order_equals_canonical(oracle):
+    N, NQ, D, K = 4000, 1200, 20, 10
+    X, Q = _uniform(N, D, 11), _uniform(NQ, D, 12)
+    i0, d0 = oracle.init_lists(NQ, K, self_in_row=False)
+    ia, da, ir, dr = i0, d0, i0, d0
+    for seed in (1, 2, 3):
+        t = oracle.build_tree_route(X, Q, 8, 24, seed=seed)
+        ia, da = oracle.ann_bucket_knn(X, Q, K, t["perm"], t["q_start"], t["q_count"], ia, da)
+        ir, dr = oracle.ann_bucket_knn_ref(X, Q, K, t["perm"], t["q_start"], t["q_count"], ir, dr)
+        si, sd = oracle.sort_rows(ir, dr)
+        np.testing.assert_array_equal(ia, si)
+        np.testing.assert_array_equal(da.view(np.int32), sd.view(np.int32))
+    # each row holds the K nearest of the union of the three buckets it met
+    assert (np.diff(da, axis=1) >= 0).all()
+
+
+def test_query_forest_recall_grows_with_trees(oracle):
+    X, Q = _uniform(4000, 8, 13), _uniform(500, 8, 14)
+    K = 8
+    bi, bd = oracle.bruteforce_ann(X, Q, K)
+    d2 = ((Q[:, None, :].astype(np.float64) - X[None, :, :]) ** 2).sum(-1)
+    np.testing.assert_allclose(bd, np.sort(d2, axis=1)[:, :K], rtol=1e-5, atol=1e-7)   # 1e-5 relative
+    r = [oracle.recall(bi, oracle.ann_forest(X, Q, K, T, 9, 18, seed=2)[0]) for T in (1, 4, 16)]
+    assert r[0] < r[1] < r[2] and r[2] > 0.9
