@@ -165,3 +165,77 @@ def test_reference_tree_is_reproduced_by_the_restated_rules(oracle, path):
     for b, members in enumerate(buckets):
         label[list(members)] = b
     assert _reconstruct(oracle, X, np.arange(N, dtype=np.int32), label, MIN, MAX, True)
+
+
+def _fill_order(K):
+    """Slots in the order the reference's replace-the-worst rule fills an empty
+    (all +inf) K-list.  Lane l of the warp scans slots l, l+32, ... and keeps its
+    first strictly larger value; a shfl_down tree (16, 8, 4, 2, 1) then keeps the
+    receiving lane's value on ties
+    (src/kernels/build_tree_update_parents_ann.cu:300-345).  While an empty slot
+    is left the winner does not depend on the finite values."""
+    filled = np.zeros(K, bool)
+    order = []
+    for _ in range(K):
+        val = np.full(32, -1.0)
+        pos = np.full(32, -1)
+        for lane in range(32):
+            for k in range(lane, K, 32):
+                v = 0.0 if filled[k] else np.inf
+                if v > val[lane]:
+                    val[lane], pos[lane] = v, k
+        for off in (16, 8, 4, 2, 1):
+            nv, npos = val.copy(), pos.copy()
+            for lane in range(32 - off):
+                if val[lane + off] > val[lane]:
+                    nv[lane], npos[lane] = val[lane + off], pos[lane + off]
+            val, pos = nv, npos
+        order.append(int(pos[0]))
+        filled[pos[0]] = True
+    return order
+
+
+@pytest.mark.parametrize("path", _load("ref_ann_*.npz"))
+def test_reference_query_path_on_its_own_base_points(oracle, path):
+    """pymodule_rsfk_knn_ann of the reference binary with the query set equal to
+    the base set (tests/golden/make_ref_ann_golden.py), one tree, K > MAX."""
+    z = np.load(path)
+    X, idx, dist = z["X"], z["idx"], z["dist"]
+    N, D, MIN, MAX, K = [int(v) for v in z["params"]]
+    fill = _fill_order(K)
+    # routing: a query equal to base point p ends in p's bucket, so the rows of the
+    # members of a bucket all list that bucket, p itself at distance 0
+    orders = {}
+    for p in range(N):
+        m = int((idx[p] >= 0).sum())
+        seq = idx[p][fill[:m]]                  # bucket order as this row saw it
+        assert (seq >= 0).all()                 # filled slots are exactly the first m of the fill order
+        assert p in seq.tolist()
+        assert dist[p][idx[p] == p][0] == 0.0
+        key = frozenset(seq.tolist())
+        orders.setdefault(key, []).append(tuple(seq.tolist()))
+    sizes = []
+    for members, seqs in orders.items():
+        assert len(seqs) == len(members)        # every member routed here, nobody else
+        assert len(set(seqs)) == 1              # all rows met the bucket in the same order
+        sizes.append(len(members))
+    assert sum(sizes) == N and min(sizes) >= MIN and max(sizes) <= MAX
+    # update rule and distance bits: the oracle over the same buckets (same order)
+    perm = np.concatenate([np.array(seqs[0], np.int32) for seqs in orders.values()])
+    counts = np.array([len(seqs[0]) for seqs in orders.values()], np.int32)
+    starts = (np.cumsum(counts) - counts).astype(np.int32)
+    q_start, q_count = np.empty(N, np.int32), np.empty(N, np.int32)
+    for s, c in zip(starts, counts):
+        q_start[perm[s:s + c]] = s
+        q_count[perm[s:s + c]] = c
+    i0, d0 = oracle.init_lists(N, K, self_in_row=False)
+    ri, rd = oracle.ann_bucket_knn_ref(X, X, K, perm, q_start, q_count, i0, d0)
+    np.testing.assert_array_equal(ri, idx)                                   # slot for slot
+    np.testing.assert_array_equal(rd.view(np.int32), dist.view(np.int32))    # bit for bit
+    ci, cd = oracle.ann_bucket_knn(X, X, K, perm, q_start, q_count, i0, d0)
+    si, sd = oracle.sort_rows(idx, dist)
+    np.testing.assert_array_equal(ci, si)
+    np.testing.assert_array_equal(cd.view(np.int32), sd.view(np.int32))
+    # and the routing rule reproduces it: a tree whose buckets are these buckets sends
+    # every base point, used as a query, to the bucket that holds it (property of
+    # orc_build_tree_route, checked on the oracle's own trees in test_oracle_properties)
