@@ -46,6 +46,10 @@ WORKLOADS = {
     "c3": dict(N=4_000_000, D=2, K=32, trees=32, min=256, max=1024, sweeps=1, gen="gauss2d", seed=1),
     "c4": dict(N=1_000_000, D=960, K=32, trees=20, min=33, max=2048, sweeps=2, gen="gauss960", seed=2),
     "c5": dict(N=20_000_000, D=128, K=64, trees=64, min=65, max=130, sweeps=2, gen="bytes128", seed=3),
+    # query (base/query) search in the shape of the reference's own experiment (test_ann.py:40-160:
+    # 3 M word vectors reduced to 32 dimensions, half of them as base set, the query set equal to the
+    # base set, K=32, buckets of 32..256 points, 5..30 trees); one GPU
+    "ann": dict(N=1_500_000, D=32, K=32, trees=20, min=32, max=256, sweeps=0, gen="mix32", seed=4),
 }
 
 # DRAM bytes (read+write) per launch of the dominant kernel from the committed
@@ -73,6 +77,15 @@ def make_points(w, n_override=None):
         for s in range(0, N, 100_000):
             e = min(N, s + 100_000)
             out[s:e] = c[rng.integers(0, 100, e - s)] + rng.normal(0, 0.3, (e - s, D))
+        return out
+    if w["gen"] == "mix32":
+        # stand-in for PCA-reduced embeddings: 200 clusters, variance falling with the dimension
+        spectrum = 1.0 / np.sqrt(1.0 + np.arange(D))
+        c = rng.normal(0, 1, (200, D)) * spectrum
+        out = np.empty((N, D), np.float32)
+        for s in range(0, N, 250_000):
+            e = min(N, s + 250_000)
+            out[s:e] = c[rng.integers(0, 200, e - s)] + rng.normal(0, 0.5, (e - s, D)) * spectrum
         return out
     if w["gen"] == "bytes128":
         c = rng.integers(0, 256, (1000, D)).astype(np.float32)
@@ -440,6 +453,246 @@ def cpu_bruteforce(X, K, seed, seconds):
                       % (nq, N, dt)}
 
 
+# --------------------------------------------------------------------------- query (ANN) workload
+ANN_METRIC = "query search queries/s at fixed recall@K"
+
+
+def ann_points(args, w):
+    """(base points, query points).  The query set is the base set itself (as the
+    reference's experiment has it) or, with --distinct-queries, as many further draws
+    of the same mixture."""
+    N = args.points or w["N"]
+    if not args.distinct_queries:
+        X = make_points(w, N)
+        return X, X
+    both = make_points(w, 2 * N)
+    return np.ascontiguousarray(both[:N]), np.ascontiguousarray(both[N:])
+
+
+def ann_config(args, w, N, NQ):
+    return {"workload": "%s: base N=%d, queries NQ=%d (%s), D=%d K=%d n_trees=%d min/max_tree_children=%d/%d %s seed %d"
+                        % (args.workload, N, NQ, "fresh draws" if args.distinct_queries else "the base set itself",
+                           w["D"], w["K"], w["trees"], w["min"], w["max"], w["gen"], w["seed"]),
+            "parallelism": "single GPU",
+            "l2": "inputs (%.0f MB points + %.0f MB queries + %.0f MB lists) exceed the 126 MB L2; no flush"
+                  % (4e-6 * N * w["D"], 4e-6 * NQ * w["D"], 8e-6 * NQ * w["K"])}
+
+
+def run_ann(args, w):
+    import torch
+    from gpu_rsfk import RSFK
+    from gpu_rsfk.device import DeviceForest
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        raise RuntimeError("the query workload is a single-GPU bench line")
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    D, K, T = w["D"], w["K"], w["trees"]
+    X, Q = ann_points(args, w)
+    N, NQ = X.shape[0], Q.shape[0]
+    X_dev = torch.from_numpy(X).to(dev)
+    Q_dev = X_dev if Q is X else torch.from_numpy(Q).to(dev)
+    f = DeviceForest(dev)
+
+    def step():
+        idx, dist = f.init_lists(NQ, K, dev, self_in_row=False)
+        f.forest_ann(X_dev, Q_dev, idx, dist, T, w["min"], w["max"], seed=w["seed"])
+        return idx, dist
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    launches0, before = f.kernel_launches(), f.stats()
+    sampler = ClockSampler(0)
+    with sampler:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            idx, dist = step()
+        e1.record()
+        torch.cuda.synchronize()
+    after = f.stats()
+    launches = f.kernel_launches() - launches0
+    tot = {n: after[n] - before[n] for n in after}
+    ms_per_step = e0.elapsed_time(e1) / args.steps
+    value = NQ / (ms_per_step * 1e-3)
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    trees_run = max(1, tot["trees"])
+    sub_pts, sub_nodes = tot["sub_active_points"], tot["sub_nodes"]
+    lvl_pts, lvl_nodes = tot["tree_active_points"] - sub_pts, tot["tree_nodes"] - sub_nodes
+    proj_n = max(1, tot["project_launches"])
+    phases = {
+        "tree_build_host_observed": dict(launches=trees_run, ms_per_launch=tot["tree_build_us"] / 1e3 / trees_run,
+                                         bytes_per_launch=(4.0 * (D + 2) * tot["tree_active_points"]
+                                                           + 4.0 * (D + 1) * tot["tree_nodes"]) / trees_run),
+        "tree_project": dict(launches=proj_n, ms_per_launch=tot["project_us"] / 1e3 / proj_n,
+                             bytes_per_launch=(4.0 * (D + 1) * lvl_pts + 4.0 * (D + 1) * lvl_nodes) / proj_n),
+        "tree_subtrees": dict(launches=trees_run, ms_per_launch=tot["subtree_us"] / 1e3 / trees_run,
+                              bytes_per_launch=(4.0 * (D + 2) * sub_pts + 4.0 * (D + 1) * sub_nodes) / trees_run),
+        # hyperplanes + descent + grouping: every query row once, every hyperplane once, leaf ids out
+        "query_route": dict(launches=trees_run, ms_per_launch=tot["route_us"] / 1e3 / trees_run,
+                            bytes_per_launch=4.0 * NQ * D + 4.0 * (D + 1) * tot["tree_nodes"] / trees_run + 12.0 * NQ),
+        # bucket update: every query row and every base row once, lists read and written
+        "query_update": dict(launches=trees_run, ms_per_launch=tot["query_update_us"] / 1e3 / trees_run,
+                             bytes_per_launch=4.0 * NQ * D + 4.0 * N * D + 4.0 * N + 2 * 8.0 * NQ * K),
+    }
+    for p in phases.values():
+        p["gbs"] = p["bytes_per_launch"] / (p["ms_per_launch"] * 1e-3) / 1e9 if p["ms_per_launch"] > 0 else None
+        p["total_ms"] = p["ms_per_launch"] * p["launches"]
+    dom = max((n for n in phases if n != "tree_build_host_observed"), key=lambda n: phases[n]["total_ms"])
+    kernel_of = {"tree_project": "k_project_wide", "tree_subtrees": "k_subtree",
+                 "query_route": "k_planes + k_route + k_leaf_offsets + k_place_queries",
+                 "query_update": "k_ann_bucket"}
+    roofline = dict(bound="hbm", kernel=kernel_of[dom], achieved=phases[dom]["gbs"], peak=peak_gbs, unit="GB/s",
+                    frac=(phases[dom]["gbs"] or 0) / peak_gbs,
+                    peak_kind="measured" if "hbm_gbs" in peaks else "fallback", traffic=None,
+                    algorithmic_bytes_per_launch=phases[dom]["bytes_per_launch"],
+                    ms_per_launch=phases[dom]["ms_per_launch"])
+
+    recall = None
+    if not args.no_recall:
+        nq = min(NQ, args.recall_queries)
+        rows = np.sort(np.random.default_rng(w["seed"] + 1000).choice(NQ, nq, replace=False))
+        rows_t = torch.as_tensor(rows, device=dev)
+        truth = []
+        chunk = max(1, int(2.5e8 // N))
+        x2 = (X_dev * X_dev).sum(1)
+        for s in range(0, nq, chunk):
+            qv = Q_dev[rows_t[s:s + chunk]]
+            d2 = x2[None, :] - 2.0 * (qv @ X_dev.T)
+            truth.append(d2.topk(K, dim=1, largest=False).indices)
+        truth = torch.cat(truth).cpu().numpy()
+        recall = recall_of(truth, idx[rows_t].cpu().numpy())
+    del idx, dist
+    torch.cuda.empty_cache()
+
+    e2e = None
+    if not args.no_e2e:
+        r = RSFK(random_state=w["seed"])
+        times = []
+        for i in range(args.e2e_steps + 2):
+            r.find_nearest_neighbors_ann(X, Q, K, n_trees=T, min_tree_children=w["min"],
+                                         max_tree_children=w["max"], ensure_valid_indices=False)
+            if i > 1:
+                times.append(r._last_search_time)
+        t = float(np.mean(times))
+        e2e = dict(value=NQ / t, unit="queries/s", h2d_bytes_per_step=4 * (N + NQ) * D + 8 * NQ * K,
+                   d2h_bytes_per_step=8 * NQ * K, ms_per_step=t * 1e3, ms_each=[round(v * 1e3, 2) for v in times],
+                   api="gpu_rsfk.RSFK.find_nearest_neighbors_ann -> pymodule_rsfk_knn_ann (host buffers)")
+
+    cpu = None
+    if not args.no_cpu:
+        from oracle import rsfk_oracle as orc
+        probe = Q[:32]
+        t0 = time.time()
+        orc.bruteforce_ann(X, probe, K)
+        per_row = (time.time() - t0) / len(probe)
+        nq = int(max(32, min(NQ, args.cpu_seconds / max(per_row, 1e-9))))
+        t0 = time.time()
+        orc.bruteforce_ann(X, Q[:nq], K)
+        dt = time.time() - t0
+        cpu = {"value": nq / dt, "unit": "queries/s", "cores": os.cpu_count(), "kind": "port",
+               "sample": "exact brute-force search (OpenMP, fmaf) of the first %d query rows against all %d base "
+                         "points, %.1f s" % (nq, N, dt)}
+
+    print(json.dumps({
+        "metric": ANN_METRIC, "value": value, "unit": "queries/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": ann_config(args, w, N, NQ),
+        "recall_at_k": recall, "e2e": e2e, "gpu_launches": int(launches), "clocks": sampler.summary(),
+        "roofline": roofline,
+        "phases": {n: {k: (round(v, 4) if isinstance(v, float) else v) for k, v in p.items()}
+                   for n, p in phases.items()},
+        "cpu_baseline": cpu}))
+
+
+def ann_reference_worker(args, w):
+    """Child process: the reference's pymodule_rsfk_knn_ann (src/python/pymodule_ext.cu:149-181) with the
+    query set equal to the base set -- the shape of its own experiment and the only one its driver
+    handles within bounds (src/rsfk.cu:396-403)."""
+    L = ctypes.CDLL(REF_SO)
+    L.pymodule_rsfk_knn_ann.restype = None
+    L.pymodule_rsfk_knn_ann.argtypes = [ctypes.c_int] * 11 + [ctypes.c_void_p] * 5
+    X = make_points(w, args.points)
+    N, D, K, T = X.shape[0], w["D"], w["K"], w["trees"]
+    Q = X.copy()
+    times = []
+    for s in range(args.warmup + args.steps):
+        idx = np.full((N, K), -1, np.int32)
+        dst = np.full((N, K), np.inf, np.float32)
+        log = np.zeros(16 * T + 2, np.float32)
+        t0 = time.time()
+        L.pymodule_rsfk_knn_ann(T, K, N, N, D, w["min"], w["max"], 5000, 0, w["seed"], 0, X.ctypes.data,
+                                Q.ctypes.data, idx.ctypes.data, dst.ctypes.data, log.ctypes.data)
+        if s >= args.warmup:
+            times.append(time.time() - t0)
+    recall = None
+    if not args.no_recall:
+        import torch
+        dev = torch.device("cuda", 0)
+        Xd = torch.from_numpy(X).to(dev)
+        nq = min(N, args.recall_queries)
+        rows = np.sort(np.random.default_rng(w["seed"] + 1000).choice(N, nq, replace=False))
+        truth = exact_knn_torch(Xd, rows, K).cpu().numpy()
+        recall = recall_of(truth, idx[rows])
+    print("REFRESULT " + json.dumps({"times": times, "recall": recall, "trees": T, "forest_s": 0.0,
+                                     "explore_s": 0.0}))
+
+
+def run_ann_reference(args, w):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    base = {"impl": "reference"}
+    if args.distinct_queries:
+        print(json.dumps(dict(base, unavailable="the reference's query driver reads and scatters out of bounds "
+                                                "unless the query set is the base set (src/rsfk.cu:396-403); "
+                                                "not run")))
+        return
+    if not os.path.exists(REF_SO):
+        print(json.dumps(dict(base, unavailable="oracle/_ref/librsfk_ref.so was not built (make -C oracle ref)")))
+        return
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-worker", "--workload", args.workload,
+           "--steps", str(args.steps), "--warmup", str(args.warmup), "--recall-queries", str(args.recall_queries)]
+    if args.points:
+        cmd += ["--points", str(args.points)]
+    if args.no_recall:
+        cmd += ["--no-recall"]
+    env = dict(os.environ)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    try:
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.ref_timeout)
+    except subprocess.TimeoutExpired:
+        print(json.dumps(dict(base, unavailable="reference library did not finish within %d s" % args.ref_timeout)))
+        return
+    res = [l for l in out.stdout.splitlines() if l.startswith("REFRESULT ")]
+    if out.returncode != 0 or not res:
+        tail = (out.stderr or out.stdout).strip().splitlines()[-1:] or ["no output"]
+        print(json.dumps(dict(base, unavailable="reference library failed (exit %d): %s" % (out.returncode, tail[0][:200]))))
+        return
+    r = json.loads(res[0][len("REFRESULT "):])
+    t = float(np.mean(r["times"]))
+    N = args.points or w["N"]
+    value = N / t
+    print(json.dumps({
+        "impl": "reference", "metric": ANN_METRIC, "value": value, "unit": "queries/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": ann_config(args, w, N, N), "recall_at_k": r["recall"],
+        "cpu_baseline": {"value": value, "unit": "queries/s", "cores": 0, "kind": "reference",
+                         "sample": "the reference's own CUDA library (it has no CPU path), unmodified sources "
+                                   "compiled for sm_100, one GPU, host buffers, whole workload"},
+        "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
 # --------------------------------------------------------------------------- reference arm
 REF_SO = os.path.join(ROOT, "oracle", "_ref", "librsfk_ref.so")
 
@@ -551,9 +804,13 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--ref-trees", type=int, default=0, help="reference arm: time this many trees and scale")
     ap.add_argument("--ref-timeout", type=int, default=900)
+    ap.add_argument("--distinct-queries", action="store_true",
+                    help="query workload: fresh draws instead of the base set itself")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference":
+    if args.workload == "ann":
+        {"reference": run_ann_reference, "reference-worker": ann_reference_worker}.get(args.impl, run_ann)(args, w)
+    elif args.impl == "reference":
         run_reference(args, w)
     elif args.impl == "reference-worker":
         reference_worker(args, w)

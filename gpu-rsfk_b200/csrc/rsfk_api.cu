@@ -555,11 +555,13 @@ int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
             !c.check(cudaStreamSynchronize(c.stream), "stats"))
             return c.status;
     }
-    const double v[11] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+    c.resolve_ann_events();
+    const double v[13] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
                          c.stats.bucket_knn_us, (double)evaluated, c.stats.subtree_us,
                          (double)c.stats.sub_active_points, (double)c.stats.sub_nodes, c.stats.tree_build_us,
-                         c.stats.project_us, (double)c.stats.project_launches};
-    for (int i = 0; i < n && i < 11; ++i) out[i] = v[i];
+                         c.stats.project_us, (double)c.stats.project_launches, c.stats.route_us,
+                         c.stats.query_update_us};
+    for (int i = 0; i < n && i < 13; ++i) out[i] = v[i];
     return RSFK_OK;
 }
 

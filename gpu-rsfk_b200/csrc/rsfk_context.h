@@ -71,6 +71,8 @@ struct Stats {
     double tree_build_us = 0.0;       // host-observed time of the tree builds (each ends with a stream sync)
     long long sub_active_points = 0;  // part of tree_active_points projected inside subtree CTAs
     long long sub_nodes = 0;          // part of tree_nodes split inside subtree CTAs
+    double route_us = 0.0;            // query path: device time of hyperplanes + descent + grouping by leaf
+    double query_update_us = 0.0;     // query path: device time of the query-bucket kernels
 };
 
 struct TreeResult {
@@ -113,6 +115,21 @@ struct Context {
     LevelCounters* host_counters = nullptr; // pinned
     LevelMail* mail = nullptr;              // pinned + mapped
     cudaEvent_t sub_ev[2] = {nullptr, nullptr};
+    cudaEvent_t ann_ev[3] = {nullptr, nullptr, nullptr}; // query path: before routing, after grouping, after the update
+    bool ann_ev_pending = false;
+    // adds the last query update's device times to the stats (waits for its last event)
+    void resolve_ann_events()
+    {
+        if (!ann_ev_pending) return;
+        ann_ev_pending = false;
+        float a = 0.0f, b = 0.0f;
+        if (cudaEventSynchronize(ann_ev[2]) == cudaSuccess &&
+            cudaEventElapsedTime(&a, ann_ev[0], ann_ev[1]) == cudaSuccess &&
+            cudaEventElapsedTime(&b, ann_ev[1], ann_ev[2]) == cudaSuccess) {
+            stats.route_us += a * 1e3;
+            stats.query_update_us += b * 1e3;
+        }
+    }
     std::vector<cudaEvent_t> level_ev; // two per tree level, reused by every tree
     // A forest overlaps the bucket KNN of tree t (second stream) with the build
     // of tree t+1 (main stream); trees alternate between two result buffers.
@@ -196,6 +213,8 @@ struct Context {
         if (host_counters) { cudaFreeHost(host_counters); host_counters = nullptr; }
         if (mail) { cudaFreeHost(mail); mail = nullptr; }
         for (auto& e : sub_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
+        for (auto& e : ann_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
+        ann_ev_pending = false;
         for (auto& e : level_ev) cudaEventDestroy(e);
         level_ev.clear();
         for (int i = 0; i < 2; ++i) {

@@ -794,6 +794,10 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
     int* q_order = (int*)ctx.scratch(Context::QUERY_ORDER, sizeof(int) * (size_t)NQ);
     int* leaf_queries = (int*)ctx.scratch(Context::LEAF_QUERIES, sizeof(int) * (size_t)(tree.n_leaves + 1));
     if (ctx.status != RSFK_OK) return false;
+    ctx.resolve_ann_events();
+    for (auto& e : ctx.ann_ev)
+        if (!e && !ctx.check(cudaEventCreate(&e), "cudaEventCreate")) return false;
+    cudaEventRecord(ctx.ann_ev[0], st);
     if (!ctx.check(cudaMemsetAsync(leaf_queries, 0, sizeof(int) * (size_t)(tree.n_leaves + 1), st),
                    "clear leaf counts"))
         return false;
@@ -803,6 +807,7 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
     if (grid > ctx.sm_count * 16) grid = ctx.sm_count * 16;
     k_place_queries<<<grid, 256, 0, st>>>(q_leaf, NQ, leaf_queries, q_order);
     count_launches(2);
+    cudaEventRecord(ctx.ann_ev[1], st);
     // leaf_queries[n_leaves] = number of queries that reached a leaf = entries of q_order
     const size_t smem = sizeof(float) * (size_t)KNN_WARPS * D;
     if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "ann_bucket_knn: D too large");
@@ -820,6 +825,8 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
                                                      leaf_queries + tree.n_leaves, d_idx, d_dist);
     });
     count_launches(1);
+    cudaEventRecord(ctx.ann_ev[2], st);
+    ctx.ann_ev_pending = true;
     return ctx.check(cudaGetLastError(), "query bucket launch");
 }
 

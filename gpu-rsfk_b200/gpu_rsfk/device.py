@@ -191,11 +191,11 @@ class DeviceForest(object):
 
     def stats(self):
         """Work counters of this context (synchronizes the stream)."""
-        out = (ctypes.c_double * 11)()
-        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 11), "stats")
+        out = (ctypes.c_double * 13)()
+        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 13), "stats")
         names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates",
                  "subtree_us", "sub_active_points", "sub_nodes", "tree_build_us",
-                 "project_us", "project_launches")
+                 "project_us", "project_launches", "route_us", "query_update_us")
         return dict(zip(names, [float(v) for v in out]))
 
     def kernel_launches(self):

@@ -100,7 +100,9 @@ RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
  * evaluated, out[5] device microseconds spent in the subtree kernels, out[6] and
  * out[7] the part of out[1] and out[2] done inside subtree kernels, out[8] microseconds
  * the tree builds took as seen from the host, out[9] device microseconds spent in the
- * projection kernels of the tree levels and out[10] their launch count.  The reference's counterpart is its ForestLog of per-phase
+ * projection kernels of the tree levels and out[10] their launch count; query path:
+ * out[11] device microseconds of hyperplanes + descent + grouping by leaf, out[12] of
+ * the query-bucket kernels.  The reference's counterpart is its ForestLog of per-phase
  * wall-clock times (src/include/rsfk.h:274-392). */
 RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
