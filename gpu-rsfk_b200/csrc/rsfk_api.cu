@@ -17,6 +17,11 @@ struct rsfk_ctx {
     Context c;
     TreeResult tree;
     bool has_tree = false;
+    // Helper contexts (own stream, own scratch) that build part of a forest beside
+    // this one on the same GPU; created on first use, destroyed with the context.
+    std::vector<rsfk_ctx*> lanes;
+    cudaEvent_t lane_ready = nullptr;
+    int lanes_wanted = 0; // 0: the library's default (RSFK_LANES, else 2)
 };
 
 namespace {
@@ -159,12 +164,188 @@ void publish(const Context& c)
     g_last_message = c.message;
 }
 
+// Number of lanes a forest is split over on one GPU.  The trees of a forest are
+// independent and several of their kernels are latency-bound (the host round trip
+// of every tree level, the first levels' small grids, the subtree kernel), so two
+// tree sequences on two streams fill each other's gaps.  Each lane merges its trees
+// into a list of its own; the lists are combined at the end, which gives the same
+// rows as one sequence (the row of a point is the K smallest distinct of everything
+// it met, in whatever order).  Three lanes by default: two sometimes fall into step
+// with each other (both in the same phase at the same time) and then gain nothing.
+// RSFK_LANES overrides (1 = off, at most 4).  list_rows x K is the size of one list.
+int forest_lanes(const rsfk_ctx* h, int n_trees, size_t N, size_t list_rows, int K)
+{
+    static const int by_default = [] {
+        const char* e = getenv("RSFK_LANES");
+        const int v = e ? atoi(e) : 3;
+        return v < 1 ? 1 : (v > 4 ? 4 : v);
+    }();
+    int g = h->lanes_wanted > 0 ? h->lanes_wanted : by_default;
+    while (g > 1 && n_trees < 2 * g) --g; // at least two trees per lane
+    // every lane holds a list of its own and tree scratch (about 64 bytes per point):
+    // stay within half of the memory that is free now
+    size_t free_b = 0, total_b = 0;
+    if (g > 1 && cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+        const size_t per_lane = list_rows * (size_t)K * 8 + N * 64;
+        size_t held = 0; // lanes that exist already hold their memory
+        for (const rsfk_ctx* l : h->lanes)
+            for (const auto& b : l->c.slots) held += b.bytes;
+        held += h->c.slots[Context::LANE_IDX].bytes + h->c.slots[Context::LANE_DIST].bytes;
+        while (g > 1 && per_lane * g > (free_b + held) / 2) --g;
+    }
+    return g;
+}
+
+void destroy_lanes(rsfk_ctx* h)
+{
+    for (rsfk_ctx* l : h->lanes) {
+        cudaStreamSynchronize(l->c.stream);
+        l->c.release();
+        delete l;
+    }
+    h->lanes.clear();
+    if (h->lane_ready) { cudaEventDestroy(h->lane_ready); h->lane_ready = nullptr; }
+}
+
+// One lane's share of a forest: trees lane, lane+G, ... of the call, on the lane's
+// context and stream, merged into the lane's lists.
+// With d_queries the lists are query lists (NQ rows) and every tree is followed by the
+// query update instead of the bucket KNN.
+void lane_forest(rsfk_ctx* l, int lane, int G, const float* d_points, int N, int D, int K, int n_trees,
+                 int first_tree, int tree_stride, int min_children, int max_children, int max_depth, int seed,
+                 int* idx, float* dist, float* log_forest, int verbose, std::vector<cudaEvent_t>* ev,
+                 const float* d_queries, int NQ)
+{
+    Context& c = l->c;
+    cudaSetDevice(c.device);
+    c.keep_index = d_queries != nullptr;
+    bool ok = true;
+    for (int i = lane; i < n_trees && ok; i += G) {
+        const int t = first_tree + i * tree_stride;
+        const double tb0 = now_s();
+        ok = rsfk::tree_build(c, d_points, N, D, min_children, max_children, max_depth, seed + t, nullptr, 0,
+                              l->tree);
+        l->has_tree = ok;
+        const double tb1 = now_s();
+        c.stats.tree_build_us += (tb1 - tb0) * 1e6;
+        if (!ok) break;
+        cudaEventRecord((*ev)[2 * i], c.stream);
+        ok = d_queries ? rsfk::ann_bucket_knn(c, d_points, N, d_queries, NQ, D, K, l->tree, idx, dist)
+                       : rsfk::bucket_knn(c, d_points, N, D, K, l->tree, idx, dist);
+        cudaEventRecord((*ev)[2 * i + 1], c.stream);
+        if (log_forest) {
+            log_forest[0 * n_trees + i] = (float)l->tree.levels;
+            log_forest[1 * n_trees + i] = (float)l->tree.max_leaf;
+            log_forest[2 * n_trees + i] = (float)l->tree.min_leaf;
+            log_forest[3 * n_trees + i] = (float)l->tree.n_leaves;
+            log_forest[5 * n_trees + i] = (float)(tb1 - tb0);
+        }
+        if (verbose >= 2)
+            printf("tree %d: depth %d, leaves %d, leaf size %d..%d, build %.6f s\n", t, l->tree.levels,
+                   l->tree.n_leaves, l->tree.min_leaf, l->tree.max_leaf, tb1 - tb0);
+    }
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest lane");
+    ok = ok && c.check_error_flag();
+    c.resolve_ann_events();
+    c.keep_index = false;
+}
+
+bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, int K, int n_trees,
+                      int first_tree, int tree_stride, int min_children, int max_children, int max_depth,
+                      int seed, int* d_idx, float* d_dist, float* log_forest, int verbose,
+                      const float* d_queries = nullptr, int NQ = 0)
+{
+    Context& c = h->c;
+    while ((int)h->lanes.size() < G) {
+        rsfk_ctx* l = make_ctx(c.device, nullptr, true);
+        if (!l) return c.fail(RSFK_ERR_CUDA, "forest lanes: no stream for a lane");
+        h->lanes.push_back(l);
+    }
+    if (!h->lane_ready &&
+        !c.check(cudaEventCreateWithFlags(&h->lane_ready, cudaEventDisableTiming), "cudaEventCreate"))
+        return false;
+    const long long list_rows = d_queries ? NQ : N;
+    const size_t list_elems = (size_t)list_rows * K;
+    // every lane works on a stream and lists of its own; the caller's stream only empties the
+    // lane lists before and combines them with the caller's lists after
+    int* lane_idx = (int*)c.scratch(Context::LANE_IDX, sizeof(int) * list_elems * G);
+    float* lane_dist = (float*)c.scratch(Context::LANE_DIST, sizeof(float) * list_elems * G);
+    if (!lane_idx || !lane_dist) return false;
+    if (!rsfk::fill_empty_lists(c, lane_idx, lane_dist, (long long)list_elems * G)) return false;
+    // the points and the emptied lane lists are ready once the main stream gets here
+    cudaEventRecord(h->lane_ready, c.stream);
+    std::vector<cudaEvent_t> ev(2 * (size_t)n_trees);
+    for (auto& e : ev) cudaEventCreate(&e);
+    if (log_forest) memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
+    const double t0 = now_s();
+    std::vector<std::thread> workers;
+    for (int g = 0; g < G; ++g) {
+        rsfk_ctx* l = h->lanes[g];
+        l->c.status = RSFK_OK;
+        l->c.message.clear();
+        l->c.keep_index = false;
+        l->c.result_buf = 0;
+        cudaStreamWaitEvent(l->c.stream, h->lane_ready, 0);
+        if (g == 0) continue; // lane 0 runs on the calling thread
+        workers.emplace_back(lane_forest, l, g, G, d_points, N, D, K, n_trees, first_tree, tree_stride,
+                             min_children, max_children, max_depth, seed, lane_idx + list_elems * g,
+                             lane_dist + list_elems * g, log_forest, verbose, &ev, d_queries, NQ);
+    }
+    lane_forest(h->lanes[0], 0, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
+                max_children, max_depth, seed, lane_idx, lane_dist, log_forest, verbose, &ev, d_queries, NQ);
+    for (auto& w : workers) w.join();
+    bool ok = c.status == RSFK_OK;
+    for (int g = 0; g < G; ++g) {
+        Context& lc = h->lanes[g]->c;
+        if (ok && lc.status != RSFK_OK) ok = c.fail(lc.status, lc.message);
+        c.stats.add(lc.stats);
+        lc.stats = rsfk::Stats();
+    }
+    // the context's tree is the last one its first lane built
+    h->tree = h->lanes[0]->tree;
+    h->has_tree = ok && h->lanes[0]->has_tree;
+    if (ok) {
+        // every lane's stream is idle now; combine on the main stream, in place over the caller's lists
+        const int* ip[5];
+        const float* dp[5];
+        ip[0] = d_idx;
+        dp[0] = d_dist;
+        for (int g = 0; g < G; ++g) {
+            ip[g + 1] = lane_idx + list_elems * g;
+            dp[g + 1] = lane_dist + list_elems * g;
+        }
+        ok = rsfk::merge_lists(c, list_rows, K, G + 1, ip, dp, d_idx, d_dist) &&
+             c.check(cudaStreamSynchronize(c.stream), "forest merge");
+    }
+    if (ok && !d_queries)
+        for (int i = 0; i < n_trees; ++i) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]) == cudaSuccess) {
+                c.stats.bucket_knn_us += ms * 1e3;
+                if (log_forest) log_forest[15 * n_trees + i] = ms * 1e-3f;
+            }
+        }
+    for (auto& e : ev) cudaEventDestroy(e);
+    if (log_forest) log_forest[16 * n_trees] = (float)(now_s() - t0);
+    return ok;
+}
+
 // Trees + bucket KNN into canonical device lists; fills the ForestLog rows.
 bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_trees, int first_tree,
                 int tree_stride, int min_children, int max_children, int max_depth, int seed,
                 int* d_idx, float* d_dist, float* log_forest, int verbose)
 {
     Context& c = h->c;
+    {
+        static const bool single = [] {
+            const char* o = getenv("RSFK_OVERLAP");
+            return (o && o[0] == '1') || getenv("RSFK_TIMELINE") != nullptr;
+        }();
+        const int G = single ? 1 : forest_lanes(h, n_trees, (size_t)N, (size_t)N, K);
+        if (G > 1)
+            return run_forest_lanes(h, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
+                                    max_children, max_depth, seed, d_idx, d_dist, log_forest, verbose);
+    }
     std::vector<cudaEvent_t> ev(2 * (size_t)n_trees);
     for (auto& e : ev) cudaEventCreate(&e);
     if (log_forest) memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
@@ -260,6 +441,14 @@ bool run_forest_ann(rsfk_ctx* h, const float* d_points, int N, const float* d_qu
                     int max_children, int max_depth, int seed, int* d_idx, float* d_dist, int verbose)
 {
     Context& c = h->c;
+    {
+        // lanes only on request (rsfk_ctx_set_lanes): the query update is issue-bound and takes
+        // most of a tree's time here, so sequences side by side gain nothing (measured)
+        const int G = h->lanes_wanted > 1 ? forest_lanes(h, n_trees, (size_t)N, (size_t)NQ, K) : 1;
+        if (G > 1)
+            return run_forest_lanes(h, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
+                                    max_children, max_depth, seed, d_idx, d_dist, nullptr, verbose, d_queries, NQ);
+    }
     const bool keep_before = c.keep_index;
     c.keep_index = true;
     c.result_buf = 0;
@@ -314,6 +503,7 @@ void rsfk_release_memory(void)
     if (!g_default) return;
     cudaSetDevice(g_default->c.device);
     cudaStreamSynchronize(g_default->c.stream);
+    destroy_lanes(g_default);
     for (auto& b : g_default->c.slots) {
         if (b.ptr) cudaFree(b.ptr);
         b.ptr = nullptr;
@@ -536,6 +726,7 @@ void rsfk_ctx_destroy(rsfk_ctx* ctx)
 {
     if (!ctx) return;
     cudaSetDevice(ctx->c.device);
+    destroy_lanes(ctx);
     cudaStreamSynchronize(ctx->c.stream);
     ctx->c.release();
     delete ctx;
@@ -653,6 +844,13 @@ int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, int N, int D
     t.max_leaf = max_leaf;
     rsfk::bucket_knn(ctx->c, d_points, N, D, K, t, d_idx, d_dist);
     return ctx->c.status;
+}
+
+int rsfk_ctx_set_lanes(rsfk_ctx* ctx, int lanes)
+{
+    if (!ctx || lanes < 0 || lanes > 4) return RSFK_ERR_ARG;
+    ctx->lanes_wanted = lanes;
+    return RSFK_OK;
 }
 
 int rsfk_ctx_keep_index(rsfk_ctx* ctx, int on)

@@ -71,6 +71,14 @@ struct Stats {
     double tree_build_us = 0.0;       // host-observed time of the tree builds (each ends with a stream sync)
     long long sub_active_points = 0;  // part of tree_active_points projected inside subtree CTAs
     long long sub_nodes = 0;          // part of tree_nodes split inside subtree CTAs
+    void add(const Stats& o)
+    {
+        trees += o.trees; tree_active_points += o.tree_active_points; tree_nodes += o.tree_nodes;
+        bucket_knn_us += o.bucket_knn_us; subtree_us += o.subtree_us; project_us += o.project_us;
+        project_launches += o.project_launches; tree_build_us += o.tree_build_us;
+        sub_active_points += o.sub_active_points; sub_nodes += o.sub_nodes;
+        route_us += o.route_us; query_update_us += o.query_update_us;
+    }
     double route_us = 0.0;            // query path: device time of hyperplanes + descent + grouping by leaf
     double query_update_us = 0.0;     // query path: device time of the query-bucket kernels
 };
@@ -104,6 +112,7 @@ struct Context {
         PERM_FINAL_B, LEAF_START_B, LEAF_COUNT_B,
         SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
         RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
+        LANE_IDX, LANE_DIST,
         N_SLOTS
     };
     // When set, tree_build keeps the tree index (TreeResult::records) that the
@@ -240,6 +249,8 @@ bool tree_route(Context& ctx, const float* d_points, int D, const TreeResult& tr
 // rsfk_knn.cu
 int list_capacity();                      // largest supported K
 bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K);
+// n list entries set to empty: index -1, distance +inf
+bool fill_empty_lists(Context& ctx, int* d_idx, float* d_dist, long long n);
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
                 int* d_idx, float* d_dist, bool on_aux_stream = false);
 // Query lists (rows of d_idx/d_dist, NQ x K, indices of base points) merged with the

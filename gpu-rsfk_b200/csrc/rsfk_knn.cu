@@ -683,6 +683,24 @@ static bool check_k(Context& ctx, int K)
     return true;
 }
 
+__global__ void k_fill_empty(int* __restrict__ idx, float* __restrict__ dist, long long n)
+{
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {
+        idx[e] = -1;
+        dist[e] = CUDART_INF_F;
+    }
+}
+
+bool fill_empty_lists(Context& ctx, int* d_idx, float* d_dist, long long n)
+{
+    if (n <= 0) return true;
+    long long blocks = (n + 255) / 256;
+    if (blocks > ctx.sm_count * 16) blocks = ctx.sm_count * 16;
+    k_fill_empty<<<(int)blocks, 256, 0, ctx.stream>>>(d_idx, d_dist, n);
+    count_launches(1);
+    return ctx.check(cudaGetLastError(), "fill launch");
+}
+
 bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K)
 {
     if (!check_k(ctx, K)) return false;

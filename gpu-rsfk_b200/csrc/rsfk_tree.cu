@@ -1075,44 +1075,91 @@ k_planes(const float* __restrict__ pts, int D, const int4* __restrict__ records,
     if (lane == 0) offsets[r] = c;
 }
 
-// One warp per query: descend from row 0 to a leaf slot.  The projection is the
-// reference's warp sum (term k on lane k%32, fused multiply-add, xor butterfly),
-// the comparison `n.x < c` sends the query right.  The descent is bounded by
-// max_steps; a query that does not reach a leaf raises the error flag.
+// Descent from row 0 to a leaf slot.  The projection is the reference's warp sum
+// (term k on lane k%32, fused multiply-add, xor butterfly), the comparison
+// `n.x < c` sends the query right.  The descent is bounded by max_steps; a query
+// that does not reach a leaf raises the error flag.
+//
+// VEC4 (D % 4 == 0, 16-byte aligned rows): eight lanes per query, four queries
+// per warp; lane t of the eight owns terms 4t..4t+3 (+32, ...), i.e. virtual
+// lanes 4t..4t+3 of that sum (the layout of project_group_vec4), so a warp keeps
+// four independent descents in flight.  Otherwise one warp per query.
 constexpr int ROUTE_WARPS = 8;
 
+template <bool VEC4>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 k_route(const float* __restrict__ queries, int NQ, int D, const int4* __restrict__ records, int n_recs,
         const float* __restrict__ normals, const float* __restrict__ offsets, int max_steps,
         int n_leaves, int* __restrict__ q_leaf, int* __restrict__ leaf_queries, int* __restrict__ error_flag)
 {
+    constexpr int QPW = VEC4 ? 4 : 1;       // queries per warp
+    constexpr int GL = 32 / QPW;            // lanes per query
     extern __shared__ float4 smem4[];
-    float* xq = reinterpret_cast<float*>(smem4) + (size_t)(threadIdx.x >> 5) * D;
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane / GL, t = lane % GL;
+    float* xq = reinterpret_cast<float*>(smem4) + ((size_t)warp * QPW + g) * D;
     const int warp0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int n_warps = (gridDim.x * blockDim.x) >> 5;
-    for (int q = warp0; q < NQ; q += n_warps) {
+    const int D4 = D >> 2;
+    for (int q0 = warp0 * QPW; q0 < NQ; q0 += n_warps * QPW) {
+        const int q = q0 + g;
+        const bool live = q < NQ;
         __syncwarp();
-        for (int k = lane; k < D; k += 32) xq[k] = __ldg(queries + (size_t)q * D + k);
+        if (live) {
+            if (VEC4) {
+                const float4* src = reinterpret_cast<const float4*>(queries + (size_t)q * D);
+                for (int k4 = t; k4 < D4; k4 += GL) reinterpret_cast<float4*>(xq)[k4] = __ldg(src + k4);
+            } else {
+                for (int k = t; k < D; k += GL) xq[k] = __ldg(queries + (size_t)q * D + k);
+            }
+        }
         __syncwarp();
         int cur = 0, leaf = -1;
-        for (int step = 0; step < max_steps; ++step) {
-            const int4 rec = records[cur];
-            int ref = rec.z;
-            if (rec.x >= 0) {
-                const float* nrm = normals + (size_t)cur * D;
+        bool done = !live;
+        for (int step = 0; step < max_steps && __any_sync(RSFK_FULL, !done); ++step) {
+            int4 rec = make_int4(-1, -1, -1, -1);
+            if (!done) rec = records[cur];
+            float pr = 0.0f;
+            if (VEC4) {
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+                if (!done && rec.x >= 0) {
+                    const float4* nrm = reinterpret_cast<const float4*>(normals + (size_t)cur * D);
+                    const float4* x4 = reinterpret_cast<const float4*>(xq);
+                    for (int k4 = t; k4 < D4; k4 += GL) {
+                        const float4 n = __ldg(nrm + k4);
+                        const float4 x = x4[k4];
+                        a0 = __fmaf_rn(n.x, x.x, a0);
+                        a1 = __fmaf_rn(n.y, x.y, a1);
+                        a2 = __fmaf_rn(n.z, x.z, a2);
+                        a3 = __fmaf_rn(n.w, x.w, a3);
+                    }
+                }
+                pr = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
+                pr = __fadd_rn(pr, __shfl_xor_sync(RSFK_FULL, pr, 1));
+                pr = __fadd_rn(pr, __shfl_xor_sync(RSFK_FULL, pr, 2));
+                pr = __fadd_rn(pr, __shfl_xor_sync(RSFK_FULL, pr, 4));
+            } else {
                 float acc = 0.0f;
-                for (int k = lane; k < D; k += 32) acc = __fmaf_rn(__ldg(nrm + k), xq[k], acc);
-                if (butterfly_sum(acc) < offsets[cur]) ref = rec.w;
+                if (!done && rec.x >= 0) {
+                    const float* nrm = normals + (size_t)cur * D;
+                    for (int k = t; k < D; k += GL) acc = __fmaf_rn(__ldg(nrm + k), xq[k], acc);
+                }
+                pr = butterfly_sum(acc);
             }
-            if (ref < 0) {
-                leaf = -1 - ref;
-                break;
+            if (!done) {
+                int ref = rec.z;
+                if (rec.x >= 0 && pr < offsets[cur]) ref = rec.w;
+                if (ref < 0) {
+                    leaf = -1 - ref;
+                    done = true;
+                } else if (ref >= n_recs) {
+                    done = true;
+                } else {
+                    cur = ref;
+                }
             }
-            if (ref >= n_recs) break;
-            cur = ref;
         }
-        if (lane == 0) {
+        if (live && t == 0) {
             if (leaf < 0 || leaf >= n_leaves) {
                 q_leaf[q] = -1;
                 atomicExch(error_flag, RSFK_ERR_OVERFLOW);
@@ -1142,17 +1189,21 @@ bool tree_route(Context& ctx, const float* d_points, int D, const TreeResult& tr
         count_launches(1);
         ctx.planes_ready = true;
     }
-    const size_t smem = sizeof(float) * (size_t)ROUTE_WARPS * D;
+    const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_queries) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(normals) & 15) == 0);
+    const int qpw = vec4 ? 4 : 1;
+    const size_t smem = sizeof(float) * (size_t)ROUTE_WARPS * qpw * D;
     if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "tree_route: D too large");
+    auto kern = vec4 ? k_route<true> : k_route<false>;
     if (smem > 48 * 1024 &&
-        !ctx.check(cudaFuncSetAttribute(k_route, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+        !ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    "route smem attribute"))
         return false;
-    long long blocks = ((long long)NQ + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    long long blocks = ((long long)NQ + ROUTE_WARPS * qpw - 1) / (ROUTE_WARPS * qpw);
     if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
-    k_route<<<(int)blocks, ROUTE_WARPS * 32, smem, st>>>(d_queries, NQ, D, tree.records, n_recs, normals,
-                                                          offsets, tree.levels + 8, tree.n_leaves, d_q_leaf,
-                                                          d_leaf_queries, error_flag);
+    kern<<<(int)blocks, ROUTE_WARPS * 32, smem, st>>>(d_queries, NQ, D, tree.records, n_recs, normals, offsets,
+                                                       tree.levels + 8, tree.n_leaves, d_q_leaf, d_leaf_queries,
+                                                       error_flag);
     count_launches(1);
     return ctx.check(cudaGetLastError(), "route launch");
 }

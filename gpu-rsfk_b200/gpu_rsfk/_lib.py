@@ -91,6 +91,8 @@ def load():
     L.rsfk_dev_explore.argtypes = [vp, vp, i, i, i, vp, vp, vp, i, i, i]
     L.rsfk_dev_merge_lists.restype = i
     L.rsfk_dev_merge_lists.argtypes = [vp, ll, i, i, vp, vp, vp, vp]
+    L.rsfk_ctx_set_lanes.restype = i
+    L.rsfk_ctx_set_lanes.argtypes = [vp, i]
     L.rsfk_ctx_keep_index.restype = i
     L.rsfk_ctx_keep_index.argtypes = [vp, i]
     L.rsfk_dev_route_queries.restype = i

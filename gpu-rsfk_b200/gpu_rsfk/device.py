@@ -107,6 +107,11 @@ class DeviceForest(object):
                                                    int(max_leaf), _ptr(idx), _ptr(dist))
         _lib.raise_on_status(code, "bucket_knn_table")
 
+    def set_lanes(self, lanes):
+        """Tree sequences a forest call runs side by side (1..4; 0 = library default).
+        The result does not depend on it."""
+        _lib.raise_on_status(self._lib.rsfk_ctx_set_lanes(self._ctx, int(lanes)), "set_lanes")
+
     def forest(self, points, idx, dist, n_trees, min_children, max_children, max_depth=5000, seed=0,
                first_tree=0, tree_stride=1, want_log=False):
         _want(points, torch.float32, "points"); _want(idx, torch.int32, "idx"); _want(dist, torch.float32, "dist")

@@ -134,6 +134,13 @@ RSFK_EXPORT int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, 
                               const int* d_leaf_count, int n_leaves, int max_leaf,
                               int* d_idx, float* d_dist);
 
+/* How many tree sequences ("lanes") a forest call of this context runs side by side on
+ * the GPU, each on a stream of its own with lists of its own that are combined at the
+ * end: 1..4, or 0 for the default (environment variable RSFK_LANES, else 2; never more
+ * than n_trees/2).  The result does not depend on it.  No reference counterpart (the
+ * reference builds its trees one after another, src/rsfk.cu:2073-2088). */
+RSFK_EXPORT int rsfk_ctx_set_lanes(rsfk_ctx* ctx, int lanes);
+
 /* Trees first_tree, first_tree+tree_stride, ... (n_trees of them), tree t with
  * seed `seed`+t, each followed by its bucket KNN (reference: the tree loop of
  * RSFK::knn_gpu_rsfk_forest, src/rsfk.cu:2073-2088).  log_forest (host,

@@ -167,6 +167,16 @@ def test_query_forest_on_the_device_matches_oracle(indexed, oracle):
     torch.cuda.synchronize()
     np.testing.assert_array_equal(didx.cpu().numpy(), ri)
     np.testing.assert_array_equal(ddist.cpu().numpy().view(np.int32), rd.view(np.int32))
+    # the same forest as three tree sequences side by side
+    li, ld = _dev(i0), _dev(d0)
+    indexed.set_lanes(3)
+    try:
+        indexed.forest_ann(_dev(X), _dev(Q), li, ld, T, 13, 26, seed=100)
+    finally:
+        indexed.set_lanes(0)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(li.cpu().numpy(), ri)
+    np.testing.assert_array_equal(ld.cpu().numpy().view(np.int32), rd.view(np.int32))
     # sharded over two "ranks" (trees 0,2,4 and 1,3,5) then merged = the same lists
     parts = []
     for g in range(2):

@@ -223,6 +223,34 @@ def test_forest_equals_oracle_pipeline(forest, oracle):
     assert log[3 * T:4 * T].min() > 0          # total leaves per tree
 
 
+@pytest.mark.parametrize("lanes", [1, 2, 3, 4])
+def test_forest_lanes_do_not_change_the_graph(forest, oracle, lanes):
+    """A forest split over several tree sequences on one GPU (each with lists of
+    its own, combined at the end) returns the rows of the oracle's sequential
+    pipeline, whatever the number of lanes; caller-supplied rows take part once."""
+    N, D, K, T = 6000, 40, 12, 9
+    X = _uniform(N, D, 23)
+    idx, dist = oracle.init_lists(N, K)
+    idx[:, 1] = (np.arange(N) + 1) % N                    # a valid neighbour the caller already knows
+    dist[:, 1] = [oracle.dist_sqr(X[p], X[(p + 1) % N]) for p in range(N)]
+    d_idx, d_dist = _dev(idx), _dev(dist)
+    ridx, rdist = oracle.sort_rows(idx, dist)
+    for t in range(T):
+        tr = oracle.build_tree(X, 13, 26, seed=50 + t)
+        ridx, rdist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], ridx, rdist)
+    forest.set_lanes(lanes)
+    try:
+        forest.sort_rows(d_idx, d_dist)
+        log = forest.forest(_dev(X), d_idx, d_dist, T, 13, 26, seed=50, want_log=True)
+    finally:
+        forest.set_lanes(0)
+    np.testing.assert_array_equal(d_idx.cpu().numpy(), ridx)
+    np.testing.assert_array_equal(d_dist.cpu().numpy().view(np.int32), rdist.view(np.int32))
+    assert (log[3 * T:4 * T] > 0).all() and (log[15 * T:16 * T] > 0).all()   # every tree logged
+    st = forest.stats()
+    assert st["trees"] >= T
+
+
 def test_config1_recall_through_wrapper(oracle):
     """Small plumbing configuration: N=20000, D=32, K=16, 4 trees, 32/128, one
     sweep, through the drop-in Python class; recall against exact brute force."""
