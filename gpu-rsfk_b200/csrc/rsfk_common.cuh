@@ -148,13 +148,19 @@ struct WarpList {
     // rows in memory are already canonical
     __device__ __forceinline__ void load(const int* gi, const float* gd, int K, int lane)
     {
+        load_raw(gi, gd, K, lane);
+        refresh_threshold(K);
+    }
+    // The loads alone, so that they can be issued early; refresh_threshold() must
+    // follow before the list is used.
+    __device__ __forceinline__ void load_raw(const int* gi, const float* gd, int K, int lane)
+    {
 #pragma unroll
         for (int r = 0; r < KPL; ++r) {
             int e = r * 32 + lane;
             d[r] = e < K ? gd[e] : CUDART_INF_F;
             i[r] = e < K ? gi[e] : -1;
         }
-        refresh_threshold(K);
     }
     __device__ __forceinline__ void store(int* gi, float* gd, int K, int lane) const
     {

@@ -107,13 +107,37 @@ __device__ __forceinline__ void merge_candidates(WarpList<KPL>& L, const float* 
     }
 }
 
+// Rows ids[0..n) of the point array into X[n][D] (shared memory).  A warp takes
+// rows warp, warp+8, ...; with 16-byte loads (VEC4: D % 4 == 0, aligned rows)
+// four of its rows are in flight at a time, so that a 50-point bucket is fetched
+// in two round trips instead of six.
+template <bool VEC4>
 __device__ __forceinline__ void stage_rows(const float* __restrict__ pts, int D, const int* ids, int n,
                                            float* X, int warp, int lane)
 {
-    for (int r = warp; r < n; r += KNN_WARPS) {
-        const float* src = pts + (size_t)ids[r] * D;
-        float* dst = X + (size_t)r * D;
-        for (int k = lane; k < D; k += 32) dst[k] = __ldg(src + k);
+    if (VEC4) {
+        const int D4 = D >> 2;
+        float4* X4 = reinterpret_cast<float4*>(X);
+        for (int rb = warp; rb < n; rb += 4 * KNN_WARPS) {
+            const float4* src[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                src[u] = reinterpret_cast<const float4*>(pts + (size_t)ids[min(rb + u * KNN_WARPS, n - 1)] * D);
+            for (int k4 = lane; k4 < D4; k4 += 32) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = __ldg(src[u] + k4);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (rb + u * KNN_WARPS < n) X4[(size_t)(rb + u * KNN_WARPS) * D4 + k4] = v[u];
+            }
+        }
+    } else {
+        for (int r = warp; r < n; r += KNN_WARPS) {
+            const float* src = pts + (size_t)ids[r] * D;
+            float* dst = X + (size_t)r * D;
+            for (int k = lane; k < D; k += 32) dst[k] = __ldg(src + k);
+        }
     }
 }
 
@@ -171,7 +195,16 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
         __syncthreads();
         for (int r = threadIdx.x; r < mI; r += blockDim.x) idsI[r] = ids[i0 + r];
         __syncthreads();
-        stage_rows(pts, D, idsI, mI, XI, warp, lane);
+        // A leaf that fits one block visits every row once: the first list of each warp is
+        // requested now, before the rows and the distance tile, and each later one while
+        // the previous row is merged, so that no warp waits for its list.
+        const bool single = (n_blocks == 1);
+        WarpList<KPL> Lnext;
+        if (single && warp < mI) {
+            const int first = idsI[warp];
+            Lnext.load_raw(knn_idx + (size_t)first * K, knn_dist + (size_t)first * K, K, lane);
+        }
+        stage_rows<VEC4 && !SMALL_D>(pts, D, idsI, mI, XI, warp, lane);
         for (int bj = bi; bj < n_blocks; ++bj) {
             const int j0 = bj * B, mJ = min(B, m - j0);
             const bool diag = (bj == bi);
@@ -179,7 +212,7 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
                 __syncthreads();
                 for (int r = threadIdx.x; r < mJ; r += blockDim.x) idsJ[r] = ids[j0 + r];
                 __syncthreads();
-                stage_rows(pts, D, idsJ, mJ, XJ, warp, lane);
+                stage_rows<VEC4 && !SMALL_D>(pts, D, idsJ, mJ, XJ, warp, lane);
             }
             __syncthreads();
             const float* XJc = diag ? XI : XJ;
@@ -290,7 +323,16 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
             for (int r = warp; r < mI; r += KNN_WARPS) {
                 const int self = idsI[r];
                 WarpList<KPL> L;
-                L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                if (single) {
+                    L = Lnext;
+                    L.refresh_threshold(K);
+                    if (r + KNN_WARPS < mI) {
+                        const int nxt = idsI[r + KNN_WARPS];
+                        Lnext.load_raw(knn_idx + (size_t)nxt * K, knn_dist + (size_t)nxt * K, K, lane);
+                    }
+                } else {
+                    L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                }
                 bool changed = false;
                 merge_candidates<KPL>(L, tile + r * TS, 1, idsJc, mJ, self, K, lane, changed);
                 if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
@@ -760,7 +802,7 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     }
     const size_t smem = bytes(B, two);
     RSFK_DISPATCH_KPL(K, {
-        const bool v4 = (D % 4 == 0) && (B % 4 == 0);
+        const bool v4 = (D % 4 == 0) && (B % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
         auto kern = (D <= 16) ? k_bucket_knn<KPL, true, false>
                               : (v4 ? k_bucket_knn<KPL, false, true> : k_bucket_knn<KPL, false, false>);
         if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
