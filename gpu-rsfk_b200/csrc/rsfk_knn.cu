@@ -659,6 +659,136 @@ k_ann_bucket(const float* __restrict__ pts, const float* __restrict__ queries, i
     }
 }
 
+// Squared distances from the query (xq, shared memory) to rows row0 .. row0+n-1
+// (n <= 32) of X[.][D] in shared memory, in the summation order of
+// explore_dist32_*; lane l returns the distance of row row0 + item.
+__device__ __forceinline__ float leaf_dist32_scalar(const float* X, int D, const float* xq, int row0, int n,
+                                                    int lane, int& item)
+{
+    float acc[32];
+    const float* row[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+        acc[c] = 0.0f;
+        row[c] = X + (size_t)(row0 + min(c, n - 1)) * D;
+    }
+    for (int k = lane; k < D; k += 32) {
+        const float x = xq[k];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            const float df = __fsub_rn(row[c][k], x);
+            acc[c] = __fmaf_rn(df, df, acc[c]);
+        }
+    }
+    const float dsum = transposed_sum32(acc, lane);
+    item = item32_of_lane(lane);
+    return dsum;
+}
+
+__device__ __forceinline__ float leaf_dist32_vec4(const float* X, int D, const float* xq, int row0, int n,
+                                                  int lane, int& item)
+{
+    const int g = lane >> 3, t = lane & 7;
+    const float4* xq4 = reinterpret_cast<const float4*>(xq);
+    const int D4 = D >> 2;
+    float acc[8][4];
+    const float4* row[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        row[j] = reinterpret_cast<const float4*>(X) + (size_t)(row0 + min(4 * j + g, n - 1)) * D4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[j][q] = 0.0f;
+    }
+    for (int k4 = t; k4 < D4; k4 += 8) {
+        const float4 x = xq4[k4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 v = row[j][k4];
+            float df;
+            df = __fsub_rn(v.x, x.x); acc[j][0] = __fmaf_rn(df, df, acc[j][0]);
+            df = __fsub_rn(v.y, x.y); acc[j][1] = __fmaf_rn(df, df, acc[j][1]);
+            df = __fsub_rn(v.z, x.z); acc[j][2] = __fmaf_rn(df, df, acc[j][2]);
+            df = __fsub_rn(v.w, x.w); acc[j][3] = __fmaf_rn(df, df, acc[j][3]);
+        }
+    }
+    float mine = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float s = __fadd_rn(__fadd_rn(acc[j][0], acc[j][1]), __fadd_rn(acc[j][2], acc[j][3]));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 1));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 2));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 4));
+        if (j == t) mine = s;
+    }
+    item = 4 * t + g;
+    return mine;
+}
+
+// Query update, one CTA per leaf: the leaf's base rows are staged in shared
+// memory once and every query routed to the leaf is compared with them there
+// (same arithmetic, same lists as k_ann_bucket).  group_end[l] is the end of leaf
+// l's group in q_order (groups in leaf order); a leaf without queries costs one
+// load.  Used when the rows of the largest leaf fit shared memory.
+template <int KPL, bool VEC4>
+__global__ void __launch_bounds__(KNN_THREADS, KPL <= 1 ? 3 : 2)
+k_ann_leaf(const float* __restrict__ pts, const float* __restrict__ queries, int D, int K,
+           const int* __restrict__ perm, const int* __restrict__ leaf_start,
+           const int* __restrict__ leaf_count, const int* __restrict__ group_end,
+           const int* __restrict__ q_order, int max_leaf, int* __restrict__ knn_idx,
+           float* __restrict__ knn_dist)
+{
+    extern __shared__ float4 smem4[];
+    float* X = reinterpret_cast<float*>(smem4);                  // [max_leaf][D]
+    float* xq_all = X + (size_t)max_leaf * D;                    // [KNN_WARPS][D]
+    int* ids = reinterpret_cast<int*>(xq_all + (size_t)KNN_WARPS * D); // [max_leaf]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int leaf = blockIdx.x;
+    const int q_end = group_end[leaf];
+    const int q_beg = leaf > 0 ? group_end[leaf - 1] : 0;
+    if (q_end <= q_beg) return;
+    const int m = min(leaf_count[leaf], max_leaf);
+    const int* ids_g = perm + leaf_start[leaf];
+    for (int r = threadIdx.x; r < m; r += blockDim.x) ids[r] = ids_g[r];
+    // the first query of each warp: its list and its row are requested before the leaf's rows
+    WarpList<KPL> Lnext;
+    int q_next = -1;
+    if (q_beg + warp < q_end) {
+        q_next = q_order[q_beg + warp];
+        Lnext.load_raw(knn_idx + (size_t)q_next * K, knn_dist + (size_t)q_next * K, K, lane);
+    }
+    __syncthreads();
+    stage_rows<VEC4>(pts, D, ids, m, X, warp, lane);
+    __syncthreads();
+    float* xq = xq_all + (size_t)warp * D;
+    for (int o = q_beg + warp; o < q_end; o += KNN_WARPS) {
+        const int q = q_next;
+        __syncwarp();
+        for (int k = lane; k < D; k += 32) xq[k] = __ldg(queries + (size_t)q * D + k);
+        WarpList<KPL> L = Lnext;
+        L.refresh_threshold(K);
+        if (o + KNN_WARPS < q_end) {
+            q_next = q_order[o + KNN_WARPS];
+            Lnext.load_raw(knn_idx + (size_t)q_next * K, knn_dist + (size_t)q_next * K, K, lane);
+        }
+        __syncwarp();
+        bool changed = false;
+        for (int b0 = 0; b0 < m; b0 += 32) {
+            const int n = min(32, m - b0);
+            int item;
+            const float dsum = VEC4 ? leaf_dist32_vec4(X, D, xq, b0, n, lane, item)
+                                    : leaf_dist32_scalar(X, D, xq, b0, n, lane, item);
+            const int ci = item < n ? ids[b0 + item] : -1;
+            unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(dsum, ci));
+            while (mask) {
+                const int b = __ffs(mask) - 1;
+                mask &= mask - 1;
+                changed |= L.try_insert(__shfl_sync(RSFK_FULL, dsum, b), __shfl_sync(RSFK_FULL, ci, b), K, lane);
+            }
+        }
+        if (changed) L.store(knn_idx + (size_t)q * K, knn_dist + (size_t)q * K, K, lane);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // G-way merge of canonical lists: out = K smallest distinct of all G rows.
 // ---------------------------------------------------------------------------
@@ -874,6 +1004,25 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
     long long blocks = ((long long)NQ + KNN_WARPS - 1) / KNN_WARPS;
     if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
     const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
+    // one CTA per leaf with the leaf's rows in shared memory, when they fit twice per SM and
+    // leaves receive several queries each; else one warp per query reading rows through L2
+    const size_t leaf_smem = sizeof(float) * ((size_t)tree.max_leaf + KNN_WARPS) * D + sizeof(int) * (size_t)tree.max_leaf;
+    if (leaf_smem <= 100 * 1024 && (long long)NQ >= 4LL * tree.n_leaves) {
+        RSFK_DISPATCH_KPL(K, {
+            auto kern = vec4 ? k_ann_leaf<KPL, true> : k_ann_leaf<KPL, false>;
+            if (leaf_smem > 48 * 1024 &&
+                !ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)leaf_smem),
+                           "query leaf smem attribute"))
+                return false;
+            kern<<<tree.n_leaves, KNN_THREADS, leaf_smem, st>>>(d_points, d_queries, D, K, tree.perm, tree.leaf_start,
+                                                                tree.leaf_count, leaf_queries, q_order,
+                                                                tree.max_leaf, d_idx, d_dist);
+        });
+        count_launches(1);
+        cudaEventRecord(ctx.ann_ev[2], st);
+        ctx.ann_ev_pending = true;
+        return ctx.check(cudaGetLastError(), "query leaf launch");
+    }
     RSFK_DISPATCH_KPL(K, {
         auto kern = vec4 ? k_ann_bucket<KPL, true> : k_ann_bucket<KPL, false>;
         if (smem > 48 * 1024 &&
