@@ -3,6 +3,7 @@
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <mutex>
 #include <thread>
 #include <vector>
@@ -253,7 +254,8 @@ void lane_forest(rsfk_ctx* l, int lane, int G, const float* d_points, int N, int
 bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, int K, int n_trees,
                       int first_tree, int tree_stride, int min_children, int max_children, int max_depth,
                       int seed, int* d_idx, float* d_dist, float* log_forest, int verbose,
-                      const float* d_queries = nullptr, int NQ = 0)
+                      const float* d_queries = nullptr, int NQ = 0,
+                      const std::function<bool()>* lists_ready = nullptr)
 {
     Context& c = h->c;
     while ((int)h->lanes.size() < G) {
@@ -304,6 +306,8 @@ bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, i
     // the context's tree is the last one its first lane built
     h->tree = h->lanes[0]->tree;
     h->has_tree = ok && h->lanes[0]->has_tree;
+    // the caller's lists take part from here on only
+    if (lists_ready != nullptr && !(*lists_ready)()) ok = false;
     if (ok) {
         // every lane's stream is idle now; combine on the main stream, in place over the caller's lists
         const int* ip[5];
@@ -331,9 +335,13 @@ bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, i
 }
 
 // Trees + bucket KNN into canonical device lists; fills the ForestLog rows.
+// lists_ready (optional) is called once, on the calling thread, before the first use of
+// d_idx/d_dist: a host entry point finishes uploading the caller's lists there, so that the
+// upload runs beside the trees when the forest works on lane lists of its own.
 bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_trees, int first_tree,
                 int tree_stride, int min_children, int max_children, int max_depth, int seed,
-                int* d_idx, float* d_dist, float* log_forest, int verbose)
+                int* d_idx, float* d_dist, float* log_forest, int verbose,
+                const std::function<bool()>* lists_ready = nullptr)
 {
     Context& c = h->c;
     {
@@ -344,8 +352,10 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
         const int G = single ? 1 : forest_lanes(h, n_trees, (size_t)N, (size_t)N, K);
         if (G > 1)
             return run_forest_lanes(h, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
-                                    max_children, max_depth, seed, d_idx, d_dist, log_forest, verbose);
+                                    max_children, max_depth, seed, d_idx, d_dist, log_forest, verbose,
+                                    nullptr, 0, lists_ready);
     }
+    if (lists_ready != nullptr && !(*lists_ready)()) return false;
     std::vector<cudaEvent_t> ev(2 * (size_t)n_trees);
     for (auto& e : ev) cudaEventCreate(&e);
     if (log_forest) memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
@@ -559,16 +569,30 @@ void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TRE
         if (g_copier.copy(d, h, n, false, dev_id)) return true;
         return c.fail(RSFK_ERR_CUDA, std::string(what) + " failed");
     };
-    ok = ok && h2d(d_points, points, pts_bytes, "H2D points");
-    ok = ok && h2d(d_idx, knn_indices, sizeof(int) * list_elems, "H2D indices");
-    ok = ok && h2d(d_dist, knn_sqr_distances, sizeof(float) * list_elems, "H2D distances");
     const double th0 = now_s();
-    ok = ok && rsfk::sort_rows(c, d_idx, d_dist, N, K);
-    ok = ok && c.check(cudaStreamSynchronize(c.stream), "H2D");
+    ok = ok && h2d(d_points, points, pts_bytes, "H2D points");
     const double t0 = now_s();
-    if (ok && VERBOSE >= 1) printf("Host to device copies take %lf seconds\n", t0 - th0);
+    if (ok && VERBOSE >= 1) printf("Host to device copy of the points takes %lf seconds\n", t0 - th0);
+    // The caller's lists are needed only where the forest first touches them (with lanes: at the
+    // final combination), so they travel on a thread of their own beside the trees.
+    bool lists_up = true, joined = true;
+    std::thread uploader;
+    if (ok) {
+        joined = false;
+        uploader = std::thread([&] {
+            cudaSetDevice(dev_id);
+            lists_up = g_copier.copy(d_idx, knn_indices, sizeof(int) * list_elems, true, dev_id) &&
+                       g_copier.copy(d_dist, knn_sqr_distances, sizeof(float) * list_elems, true, dev_id);
+        });
+    }
+    const std::function<bool()> lists_ready = [&]() -> bool {
+        if (!joined) { uploader.join(); joined = true; }
+        if (!lists_up) return c.fail(RSFK_ERR_CUDA, "H2D lists failed");
+        return rsfk::sort_rows(c, d_idx, d_dist, N, K);
+    };
     ok = ok && run_forest(h, d_points, N, D, K, n_trees, 0, 1, MIN_TREE_CHILD, MAX_TREE_CHILD, MAX_DEPTH,
-                          RANDOM_STATE, d_idx, d_dist, log_forest, VERBOSE);
+                          RANDOM_STATE, d_idx, d_dist, log_forest, VERBOSE, &lists_ready);
+    if (!joined) { uploader.join(); joined = true; }
     const double t1 = now_s();
     if (ok && VERBOSE >= 1) printf("Creating RSFK forest takes %lf seconds\n", t1 - t0);
     ok = ok && run_sweeps(h, d_points, N, D, K, nn_exploring_factor, d_idx, d_dist);
