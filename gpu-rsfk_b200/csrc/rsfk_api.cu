@@ -286,7 +286,6 @@ bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, i
         l->c.status = RSFK_OK;
         l->c.message.clear();
         l->c.keep_index = false;
-        l->c.result_buf = 0;
         cudaStreamWaitEvent(l->c.stream, h->lane_ready, 0);
         if (g == 0) continue; // lane 0 runs on the calling thread
         workers.emplace_back(lane_forest, l, g, G, d_points, N, D, K, n_trees, first_tree, tree_stride,
@@ -345,10 +344,7 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
 {
     Context& c = h->c;
     {
-        static const bool single = [] {
-            const char* o = getenv("RSFK_OVERLAP");
-            return (o && o[0] == '1') || getenv("RSFK_TIMELINE") != nullptr;
-        }();
+        static const bool single = getenv("RSFK_TIMELINE") != nullptr;
         const int G = single ? 1 : forest_lanes(h, n_trees, (size_t)N, (size_t)N, K);
         if (G > 1)
             return run_forest_lanes(h, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
@@ -369,20 +365,8 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
     }
     const double t0 = now_s();
     bool ok = true;
-    // bucket KNN of tree i runs on a second stream while tree i+1 is built
-    // (off unless RSFK_OVERLAP=1: with the present kernels' register footprints the two
-    // streams do not co-reside on an SM, so nothing is gained)
-    static const bool overlap_allowed = [] { const char* e = getenv("RSFK_OVERLAP"); return e && e[0] == '1'; }();
-    const bool overlap = overlap_allowed && n_trees > 1 && c.ensure_aux() && c.error_flag() != nullptr;
-    if (overlap) {
-        cudaEventRecord(c.ev_join, c.stream); // the lists are ready on the main stream
-        cudaStreamWaitEvent(c.aux, c.ev_join, 0);
-    }
     for (int i = 0; i < n_trees && ok; ++i) {
         const int t = first_tree + i * tree_stride;
-        const int buf = overlap ? (i & 1) : 0;
-        c.result_buf = buf;
-        if (overlap && i >= 2) cudaStreamWaitEvent(c.stream, c.ev_knn[buf], 0); // buffer still being read?
         const double tb0 = now_s();
         ok = rsfk::tree_build(c, d_points, N, D, min_children, max_children, max_depth, seed + t,
                               nullptr, 0, h->tree);
@@ -391,18 +375,9 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
         c.stats.tree_build_us += (tb1 - tb0) * 1e6;
         if (timeline) { tl.push_back((tb0 - t0) * 1e3); tl.push_back((tb1 - t0) * 1e3); }
         if (!ok) break;
-        if (overlap) {
-            cudaEventRecord(c.ev_tree[buf], c.stream);
-            cudaStreamWaitEvent(c.aux, c.ev_tree[buf], 0);
-            cudaEventRecord(ev[2 * i], c.aux);
-            ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist, true);
-            cudaEventRecord(ev[2 * i + 1], c.aux);
-            cudaEventRecord(c.ev_knn[buf], c.aux);
-        } else {
-            cudaEventRecord(ev[2 * i], c.stream);
-            ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist);
-            cudaEventRecord(ev[2 * i + 1], c.stream);
-        }
+        cudaEventRecord(ev[2 * i], c.stream);
+        ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist);
+        cudaEventRecord(ev[2 * i + 1], c.stream);
         if (log_forest) {
             log_forest[0 * n_trees + i] = (float)h->tree.levels;
             log_forest[1 * n_trees + i] = (float)h->tree.max_leaf;
@@ -413,11 +388,6 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
         if (verbose >= 2)
             printf("tree %d: depth %d, leaves %d, leaf size %d..%d, build %.6f s\n", t, h->tree.levels,
                    h->tree.n_leaves, h->tree.min_leaf, h->tree.max_leaf, tb1 - tb0);
-    }
-    c.result_buf = 0;
-    if (overlap) {
-        cudaEventRecord(c.ev_join, c.aux); // later work on the main stream sees the finished lists
-        cudaStreamWaitEvent(c.stream, c.ev_join, 0);
     }
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
     ok = ok && c.check_error_flag();
@@ -461,7 +431,6 @@ bool run_forest_ann(rsfk_ctx* h, const float* d_points, int N, const float* d_qu
     }
     const bool keep_before = c.keep_index;
     c.keep_index = true;
-    c.result_buf = 0;
     bool ok = true;
     for (int i = 0; i < n_trees && ok; ++i) {
         const int t = first_tree + i * tree_stride;

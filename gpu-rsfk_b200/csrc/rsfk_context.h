@@ -109,7 +109,6 @@ struct Context {
     enum Slot {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
-        PERM_FINAL_B, LEAF_START_B, LEAF_COUNT_B,
         SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
         RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
         LANE_IDX, LANE_DIST,
@@ -140,27 +139,6 @@ struct Context {
         }
     }
     std::vector<cudaEvent_t> level_ev; // two per tree level, reused by every tree
-    // A forest overlaps the bucket KNN of tree t (second stream) with the build
-    // of tree t+1 (main stream); trees alternate between two result buffers.
-    int result_buf = 0;
-    cudaStream_t aux = nullptr;
-    cudaEvent_t ev_tree[2] = {nullptr, nullptr}, ev_knn[2] = {nullptr, nullptr}, ev_join = nullptr;
-    bool ensure_aux()
-    {
-        if (aux) return true;
-        // lowest priority: CTAs of the (latency-bound) tree kernels on the main
-        // stream are placed before pending bucket-KNN CTAs
-        int least = 0, greatest = 0;
-        cudaDeviceGetStreamPriorityRange(&least, &greatest);
-        if (!check(cudaStreamCreateWithPriority(&aux, cudaStreamNonBlocking, least), "aux stream")) return false;
-        for (int i = 0; i < 2; ++i) {
-            cudaEventCreateWithFlags(&ev_tree[i], cudaEventDisableTiming);
-            cudaEventCreateWithFlags(&ev_knn[i], cudaEventDisableTiming);
-        }
-        cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming);
-        return true;
-    }
-
     bool fail(int code, const std::string& msg)
     {
         if (status == RSFK_OK) { status = code; message = msg; }
@@ -226,13 +204,6 @@ struct Context {
         ann_ev_pending = false;
         for (auto& e : level_ev) cudaEventDestroy(e);
         level_ev.clear();
-        for (int i = 0; i < 2; ++i) {
-            if (ev_tree[i]) cudaEventDestroy(ev_tree[i]);
-            if (ev_knn[i]) cudaEventDestroy(ev_knn[i]);
-            ev_tree[i] = ev_knn[i] = nullptr;
-        }
-        if (ev_join) { cudaEventDestroy(ev_join); ev_join = nullptr; }
-        if (aux) { cudaStreamDestroy(aux); aux = nullptr; }
         if (owns_stream && stream) { cudaStreamDestroy(stream); stream = nullptr; }
     }
 };
@@ -252,7 +223,7 @@ bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K);
 // n list entries set to empty: index -1, distance +inf
 bool fill_empty_lists(Context& ctx, int* d_idx, float* d_dist, long long n);
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
-                int* d_idx, float* d_dist, bool on_aux_stream = false);
+                int* d_idx, float* d_dist);
 // Query lists (rows of d_idx/d_dist, NQ x K, indices of base points) merged with the
 // bucket of base points each query is routed to.
 bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_queries, int NQ, int D,

@@ -885,10 +885,10 @@ bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K)
 }
 
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
-                int* d_idx, float* d_dist, bool on_aux_stream)
+                int* d_idx, float* d_dist)
 {
     (void)N;
-    cudaStream_t launch_stream = on_aux_stream ? ctx.aux : ctx.stream;
+    cudaStream_t launch_stream = ctx.stream;
     if (!check_k(ctx, K)) return false;
     if (tree.n_leaves <= 0) return true;
     const size_t budget = 200 * 1024;

@@ -852,7 +852,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     int* perm[2];
     perm[0] = (int*)ctx.scratch(Context::PERM_A, sizeof(int) * (size_t)N);
     perm[1] = (int*)ctx.scratch(Context::PERM_B, sizeof(int) * (size_t)N);
-    int* perm_final = (int*)ctx.scratch(ctx.result_buf ? Context::PERM_FINAL_B : Context::PERM_FINAL, sizeof(int) * (size_t)N);
+    int* perm_final = (int*)ctx.scratch(Context::PERM_FINAL, sizeof(int) * (size_t)N);
     unsigned* side_bits = (unsigned*)ctx.scratch(Context::SIDE_BITS, sizeof(unsigned) * (size_t)chunk_cap * CHUNK_WORDS);
     int* chunk_node[2];
     chunk_node[0] = (int*)ctx.scratch(Context::CHUNK_NODE_A, sizeof(int) * (size_t)chunk_cap);
@@ -872,8 +872,8 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     if (const char* e = getenv("RSFK_SUBTREE_LIMIT")) small_limit = atoi(e) < small_limit ? atoi(e) : small_limit;
     const int small_cap = node_cap;
     Node* small_nodes = (Node*)ctx.scratch(Context::SMALL_NODES, sizeof(Node) * (size_t)small_cap);
-    int* leaf_start = (int*)ctx.scratch(ctx.result_buf ? Context::LEAF_START_B : Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
-    int* leaf_count = (int*)ctx.scratch(ctx.result_buf ? Context::LEAF_COUNT_B : Context::LEAF_COUNT, sizeof(int) * (size_t)leaf_cap);
+    int* leaf_start = (int*)ctx.scratch(Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
+    int* leaf_count = (int*)ctx.scratch(Context::LEAF_COUNT, sizeof(int) * (size_t)leaf_cap);
     LevelCounters* cnt = (LevelCounters*)ctx.scratch(Context::COUNTERS, sizeof(LevelCounters));
     // tree index: a row per node that is split; with no side ever dissolving that is one
     // row less than there are leaves, dissolving sides add chain rows
