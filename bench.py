@@ -567,7 +567,7 @@ def run_ann(args, w):
     dom = max((n for n in phases if n != "tree_build_host_observed"), key=lambda n: phases[n]["total_ms"])
     kernel_of = {"tree_project": "k_project_wide", "tree_subtrees": "k_subtree",
                  "query_route": "k_planes + k_route + k_leaf_offsets + k_place_queries",
-                 "query_update": "k_ann_bucket"}
+                 "query_update": "k_ann_leaf (k_ann_bucket where the largest leaf does not fit shared memory)"}
     roofline = dict(bound="hbm", kernel=kernel_of[dom], achieved=phases[dom]["gbs"], peak=peak_gbs, unit="GB/s",
                     frac=(phases[dom]["gbs"] or 0) / peak_gbs,
                     peak_kind="measured" if "hbm_gbs" in peaks else "fallback", traffic=None,
