@@ -17,7 +17,13 @@
  * exploration sweep, and the tree rules (split side with the root's serial and
  * the other nodes' lane-strided offset, minimum side size, leaf sizes) are all
  * checked against outputs of the reference binary itself (fixtures under
- * tests/golden/, produced by tests/golden/make_ref_golden.py).
+ * tests/golden/, produced by tests/golden/make_ref_golden.py).  The query
+ * (base/query) update is checked slot for slot against the reference binary
+ * run over its own base points (tests/golden/make_ref_ann_golden.py), the only
+ * shape its query driver handles within bounds; the descent of a query that is
+ * not a base point is pinned through its parts (the split rule above, the
+ * follow-the-sibling rule read from build_tree_update_parents_ann.cu:150-160),
+ * not end to end.
  */
 #include <float.h>
 #include <math.h>
