@@ -88,6 +88,48 @@ def build_knn_graph(engine, points, K, n_trees, min_children, max_children, max_
     return own_idx[:end - begin], own_dst[:end - begin], begin, end
 
 
+def search_queries(engine, points, queries, K, n_trees, min_children, max_children, max_depth=5000,
+                   seed=0, group=None):
+    """The query (base/query) search sharded like the graph build: every rank holds
+    all base points and all queries, builds trees g, g+G, ... over the base points
+    (tree t with seed ``seed + t``) and updates a list for every query from them;
+    one all-to-all hands rank q the partial lists of the query rows it owns and a
+    merge keeps the K best.  Returns ``(idx_own, dist_own, row_begin, row_end)``
+    for this rank's query rows; the lists equal a single rank's bit for bit.
+
+    ``engine`` supplies ``init_lists, forest_ann, merge_lists`` with the signatures
+    of ``DeviceForest``.
+    """
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    NQ = queries.shape[0]
+    dev = queries.device
+    idx, dst = engine.init_lists(NQ, K, dev, False)
+    mine = tree_share(n_trees, rank, world)
+    if mine > 0:
+        engine.forest_ann(points, queries, idx, dst, mine, min_children, max_children, max_depth, seed,
+                          first_tree=rank, tree_stride=world)
+    begin, end = owned_rows(NQ, rank, world)
+    if world == 1:
+        return idx, dst, begin, end
+    blk = row_block(NQ, world)
+    pad = blk * world - NQ
+    if pad:
+        pi, pd = engine.init_lists(pad, K, dev, False)
+        idx = torch.cat([idx, pi])
+        dst = torch.cat([dst, pd])
+    recv_idx = torch.empty((world, blk, K), dtype=torch.int32, device=dev)
+    recv_dst = torch.empty((world, blk, K), dtype=torch.float32, device=dev)
+    dist.all_to_all_single(recv_idx.view(-1), idx.view(-1), group=group)
+    dist.all_to_all_single(recv_dst.view(-1), dst.view(-1), group=group)
+    del idx, dst
+    own_idx = torch.empty((blk, K), dtype=torch.int32, device=dev)
+    own_dst = torch.empty((blk, K), dtype=torch.float32, device=dev)
+    engine.merge_lists([recv_idx[g] for g in range(world)], [recv_dst[g] for g in range(world)],
+                       own_idx, own_dst)
+    return own_idx[:end - begin], own_dst[:end - begin], begin, end
+
+
 def gather_graph(idx_own, dist_own, N, group=None):
     """All ranks' owned rows concatenated into the full [N, K] graph (every rank)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1

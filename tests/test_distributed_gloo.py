@@ -36,6 +36,17 @@ class OracleEngine(object):
         idx.copy_(torch.from_numpy(i))
         dst.copy_(torch.from_numpy(d))
 
+    def forest_ann(self, points, queries, idx, dst, n_trees, min_children, max_children, max_depth=5000,
+                   seed=0, first_tree=0, tree_stride=1):
+        X, Q = points.numpy(), queries.numpy()
+        i, d = idx.numpy(), dst.numpy()
+        for k in range(n_trees):
+            t = first_tree + k * tree_stride
+            tr = self.orc.build_tree_route(X, Q, min_children, max_children, max_depth, seed + t)
+            i, d = self.orc.ann_bucket_knn(X, Q, idx.shape[1], tr["perm"], tr["q_start"], tr["q_count"], i, d)
+        idx.copy_(torch.from_numpy(i))
+        dst.copy_(torch.from_numpy(d))
+
     def merge_lists(self, idx_lists, dist_lists, out_idx, out_dist):
         i, d = self.orc.merge_lists([t.numpy() for t in idx_lists], [t.numpy() for t in dist_lists])
         out_idx.copy_(torch.from_numpy(i))
@@ -78,6 +89,31 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
+def _queries(NQ=703, D=12):
+    return torch.from_numpy(np.random.RandomState(2).uniform(0, 1, (NQ, D)).astype(np.float32))
+
+
+def _query_params():
+    return dict(K=6, n_trees=5, min_children=7, max_children=14, seed=11)
+
+
+def _query_worker(rank, world, port, out_dir):
+    for p in (ROOT, os.path.join(ROOT, "gpu-rsfk_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from gpu_rsfk import distributed as rdist
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    try:
+        X, Q = _points(), _queries()
+        oi, od, begin, end = rdist.search_queries(OracleEngine(), X, Q, **_query_params())
+        assert (begin, end) == rdist.owned_rows(Q.shape[0], rank, world)
+        fi, fd = rdist.gather_graph(oi, od, Q.shape[0])
+        if rank == 0:
+            np.savez(os.path.join(out_dir, "q%d.npz" % world), idx=fi.numpy(), dist=fd.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -96,6 +132,18 @@ def test_sharded_build_equals_single_rank(tmp_path, world):
     z = np.load(os.path.join(str(tmp_path), "w%d.npz" % world))
     np.testing.assert_array_equal(z["idx"], si.numpy())
     np.testing.assert_array_equal(z["dist"], sd.numpy())
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_query_search_equals_single_rank(tmp_path, world):
+    from gpu_rsfk import distributed as rdist
+    X, Q = _points(), _queries()
+    si, sd, b, e = rdist.search_queries(OracleEngine(), X, Q, **_query_params())
+    assert (b, e) == (0, Q.shape[0])
+    mp.spawn(_query_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    z = np.load(os.path.join(str(tmp_path), "q%d.npz" % world))
+    np.testing.assert_array_equal(z["idx"], si.numpy())
+    np.testing.assert_array_equal(z["dist"].view(np.int32), sd.numpy().view(np.int32))
 
 
 def test_tree_and_row_sharding_helpers():

@@ -25,8 +25,11 @@ X = torch.from_numpy(np.random.RandomState(3).uniform(0, 1, (30011, 48)).astype(
 eng = DeviceForest(dev)
 oi, od, b, e = rdist.build_knn_graph(eng, X, 16, 7, 17, 34, 5000, 11, 2, True)
 fi, fd = rdist.gather_graph(oi, od, X.shape[0])
+Q = torch.from_numpy(np.random.RandomState(4).uniform(0, 1, (9001, 48)).astype(np.float32)).to(dev)
+qi, qd, qb, qe = rdist.search_queries(eng, X, Q, 16, 7, 17, 34, 5000, 11)
+gqi, gqd = rdist.gather_graph(qi, qd, Q.shape[0])
 if rank == 0:
-    np.savez(%(out)r, idx=fi.cpu().numpy(), dist=fd.cpu().numpy())
+    np.savez(%(out)r, idx=fi.cpu().numpy(), dist=fd.cpu().numpy(), q_idx=gqi.cpu().numpy(), q_dist=gqd.cpu().numpy())
 dist.barrier()
 dist.destroy_process_group()
 '''
@@ -52,3 +55,8 @@ def test_two_gpu_build_equals_single_gpu(tmp_path):
     z = np.load(out)
     np.testing.assert_array_equal(z["idx"], si.cpu().numpy())
     np.testing.assert_array_equal(z["dist"], sd.cpu().numpy())
+    # the query search, sharded the same way
+    Q = torch.from_numpy(np.random.RandomState(4).uniform(0, 1, (9001, 48)).astype(np.float32)).to(dev)
+    qi, qd, _, _ = rdist.search_queries(DeviceForest(dev), X, Q, 16, 7, 17, 34, 5000, 11)
+    np.testing.assert_array_equal(z["q_idx"], qi.cpu().numpy())
+    np.testing.assert_array_equal(z["q_dist"], qd.cpu().numpy())
