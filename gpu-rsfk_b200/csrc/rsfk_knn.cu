@@ -353,6 +353,69 @@ k_bucket_knn(const float* __restrict__ pts, int D, int K, const int* __restrict_
 }
 
 // ---------------------------------------------------------------------------
+// Leaf-bucket KNN for few dimensions (D <= 16), leaves of any size whose rows fit
+// shared memory.  With so few dimensions a distance costs less than a trip
+// through a shared-memory tile: the leaf's rows are staged once, every warp owns
+// rows warp, warp+8, ... and computes the distances of its row to 32 leaf members
+// at a time (one pair per lane, the arithmetic of small_d_dist), feeding them
+// straight into the row's list, which is read and written once per tree.  Each
+// pair is evaluated from both ends (d(a,b) and d(b,a) carry the same bits).
+// ---------------------------------------------------------------------------
+template <int KPL>
+__global__ void __launch_bounds__(KNN_THREADS, 3)
+k_bucket_knn_lowd(const float* __restrict__ pts, int D, int K, const int* __restrict__ perm,
+                  const int* __restrict__ leaf_start, const int* __restrict__ leaf_count,
+                  int* __restrict__ knn_idx, float* __restrict__ knn_dist, int max_leaf)
+{
+    extern __shared__ float4 smem4[];
+    float* X = reinterpret_cast<float*>(smem4);                  // [max_leaf][D]
+    int* ids = reinterpret_cast<int*>(X + (size_t)max_leaf * D); // [max_leaf]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int leaf = blockIdx.x;
+    const int m = min(leaf_count[leaf], max_leaf);
+    const int* ids_g = perm + leaf_start[leaf];
+    for (int r = threadIdx.x; r < m; r += blockDim.x) ids[r] = ids_g[r];
+    __syncthreads();
+    WarpList<KPL> Lnext;
+    if (warp < m) {
+        const int first = ids[warp];
+        Lnext.load_raw(knn_idx + (size_t)first * K, knn_dist + (size_t)first * K, K, lane);
+    }
+    for (int e = threadIdx.x; e < m * D; e += blockDim.x) {
+        const int r = e / D;
+        X[e] = __ldg(pts + (size_t)ids[r] * D + (e - r * D));
+    }
+    __syncthreads();
+    for (int r = warp; r < m; r += KNN_WARPS) {
+        const int self = ids[r];
+        WarpList<KPL> L = Lnext;
+        L.refresh_threshold(K);
+        if (r + KNN_WARPS < m) {
+            const int nxt = ids[r + KNN_WARPS];
+            Lnext.load_raw(knn_idx + (size_t)nxt * K, knn_dist + (size_t)nxt * K, K, lane);
+        }
+        const float* xr = X + (size_t)r * D;
+        bool changed = false;
+        for (int c0 = 0; c0 < m; c0 += 32) {
+            const int j = c0 + lane;
+            float cd = CUDART_INF_F;
+            int ci = -1;
+            if (j < m && j != r) {
+                cd = small_d_dist_any(xr, X + (size_t)j * D, D);
+                ci = ids[j];
+            }
+            unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(cd, ci));
+            while (mask) {
+                const int b = __ffs(mask) - 1;
+                mask &= mask - 1;
+                changed |= L.try_insert(__shfl_sync(RSFK_FULL, cd, b), __shfl_sync(RSFK_FULL, ci, b), K, lane);
+            }
+        }
+        if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Exploration sweep: one warp per point.  Candidates old[old[p][i]][k] that
 // are not already in p's row are queued; every 32 queued candidates are
 // evaluated together (each lane owns dimensions lane, lane+32, ... of all 32
@@ -891,6 +954,21 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     cudaStream_t launch_stream = ctx.stream;
     if (!check_k(ctx, K)) return false;
     if (tree.n_leaves <= 0) return true;
+    // few dimensions: every leaf's rows fit shared memory, distances are computed where they are used
+    if (D <= 16 && (sizeof(float) * D + sizeof(int)) * (size_t)tree.max_leaf <= 72 * 1024) {
+        const size_t smem = (sizeof(float) * D + sizeof(int)) * (size_t)tree.max_leaf;
+        RSFK_DISPATCH_KPL(K, {
+            auto kern = k_bucket_knn_lowd<KPL>;
+            if (smem > 48 * 1024 &&
+                !ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                           "bucket_knn smem attribute"))
+                return false;
+            kern<<<tree.n_leaves, KNN_THREADS, smem, ctx.stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
+                                                                  tree.leaf_count, d_idx, d_dist, tree.max_leaf);
+        });
+        count_launches(1);
+        return ctx.check(cudaGetLastError(), "bucket_knn launch");
+    }
     const size_t budget = 200 * 1024;
     auto bytes = [&](int B, int two) {
         return sizeof(float) * ((size_t)B * (B + 1) + (size_t)(two ? 2 : 1) * B * D) + sizeof(int) * (size_t)(two ? 2 : 1) * B;
