@@ -173,15 +173,21 @@ void publish(const Context& c)
 // rows as one sequence (the row of a point is the K smallest distinct of everything
 // it met, in whatever order).  Three lanes by default: two sometimes fall into step
 // with each other (both in the same phase at the same time) and then gain nothing.
-// RSFK_LANES overrides (1 = off, at most 4).  list_rows x K is the size of one list.
-int forest_lanes(const rsfk_ctx* h, int n_trees, size_t N, size_t list_rows, int K)
+// Lanes pay where a tree's kernels are short (a tree level of C2 takes 80 us, about as
+// long as the host's round trip between levels); where every kernel already fills the GPU
+// for a millisecond or more the sequences only compete for cache (measured: 1 M x 960
+// 3.7 -> 4.7 s, 20 M x 128 22.2 -> 23.8 s with three lanes), so by default lanes are used up
+// to 2^28 coordinates (1 GiB of points).  rsfk_ctx_set_lanes or RSFK_LANES set the number
+// outright (1 = off, at most 4).  list_rows x K is the size of one list.
+int forest_lanes(const rsfk_ctx* h, int n_trees, size_t N, int D, size_t list_rows, int K)
 {
-    static const int by_default = [] {
+    static const int by_env = [] {
         const char* e = getenv("RSFK_LANES");
-        const int v = e ? atoi(e) : 3;
-        return v < 1 ? 1 : (v > 4 ? 4 : v);
+        const int v = e ? atoi(e) : 0;
+        return v < 0 ? 0 : (v > 4 ? 4 : v);
     }();
-    int g = h->lanes_wanted > 0 ? h->lanes_wanted : by_default;
+    int g = h->lanes_wanted > 0 ? h->lanes_wanted : by_env;
+    if (g == 0) g = (N * (size_t)D <= ((size_t)1 << 28)) ? 3 : 1;
     while (g > 1 && n_trees < 2 * g) --g; // at least two trees per lane
     // every lane holds a list of its own and tree scratch (about 64 bytes per point):
     // stay within half of the memory that is free now
@@ -345,7 +351,7 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
     Context& c = h->c;
     {
         static const bool single = getenv("RSFK_TIMELINE") != nullptr;
-        const int G = single ? 1 : forest_lanes(h, n_trees, (size_t)N, (size_t)N, K);
+        const int G = single ? 1 : forest_lanes(h, n_trees, (size_t)N, D, (size_t)N, K);
         if (G > 1)
             return run_forest_lanes(h, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
                                     max_children, max_depth, seed, d_idx, d_dist, log_forest, verbose,
@@ -424,7 +430,7 @@ bool run_forest_ann(rsfk_ctx* h, const float* d_points, int N, const float* d_qu
     {
         // lanes only on request (rsfk_ctx_set_lanes): the query update is issue-bound and takes
         // most of a tree's time here, so sequences side by side gain nothing (measured)
-        const int G = h->lanes_wanted > 1 ? forest_lanes(h, n_trees, (size_t)N, (size_t)NQ, K) : 1;
+        const int G = h->lanes_wanted > 1 ? forest_lanes(h, n_trees, (size_t)N, D, (size_t)NQ, K) : 1;
         if (G > 1)
             return run_forest_lanes(h, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
                                     max_children, max_depth, seed, d_idx, d_dist, nullptr, verbose, d_queries, NQ);
