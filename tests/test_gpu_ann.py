@@ -232,3 +232,39 @@ def test_query_lists_given_by_the_caller_are_merged(oracle):
     ri, rd = oracle.ann_forest(X, Q, K, 2, 9, 18, seed=3, idx=i0, dist=d0)
     np.testing.assert_array_equal(idx, ri)
     np.testing.assert_array_equal(dist.view(np.int32), rd.view(np.int32))
+
+
+def test_query_search_edge_cases(indexed, oracle):
+    import torch
+    from gpu_rsfk import RSFK, RSFKLibraryError
+    # one base point: every query row holds it, with its distance, and nothing else
+    X = _uniform(1, 5, 1)
+    Q = _uniform(7, 5, 2)
+    idx, dist = RSFK(random_state=0).find_nearest_neighbors_ann(X, Q, 3, n_trees=2, ensure_valid_indices=False)
+    assert (idx[:, 0] == 0).all() and (idx[:, 1:] == -1).all()
+    want = np.array([oracle.dist_sqr(q, X[0]) for q in Q], np.float32)
+    np.testing.assert_array_equal(dist[:, 0].view(np.int32), want.view(np.int32))
+    assert np.isinf(dist[:, 1:]).all()
+    # one query, one dimension, fewer base points than K
+    X1, Q1 = _uniform(40, 1, 3), _uniform(1, 1, 4)
+    i1, d1 = RSFK(random_state=0).find_nearest_neighbors_ann(X1, Q1, 64, n_trees=3)
+    ri, rd = oracle.ann_forest(X1, Q1, 64, 3, 65, 130, seed=0)
+    np.testing.assert_array_equal(i1, ri)
+    assert (i1[0, :40] >= 0).all() and (i1[0, 40:] == -1).all()
+    # no tree at all: lists come back as given (canonical order)
+    didx, ddist = _dev(np.full((5, 4), -1, np.int32)), _dev(np.full((5, 4), np.inf, np.float32))
+    indexed.forest_ann(_dev(_uniform(100, 3, 5)), _dev(_uniform(5, 3, 6)), didx, ddist, 0, 4, 8)
+    torch.cuda.synchronize()
+    assert (didx.cpu().numpy() == -1).all()
+    # the largest supported K, and one beyond
+    Xk, Qk = _uniform(3000, 6, 7), _uniform(50, 6, 8)
+    ik, dk = RSFK(random_state=1).find_nearest_neighbors_ann(Xk, Qk, 256, n_trees=2)
+    rk, _ = oracle.ann_forest(Xk, Qk, 256, 2, 257, 514, seed=1)
+    np.testing.assert_array_equal(ik, rk)
+    with pytest.raises(RSFKLibraryError):
+        RSFK().find_nearest_neighbors_ann(Xk, Qk, 257, n_trees=1)
+    # shapes that do not agree are refused before the library is called
+    with pytest.raises(Exception):
+        RSFK().find_nearest_neighbors_ann(Xk, _uniform(5, 7, 9), 4, n_trees=1)
+    with pytest.raises(ValueError):
+        indexed.forest_ann(_dev(Xk), _dev(_uniform(5, 7, 9)), didx, ddist, 1, 4, 8)
