@@ -187,7 +187,12 @@ int forest_lanes(const rsfk_ctx* h, int n_trees, size_t N, int D, size_t list_ro
         return v < 0 ? 0 : (v > 4 ? 4 : v);
     }();
     int g = h->lanes_wanted > 0 ? h->lanes_wanted : by_env;
-    if (g == 0) g = (N * (size_t)D <= ((size_t)1 << 28)) ? 3 : 1;
+    if (g == 0) {
+        g = (N * (size_t)D <= ((size_t)1 << 28)) ? 3 : 1;
+        // a lane's own list and the final combination want a few trees to pay for them
+        // (eight ranks with six trees each: 46.3 ms with three lanes, 44.5 ms with one)
+        while (g > 1 && n_trees < 4 * g) --g;
+    }
     while (g > 1 && n_trees < 2 * g) --g; // at least two trees per lane
     // every lane holds a list of its own and tree scratch (about 64 bytes per point):
     // stay within half of the memory that is free now

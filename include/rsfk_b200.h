@@ -137,7 +137,8 @@ RSFK_EXPORT int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, 
 /* How many tree sequences ("lanes") a forest call of this context runs side by side on
  * the GPU, each on a stream of its own with lists of its own that are combined at the
  * end: 1..4, or 0 for the default (environment variable RSFK_LANES, else three where
- * N*D <= 2^28 and one above that; never more than n_trees/2).  The result does not depend
+ * N*D <= 2^28 and the call has at least twelve trees, two from eight trees, else one; a
+ * number set here is used as long as every lane gets two trees).  The result does not depend
  * on it.  No reference counterpart (the
  * reference builds its trees one after another, src/rsfk.cu:2073-2088). */
 RSFK_EXPORT int rsfk_ctx_set_lanes(rsfk_ctx* ctx, int lanes);
