@@ -439,7 +439,10 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
         o.chunk_base = 0;
         o.level = child_level;
         o.rec = 0;
-        if (lane == 0) ref[k] = o.rec = new_record(records, rec_cap, cnt);
+        // an only child takes over its parent's row: both sides of the parent lead to it, so a
+        // query loses nothing by starting at the child's split, and a node that fails to split
+        // again and again (coincident points) does not use up a row per attempt
+        if (lane == 0) ref[k] = o.rec = (ch.n == 1) ? nd.rec : new_record(records, rec_cap, cnt);
         if (small) {
             if (lane == 0) {
                 const int slot = atomicAdd(&cnt->n_small, 1);
@@ -470,7 +473,7 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
     if (lane == 0) {
         split[node].n_left = nL;
         split[node].flags = flags;
-        file_refs(records, nd.rec, ch.n, ref);
+        if (ch.n == 2 || ch.leaf[0]) file_refs(records, nd.rec, ch.n, ref); // else the child rewrites the row
     }
 }
 
@@ -727,14 +730,14 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
                         o.start = ch.start[k];   o.count = ch.count[k];
                         o.pstart = ch.pstart[k]; o.pcount = ch.pcount[k];
                         o.tbl = child_table_row(table, n_table, nd.tbl, ch.side[k]);
-                        ref[k] = o.rec = new_record(records, rec_cap, cnt);
+                        ref[k] = o.rec = (ch.n == 1) ? nd.rec : new_record(records, rec_cap, cnt);
                         sOpen[nxt][slot] = o;
                     } else {
                         cnt->error = RSFK_ERR_OVERFLOW;
                     }
                 }
             }
-            if (lane == 0) file_refs(records, nd.rec, ch.n, ref);
+            if (lane == 0 && (ch.n == 2 || ch.leaf[0])) file_refs(records, nd.rec, ch.n, ref);
         }
         __syncthreads();
         n_open = min(sCount[0], SUB_NODES);
@@ -875,9 +878,9 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     int* leaf_start = (int*)ctx.scratch(Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
     int* leaf_count = (int*)ctx.scratch(Context::LEAF_COUNT, sizeof(int) * (size_t)leaf_cap);
     LevelCounters* cnt = (LevelCounters*)ctx.scratch(Context::COUNTERS, sizeof(LevelCounters));
-    // tree index: a row per node that is split; with no side ever dissolving that is one
-    // row less than there are leaves, dissolving sides add chain rows
-    const int rec_cap = ctx.keep_index ? 4 * leaf_cap + 64 : 0;
+    // tree index: a row per node with two children (an only child reuses its parent's row),
+    // i.e. one row less than there are leaves
+    const int rec_cap = ctx.keep_index ? leaf_cap + 64 : 0;
     int4* records = ctx.keep_index ? (int4*)ctx.scratch(Context::RECORDS, sizeof(int4) * (size_t)rec_cap) : nullptr;
     ctx.planes_ready = false;
     if (ctx.status != RSFK_OK) return false;
