@@ -945,6 +945,21 @@ int rsfk_dev_explore(rsfk_ctx* ctx, const float* d_points, int N, int D, int K, 
     return ctx->c.status;
 }
 
+int rsfk_dev_symmetrize_count(rsfk_ctx* ctx, int N, int K, const int* d_idx, long long* d_offsets, long long* nnz)
+{
+    RSFK_ENTER(ctx);
+    rsfk::symmetrize_count(ctx->c, d_idx, N, K, d_offsets, nnz);
+    return ctx->c.status;
+}
+
+int rsfk_dev_symmetrize_fill(rsfk_ctx* ctx, int N, int K, const int* d_idx, const float* d_dist,
+                             const long long* d_offsets, int* d_sym_idx, float* d_sym_dist)
+{
+    RSFK_ENTER(ctx);
+    rsfk::symmetrize_fill(ctx->c, d_idx, d_dist, N, K, d_offsets, d_sym_idx, d_sym_dist);
+    return ctx->c.status;
+}
+
 int rsfk_dev_merge_lists(rsfk_ctx* ctx, long long rows, int K, int G, const int* const* d_idx_lists,
                          const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist)
 {

@@ -111,7 +111,7 @@ struct Context {
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
         SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
         RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
-        LANE_IDX, LANE_DIST,
+        LANE_IDX, LANE_DIST, SYM_DEGREE, SYM_BLOCKS,
         N_SLOTS
     };
     // When set, tree_build keeps the tree index (TreeResult::records) that the
@@ -230,6 +230,10 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
                     int K, const TreeResult& tree, int* d_idx, float* d_dist);
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
                    int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0);
+// rsfk_graph.cu: symmetric closure of a K-NN graph as CSR (offsets are 64-bit, [N+1])
+bool symmetrize_count(Context& ctx, const int* d_idx, int N, int K, long long* d_offsets, long long* nnz_host);
+bool symmetrize_fill(Context& ctx, const int* d_idx, const float* d_dist, int N, int K, const long long* d_offsets,
+                     int* d_sym_idx, float* d_sym_dist);
 bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,
                  const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist);
 

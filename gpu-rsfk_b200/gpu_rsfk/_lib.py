@@ -101,6 +101,10 @@ def load():
     L.rsfk_dev_ann_bucket_knn.argtypes = [vp, vp, i, vp, i, i, i, vp, vp]
     L.rsfk_dev_forest_ann.restype = i
     L.rsfk_dev_forest_ann.argtypes = [vp, vp, i, vp, i, i, i, i, i, i, i, i, i, i, vp, vp]
+    L.rsfk_dev_symmetrize_count.restype = i
+    L.rsfk_dev_symmetrize_count.argtypes = [vp, i, i, vp, vp, ctypes.POINTER(ll)]
+    L.rsfk_dev_symmetrize_fill.restype = i
+    L.rsfk_dev_symmetrize_fill.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
     L.rsfk_explore_sweep_static.restype = i
     L.rsfk_explore_sweep_static.argtypes = [vp, i, i, i, vp, vp, vp]
     _lib = L

@@ -194,6 +194,26 @@ class DeviceForest(object):
                                               ctypes.cast(dp, ctypes.c_void_p), _ptr(out_idx), _ptr(out_dist))
         _lib.raise_on_status(code, "merge_lists")
 
+    def symmetrize(self, idx, dist=None):
+        """Symmetric closure of the K-NN graph ``idx`` ([N, K], -1 = empty) as CSR:
+        ``(offsets int64 [N+1], indices int32 [nnz], values float32 [nnz] or None)``;
+        row p holds p's neighbours and every q that lists p, ordered by index, with
+        the squared distance of the edge when ``dist`` is given."""
+        _want(idx, torch.int32, "idx")
+        if dist is not None:
+            _want(dist, torch.float32, "dist")
+        N, K = idx.shape
+        offsets = torch.empty(N + 1, dtype=torch.int64, device=idx.device)
+        nnz = ctypes.c_longlong(0)
+        code = self._lib.rsfk_dev_symmetrize_count(self._ctx, N, K, _ptr(idx), _ptr(offsets), ctypes.byref(nnz))
+        _lib.raise_on_status(code, "symmetrize_count")
+        indices = torch.empty(nnz.value, dtype=torch.int32, device=idx.device)
+        values = torch.empty(nnz.value, dtype=torch.float32, device=idx.device) if dist is not None else None
+        code = self._lib.rsfk_dev_symmetrize_fill(self._ctx, N, K, _ptr(idx), _ptr(dist), _ptr(offsets),
+                                                  _ptr(indices), _ptr(values))
+        _lib.raise_on_status(code, "symmetrize_fill")
+        return offsets, indices, values
+
     def stats(self):
         """Work counters of this context (synchronizes the stream)."""
         out = (ctypes.c_double * 13)()

@@ -192,6 +192,19 @@ RSFK_EXPORT int rsfk_dev_forest_ann(rsfk_ctx* ctx, const float* d_points, int N,
                         int min_children, int max_children, int max_depth, int seed,
                         int* d_idx, float* d_dist);
 
+/* Symmetric closure of a K-NN graph in CSR form: row p holds p's valid entries and every
+ * q that lists p without being listed by p, ordered by neighbour index (reference: the
+ * kernels symmetric_knn_graph_edge_count / _offset / _add_edges, src/rsfk.cu:1229-1299,
+ * which leave a row in atomic arrival order).  Two steps, so that the caller owns the
+ * output: _count writes the row offsets d_offsets[N+1] (64-bit) and returns the number
+ * of entries in *nnz (host); _fill writes d_sym_idx[nnz] and, when d_sym_dist is not
+ * NULL, the squared distance of every entry taken from d_dist.  Rows of d_idx must hold
+ * distinct indices (as every list this library returns does); -1 entries are skipped. */
+RSFK_EXPORT int rsfk_dev_symmetrize_count(rsfk_ctx* ctx, int N, int K, const int* d_idx,
+                              long long* d_offsets, long long* nnz);
+RSFK_EXPORT int rsfk_dev_symmetrize_fill(rsfk_ctx* ctx, int N, int K, const int* d_idx, const float* d_dist,
+                             const long long* d_offsets, int* d_sym_idx, float* d_sym_dist);
+
 /* out = the K smallest distinct entries of G canonical lists per row.
  * d_idx_lists/d_dist_lists are HOST arrays of G device pointers (G <= 16).
  * No reference counterpart (the reference is single-GPU); used to combine the

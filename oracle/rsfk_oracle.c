@@ -681,6 +681,76 @@ ORC_API void orc_bruteforce_ann(const float* points, int N, const float* queries
 }
 
 /* ------------------------------------------------------------------------- */
+/* Symmetric closure of the graph                                             */
+/* ------------------------------------------------------------------------- */
+
+/* Row p of the result: p's valid entries and every q that lists p without being
+ * listed by p (src/rsfk.cu:1229-1299: symmetric_knn_graph_edge_count counts one
+ * entry per listed neighbour plus one in the neighbour's row when the edge is
+ * not mutual; symmetric_knn_graph_add_edges writes them).  Rows are ordered by
+ * neighbour index here (the reference leaves them in atomic arrival order);
+ * -1 entries are skipped.  offsets has N+1 entries; with sym_idx == NULL only
+ * the offsets are computed.  Returns the number of entries. */
+ORC_API long long orc_symmetrize(int N, int K, const int* idx, const float* dist, long long* offsets,
+                                 int* sym_idx, float* sym_dist)
+{
+    long long* deg = (long long*)calloc((size_t)N + 1, sizeof(long long));
+    for (int p = 0; p < N; ++p)
+        for (int k = 0; k < K; ++k) {
+            int q = idx[(size_t)p * K + k];
+            if (q < 0 || q >= N) continue;
+            deg[p]++;
+            if (q != p && !row_has(idx + (size_t)q * K, K, p)) deg[q]++;
+        }
+    long long run = 0;
+    for (int p = 0; p < N; ++p) { offsets[p] = run; run += deg[p]; }
+    offsets[N] = run;
+    if (sym_idx) {
+        long long* cur = (long long*)calloc((size_t)N + 1, sizeof(long long));
+        orc_entry* tmp;
+        for (int p = 0; p < N; ++p)
+            for (int k = 0; k < K; ++k) {
+                int q = idx[(size_t)p * K + k];
+                if (q < 0 || q >= N) continue;
+                float d = dist ? dist[(size_t)p * K + k] : 0.0f;
+                sym_idx[offsets[p] + cur[p]] = q;
+                if (sym_dist) sym_dist[offsets[p] + cur[p]] = d;
+                cur[p]++;
+                if (q != p && !row_has(idx + (size_t)q * K, K, p)) {
+                    sym_idx[offsets[q] + cur[q]] = p;
+                    if (sym_dist) sym_dist[offsets[q] + cur[q]] = d;
+                    cur[q]++;
+                }
+            }
+        /* order every row by neighbour index (entries of a row are distinct) */
+        long long longest = 0;
+        for (int p = 0; p < N; ++p) if (deg[p] > longest) longest = deg[p];
+        tmp = (orc_entry*)malloc(sizeof(orc_entry) * (size_t)(longest > 0 ? longest : 1));
+        for (int p = 0; p < N; ++p) {
+            long long L = deg[p];
+            for (long long e = 0; e < L; ++e) {
+                tmp[e].i = sym_idx[offsets[p] + e];
+                tmp[e].d = sym_dist ? sym_dist[offsets[p] + e] : 0.0f;
+            }
+            for (long long a = 1; a < L; ++a) { /* insertion sort by index */
+                orc_entry x = tmp[a];
+                long long b = a - 1;
+                while (b >= 0 && tmp[b].i > x.i) { tmp[b + 1] = tmp[b]; --b; }
+                tmp[b + 1] = x;
+            }
+            for (long long e = 0; e < L; ++e) {
+                sym_idx[offsets[p] + e] = tmp[e].i;
+                if (sym_dist) sym_dist[offsets[p] + e] = tmp[e].d;
+            }
+        }
+        free(tmp);
+        free(cur);
+    }
+    free(deg);
+    return run;
+}
+
+/* ------------------------------------------------------------------------- */
 /* Neighbour-of-neighbour exploration                                         */
 /* ------------------------------------------------------------------------- */
 

@@ -91,6 +91,9 @@ def lib():
             fn.restype = None
             fn.argtypes = [_f32, _f32, ctypes.c_int, ctypes.c_int, ctypes.c_int, _i32, _i32, _i32,
                            _i32, _f32]
+        L.orc_symmetrize.restype = ctypes.c_longlong
+        L.orc_symmetrize.argtypes = [ctypes.c_int, ctypes.c_int, _i32, ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_void_p, ctypes.c_void_p]
         L.orc_bruteforce_ann.restype = None
         L.orc_bruteforce_ann.argtypes = [_f32, ctypes.c_int, _f32, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_int, _i32, _f32]
@@ -215,6 +218,20 @@ def ann_forest(points, queries, K, n_trees, min_children, max_children, max_dept
         idx, dist = ann_bucket_knn(points, queries, K, tr["perm"], tr["q_start"], tr["q_count"],
                                    idx, dist)
     return idx, dist
+
+
+def symmetrize(idx, dist=None):
+    """Symmetric closure of a K-NN graph as CSR: (offsets int64 [N+1], indices, values or None)."""
+    idx = np.ascontiguousarray(idx, np.int32)
+    N, K = idx.shape
+    dist = None if dist is None else np.ascontiguousarray(dist, np.float32)
+    offsets = np.empty(N + 1, np.int64)
+    nnz = lib().orc_symmetrize(N, K, idx, None if dist is None else dist.ctypes.data, offsets.ctypes.data, None, None)
+    indices = np.empty(max(nnz, 1), np.int32)
+    values = np.empty(max(nnz, 1), np.float32) if dist is not None else None
+    lib().orc_symmetrize(N, K, idx, None if dist is None else dist.ctypes.data, offsets.ctypes.data,
+                         indices.ctypes.data, None if values is None else values.ctypes.data)
+    return offsets, indices[:nnz], (None if values is None else values[:nnz])
 
 
 def bruteforce_ann(points, queries, K):

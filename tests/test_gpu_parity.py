@@ -382,3 +382,35 @@ def test_one_dimension_and_no_trees_through_the_host_entry_point(oracle):
     assert L.rsfk_last_status() == 2
     np.testing.assert_array_equal(shuffled_i, before)
     L.rsfk_release_memory()
+
+
+@pytest.mark.parametrize("N,D,K", [(5000, 8, 10), (3000, 40, 33), (1, 3, 4), (20000, 3, 64), (9000, 16, 1)])
+def test_symmetric_closure_matches_oracle(forest, oracle, N, D, K):
+    """CSR of the graph united with its transpose: offsets, indices (ordered by
+    index) and the edges' squared distances equal the oracle's."""
+    import torch
+    X = _uniform(N, D, 61)
+    idx, dist = oracle.init_lists(N, K)
+    tr = oracle.build_tree(X, K + 1, 2 * K + 2, seed=5)
+    idx, dist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+    if N > 100:
+        idx[::7, K - 1] = -1                          # some empty slots
+        dist[::7, K - 1] = np.inf
+    off, ind, val = oracle.symmetrize(idx, dist)
+    d_off, d_ind, d_val = forest.symmetrize(_dev(idx), _dev(dist))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(d_off.cpu().numpy(), off)
+    np.testing.assert_array_equal(d_ind.cpu().numpy(), ind)
+    np.testing.assert_array_equal(d_val.cpu().numpy().view(np.int32), val.view(np.int32))
+    o2, i2, none = forest.symmetrize(_dev(idx))
+    torch.cuda.synchronize()
+    assert none is None
+    np.testing.assert_array_equal(i2.cpu().numpy(), ind)
+    # a hub: one point listed by everybody gets a long row
+    hub = np.full((N, 2), -1, np.int32)
+    hub[:, 0] = 0
+    ho, hi, _ = oracle.symmetrize(hub)
+    go, gi, _ = forest.symmetrize(_dev(hub))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(go.cpu().numpy(), ho)
+    np.testing.assert_array_equal(gi.cpu().numpy(), hi)

@@ -227,3 +227,31 @@ def test_query_forest_recall_grows_with_trees(oracle):
     np.testing.assert_allclose(bd, np.sort(d2, axis=1)[:, :K], rtol=1e-5, atol=1e-7)   # 1e-5 relative
     r = [oracle.recall(bi, oracle.ann_forest(X, Q, K, T, 9, 18, seed=2)[0]) for T in (1, 4, 16)]
     assert r[0] < r[1] < r[2] and r[2] > 0.9
+
+
+# ---------------------------------------------------------------- symmetric closure
+def test_symmetric_closure_is_the_union_with_the_transpose(oracle):
+    N, D, K = 400, 5, 6
+    X = _uniform(N, D, 21)
+    bi, bd, _ = oracle.bruteforce_knn(X, K)
+    bi[::13, 2] = -1                                   # empty slots are skipped
+    off, ind, val = oracle.symmetrize(bi, bd)
+    A = np.zeros((N, N), bool)
+    W = np.zeros((N, N), np.float32)
+    for p in range(N):
+        for k in range(K):
+            q = bi[p, k]
+            if q >= 0:
+                A[p, q] = True
+                W[p, q] = bd[p, k]
+    S = A | A.T
+    assert off[0] == 0 and off[-1] == S.sum() == len(ind)
+    for p in range(N):
+        row = ind[off[p]:off[p + 1]]
+        np.testing.assert_array_equal(row, np.nonzero(S[p])[0])             # ordered by index, distinct
+        for q, v in zip(row, val[off[p]:off[p + 1]]):
+            assert v == (W[p, q] if A[p, q] else W[q, p])                     # the edge's own distance
+    off2, ind2, none = oracle.symmetrize(bi)
+    np.testing.assert_array_equal(off2, off)
+    np.testing.assert_array_equal(ind2, ind)
+    assert none is None
