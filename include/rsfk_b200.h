@@ -87,6 +87,9 @@ typedef struct rsfk_ctx rsfk_ctx;
 
 /* A context owns scratch memory on `device` and issues all work on `stream`
  * (a cudaStream_t passed as void*; NULL is the legacy default stream).
+ * rsfk_dev_forest and rsfk_dev_forest_ann may in addition run tree sequences on
+ * streams and host threads of their own (rsfk_ctx_set_lanes); they start after
+ * everything queued on `stream` and the call returns when they are done.
  * No reference counterpart: the reference hard-codes device 0 and the default
  * stream (src/rsfk.cu:679-684). */
 RSFK_EXPORT rsfk_ctx* rsfk_ctx_create(int device, void* stream);
