@@ -703,14 +703,37 @@ void pymodule_rsfk_knn_ann(int n_trees, int num_neighbors, int N, int NQ, int D,
     const double t0 = now_s();
     ok = ok && h2d(d_points, points, pts_bytes, "H2D points");
     ok = ok && h2d(d_queries, query_points, q_bytes, "H2D query points");
-    ok = ok && h2d(d_idx, knn_indices, sizeof(int) * list_elems, "H2D indices");
-    ok = ok && h2d(d_dist, knn_sqr_distances, sizeof(float) * list_elems, "H2D distances");
-    ok = ok && rsfk::sort_rows(c, d_idx, d_dist, NQ, K);
-    ok = ok && c.check(cudaStreamSynchronize(c.stream), "H2D");
     const double t1 = now_s();
-    if (ok && VERBOSE >= 2) printf("Allocate+copy points and KNN takes: %lf seconds\n", t1 - t0);
+    if (ok && VERBOSE >= 2) printf("Allocate+copy points takes: %lf seconds\n", t1 - t0);
+    // The trees work on lists of their own that start empty on the device; the caller's lists
+    // travel beside them on a thread of their own and are combined with the result at the end
+    // (a row is the K smallest distinct of everything it met, in whatever order).
+    int* d_work_idx = (int*)c.scratch(Context::LANE_IDX, sizeof(int) * list_elems);
+    float* d_work_dist = (float*)c.scratch(Context::LANE_DIST, sizeof(float) * list_elems);
+    ok = ok && d_work_idx && d_work_dist && rsfk::fill_empty_lists(c, d_work_idx, d_work_dist, (long long)list_elems);
+    bool lists_up = true;
+    std::thread uploader;
+    if (ok)
+        uploader = std::thread([&] {
+            cudaSetDevice(dev_id);
+            lists_up = g_copier.copy(d_idx, knn_indices, sizeof(int) * list_elems, true, dev_id) &&
+                       g_copier.copy(d_dist, knn_sqr_distances, sizeof(float) * list_elems, true, dev_id);
+        });
+    // lanes, when asked for, keep their lists in the same scratch slots: one sequence here
+    const int lanes_before = h->lanes_wanted;
+    h->lanes_wanted = 1;
     ok = ok && run_forest_ann(h, d_points, N, d_queries, NQ, D, K, n_trees, 0, 1, MIN_TREE_CHILD,
-                              MAX_TREE_CHILD, MAX_DEPTH, RANDOM_STATE, d_idx, d_dist, VERBOSE);
+                              MAX_TREE_CHILD, MAX_DEPTH, RANDOM_STATE, d_work_idx, d_work_dist, VERBOSE);
+    h->lanes_wanted = lanes_before;
+    if (uploader.joinable()) uploader.join();
+    if (ok && !lists_up) ok = c.fail(RSFK_ERR_CUDA, "H2D lists failed");
+    ok = ok && rsfk::sort_rows(c, d_idx, d_dist, NQ, K);
+    if (ok) {
+        const int* ip[2] = {d_idx, d_work_idx};
+        const float* dp[2] = {d_dist, d_work_dist};
+        ok = rsfk::merge_lists(c, NQ, K, 2, ip, dp, d_idx, d_dist) &&
+             c.check(cudaStreamSynchronize(c.stream), "list combination");
+    }
     const double t2 = now_s();
     if (ok && VERBOSE >= 1) printf("Creating RSFK forest and updating the query lists takes %lf seconds\n", t2 - t1);
     // outputs are written only when every step succeeded
