@@ -239,7 +239,7 @@ def run_ours(args, w):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = os.environ.get("RSFK_NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
+        os.environ.setdefault("NCCL_DEBUG", "WARN")   # NCCL prints to stderr; stdout stays the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     N, D, K = args.points or w["N"], w["D"], w["K"]
@@ -319,6 +319,14 @@ def run_ours(args, w):
     phases["bucket_knn"] = dict(
         launches=trees_run, ms_per_launch=knn_ms / trees_run,
         bytes_per_launch=4.0 * N * D + 4.0 * N + 2 * 8.0 * N * K)
+    tc_launches = tot.get("tc_launches", 0)
+    if tc_launches > 0 and knn_ms > 0:
+        # tensor-core bucket kernel: useful flops = 2*D*sum(leaf size^2), the contraction counted once,
+        # against half of the measured dense bf16 rate (the TF32 ceiling)
+        flops = tot.get("tc_gram_flops", 0.0) / tc_launches
+        phases["bucket_knn"].update(
+            tensor_flops_per_launch=flops, tensor_tflops=flops / (knn_ms / trees_run * 1e-3) / 1e12,
+            filter_pass_share=tot.get("tc_pairs_passed", 0) / max(1.0, tot.get("tc_pairs_seen", 0)))
     # tree levels: the projection kernel (one launch per level) and the rest of the level work
     # (decide + scatter kernels, counter read-back by the host)
     proj_ms = tot.get("project_us", 0) / 1e3
@@ -347,7 +355,7 @@ def run_ours(args, w):
         p["gbs"] = p["bytes_per_launch"] / (p["ms_per_launch"] * 1e-3) / 1e9 if p["ms_per_launch"] > 0 else None
         p["total_ms"] = p["ms_per_launch"] * p["launches"]
     dom = max((n for n in phases if n != "tree_level_rest"), key=lambda n: phases[n]["total_ms"])
-    kernel_of = {"bucket_knn": "k_bucket_knn (k_bucket_knn_tc where leaves exceed one shared-memory block)",
+    kernel_of = {"bucket_knn": "k_bucket_knn (SIMT)" if tc_launches == 0 else "k_bucket_knn_tc (tcgen05)",
                  "tree_project": "k_project_wide", "tree_level_rest": "k_decide + k_scatter + host read-back",
                  "tree_subtrees": "k_subtree", "explore": "k_explore", "merge_lists": "k_merge_lists"}
     traffic_unit = NCU_TRAFFIC_PER_POINT.get(dom)
@@ -355,19 +363,49 @@ def run_ours(args, w):
                     unit="GB/s", frac=(phases[dom]["gbs"] or 0) / peak_gbs, peak_kind=peak_kind,
                     traffic=(traffic_unit * {"explore": rows_own, "tree_project": lvl_pts / proj_n}.get(dom, N))
                     if traffic_unit and args.workload == "c2" else None,
+                    traffic_from="ncu capture of a 400 000-point case scaled by the points a launch processes "
+                                 "(an under-estimate where the L2 hit rate falls with N)"
+                    if traffic_unit and args.workload == "c2" else None,
                     algorithmic_bytes_per_launch=phases[dom]["bytes_per_launch"],
                     ms_per_launch=phases[dom]["ms_per_launch"])
+    tensor_roofline = None
+    if "tensor_tflops" in phases["bucket_knn"]:
+        tf32_peak = 0.5 * float(peaks.get("bf16_tflops", 1590.0))
+        b = phases["bucket_knn"]
+        tensor_roofline = dict(bound="tensor", kernel="k_bucket_knn_tc (tcgen05 kind::tf32)",
+                               achieved=b["tensor_tflops"], peak=tf32_peak, unit="TFLOP/s",
+                               frac=b["tensor_tflops"] / tf32_peak,
+                               peak_kind=("half of the measured bf16 rate" if "bf16_tflops" in peaks
+                                          else "half of the fallback bf16 rate"),
+                               flops_per_launch=b["tensor_flops_per_launch"], ms_per_launch=b["ms_per_launch"],
+                               hbm_achieved=b["gbs"], hbm_frac=(b["gbs"] or 0) / peak_gbs, traffic=None)
+        if dom == "bucket_knn":
+            roofline = tensor_roofline
 
     # ---- recall of the last build -----------------------------------------
     recall = None
-    if not args.no_recall:
-        full_idx, _ = rdist.gather_graph(own_idx, own_dst, N)
-        if rank == 0:
+    parity = None
+    if not args.no_recall or world > 1:
+        full_idx, full_dst = rdist.gather_graph(own_idx, own_dst, N)
+        if rank == 0 and not args.no_recall:
             nq = min(N, args.recall_queries)
             queries = np.sort(np.random.default_rng(w["seed"] + 1000).choice(N, nq, replace=False))
             truth = exact_knn_torch(X_dev, queries, K).cpu().numpy()
             recall = recall_of(truth, full_idx[torch.as_tensor(queries, device=dev)].cpu().numpy())
-        del full_idx
+        if world > 1:
+            # self-check, outside the timed region: the graph the ranks built together against
+            # the graph rank 0 builds alone (same seeds): they must be the same bits
+            if rank == 0:
+                si, sd, _, _ = rdist.build_knn_graph(engine, X_dev, K, w["trees"], w["min"], w["max"], 5000,
+                                                     w["seed"], w["sweeps"], True, single=True)
+                torch.cuda.synchronize()
+                same_i = int((si == full_idx).all(dim=1).sum().item())
+                same_d = int((sd.view(torch.int32) == full_dst.view(torch.int32)).all(dim=1).sum().item())
+                parity = {"rows": N, "rows_with_identical_indices": same_i, "rows_with_identical_distance_bits": same_d,
+                          "against": "the same build on rank 0 alone"}
+                del si, sd
+            dist.barrier()
+        del full_idx, full_dst
     del own_idx, own_dst
     torch.cuda.empty_cache()
 
@@ -392,11 +430,13 @@ def run_ours(args, w):
         out_i = torch.empty((rdist.row_block(N, world), K), dtype=torch.int32).pin_memory()
         out_d = torch.empty((rdist.row_block(N, world), K), dtype=torch.float32).pin_memory()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        xb, xe = rdist.owned_rows(N, rank, world)
         for i in range(args.e2e_steps + 1):
             if i == 1:
                 fence()
                 e0.record()
-            xd = X_host.to(dev, non_blocking=True)
+            # every rank uploads its own block of rows; an all-gather over NVLink completes the replica
+            xd = rdist.replicate_points(X_host[xb:xe].to(dev, non_blocking=True), N)
             oi, od, rb, re_ = rdist.build_knn_graph(engine, xd, K, w["trees"], w["min"], w["max"], 5000,
                                                     w["seed"], w["sweeps"], True)
             out_i[:re_ - rb].copy_(oi, non_blocking=True)
@@ -407,9 +447,11 @@ def run_ours(args, w):
         t = torch.tensor([e0.elapsed_time(e1)], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t_e2e = float(t.item()) * 1e-3 / args.e2e_steps
-        e2e = dict(value=N / t_e2e, unit="points/s", h2d_bytes_per_step=4 * N * D * world,
+        e2e = dict(value=N / t_e2e, unit="points/s", h2d_bytes_per_step=4 * N * D,
                    d2h_bytes_per_step=8 * N * K, ms_per_step=t_e2e * 1e3,
-                   api="gpu_rsfk.distributed.build_knn_graph with pinned host copies on every rank")
+                   api="gpu_rsfk.distributed.replicate_points + build_knn_graph: every rank uploads its block of "
+                       "rows from pinned host memory, an NVLink all-gather completes the replica, every rank "
+                       "reads back its own rows")
 
     # ---- CPU baseline: exact brute force on a bounded sample ---------------
     cpu = None
@@ -429,9 +471,9 @@ def run_ours(args, w):
                        if world > 1 else "single GPU",
                        "l2": "inputs (%.0f MB points + %.0f MB lists) exceed the 126 MB L2; no flush"
                              % (4e-6 * N * D, 8e-6 * N * K)},
-            "recall_at_k": recall,
+            "recall_at_k": recall, "multi_gpu_parity": parity,
             "e2e": e2e, "gpu_launches": int(launches), "clocks": sampler.summary(),
-            "roofline": roofline,
+            "roofline": roofline, "bucket_knn_tensor_roofline": tensor_roofline,
             "phases": {n: {k: (round(v, 4) if isinstance(v, float) else v) for k, v in p.items()}
                        for n, p in phases.items()},
             "phases_from": "one further build with a single tree sequence (RSFK lanes = 1), kernels back to "
@@ -712,12 +754,14 @@ def run_ann_reference(args, w):
 
 # --------------------------------------------------------------------------- reference arm
 REF_SO = os.path.join(ROOT, "oracle", "_ref", "librsfk_ref.so")
+# the reference built with its tile variant of the bucket kernel (oracle/Makefile: ref_tiles)
+REF_TILES_SO = os.path.join(ROOT, "oracle", "_ref", "librsfk_ref_tiles.so")
 
 
 def reference_worker(args, w):
     """Child process: the reference's own library through its C ABI
     (reference: src/python/pymodule_ext.cu:124-147), host buffers, as its wrapper calls it."""
-    L = ctypes.CDLL(REF_SO)
+    L = ctypes.CDLL(REF_TILES_SO if args.ref_variant == "tiles" else REF_SO)
     i = ctypes.c_int
     L.pymodule_rsfk_knn.restype = None
     L.pymodule_rsfk_knn.argtypes = [i] * 10 + [ctypes.c_void_p] * 4
@@ -754,8 +798,8 @@ def run_reference(args, w):
         return
     N, D, K = args.points or w["N"], w["D"], w["K"]
     base = {"impl": "reference"}
-    if not os.path.exists(REF_SO):
-        print(json.dumps(dict(base, unavailable="oracle/_ref/librsfk_ref.so was not built (make -C oracle ref)")))
+    if not os.path.exists(REF_TILES_SO if args.ref_variant == "tiles" else REF_SO):
+        print(json.dumps(dict(base, unavailable="oracle/_ref/librsfk_ref*.so was not built (make -C oracle ref ref_tiles)")))
         return
     cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-worker", "--workload", args.workload,
            "--steps", str(args.steps), "--warmup", str(args.warmup), "--recall-queries", str(args.recall_queries)]
@@ -765,6 +809,7 @@ def run_reference(args, w):
         cmd += ["--ref-trees", str(args.ref_trees)]
     if args.no_recall:
         cmd += ["--no-recall"]
+    cmd += ["--ref-variant", args.ref_variant]
     env = dict(os.environ)
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
         env.pop(k, None)
@@ -799,8 +844,11 @@ def run_reference(args, w):
         "recall_at_k": r["recall"],
         "cpu_baseline": {"value": value, "unit": "points/s", "cores": 0, "kind": "reference",
                          "sample": "the reference's own CUDA library (it has no CPU path), unmodified sources "
-                                   "compiled for sm_100, one GPU, host buffers, whole workload" + note},
+                                   "compiled for sm_100, one GPU, host buffers, whole workload" + note
+                                   + (" (bucket kernel: its tile variant, one launch line edited)"
+                                      if args.ref_variant == "tiles" else "")},
         "e2e": {"value": value, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "reference_forest_s": r["forest_s"], "reference_explore_s": r["explore_s"],
     }
     print(json.dumps(line))
 
@@ -821,6 +869,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--ref-trees", type=int, default=0, help="reference arm: time this many trees and scale")
     ap.add_argument("--ref-timeout", type=int, default=900)
+    ap.add_argument("--ref-variant", default="default", choices=["default", "tiles"],
+                    help="reference arm: its default bucket kernel or its tile variant")
     ap.add_argument("--distinct-queries", action="store_true",
                     help="query workload: fresh draws instead of the base set itself")
     args = ap.parse_args()

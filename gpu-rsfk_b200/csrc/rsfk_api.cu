@@ -22,7 +22,7 @@ struct rsfk_ctx {
     // this one on the same GPU; created on first use, destroyed with the context.
     std::vector<rsfk_ctx*> lanes;
     cudaEvent_t lane_ready = nullptr;
-    int lanes_wanted = 0; // 0: the library's default (RSFK_LANES, else 2)
+    int lanes_wanted = 0; // 0: the library's default (RSFK_LANES, else by the size of the call)
 };
 
 namespace {
@@ -173,8 +173,8 @@ void publish(const Context& c)
 // rows as one sequence (the row of a point is the K smallest distinct of everything
 // it met, in whatever order).  Three lanes by default: two sometimes fall into step
 // with each other (both in the same phase at the same time) and then gain nothing.
-// Lanes pay where a tree's kernels are short (a tree level of C2 takes 80 us, about as
-// long as the host's round trip between levels); where every kernel already fills the GPU
+// Lanes pay where a tree's kernels are short (a tree level of 1 M x 100 points takes 80 us);
+// where every kernel already fills the GPU
 // for a millisecond or more the sequences only compete for cache (measured: 1 M x 960
 // 3.7 -> 4.7 s, 20 M x 128 22.2 -> 23.8 s with three lanes), so by default lanes are used up
 // to 2^28 coordinates (1 GiB of points).  rsfk_ctx_set_lanes or RSFK_LANES set the number
@@ -208,6 +208,29 @@ int forest_lanes(const rsfk_ctx* h, int n_trees, size_t N, int D, size_t list_ro
     return g;
 }
 
+// Rows 0-14 of the forest log for tree i of n_trees (layout: src/include/rsfk.h:274-392 of the
+// reference, flattened [attribute][tree] as src/rsfk.cu:2148-2173 does; times in seconds).
+// Attributes without a counterpart here stay 0: there is no "check active points" pass (a
+// node's points are a contiguous segment), split pairs need no preprocessing (a counter hash
+// inside the projection kernel draws them) and child nodes are created in the tail of the
+// projection kernel, whose time is booked under "check points side".
+void log_tree(float* log_forest, int n_trees, int i, const TreeResult& t, double build_s)
+{
+    if (!log_forest) return;
+    log_forest[0 * n_trees + i] = (float)t.levels;
+    log_forest[1 * n_trees + i] = (float)t.max_leaf;
+    log_forest[2 * n_trees + i] = (float)t.min_leaf;
+    log_forest[3 * n_trees + i] = (float)t.n_leaves;
+    log_forest[4 * n_trees + i] = t.times.init_s;     // buffers, identity permutation, root
+    log_forest[5 * n_trees + i] = (float)build_s;     // the whole build as the host saw it
+    log_forest[7 * n_trees + i] = t.times.project_s;  // projection kernels (device)
+    log_forest[8 * n_trees + i] = t.times.wait_s;     // host waiting for the levels' node counts
+    log_forest[9 * n_trees + i] = t.times.alloc_s;    // growth of the scratch pool
+    log_forest[12 * n_trees + i] = t.times.scatter_s; // partition kernels (device)
+    log_forest[13 * n_trees + i] = t.times.subtree_s; // in-CTA subtrees down to the leaf buckets (device)
+    log_forest[14 * n_trees + i] = t.times.end_s;     // counters read back, final synchronisation
+}
+
 void destroy_lanes(rsfk_ctx* h)
 {
     for (rsfk_ctx* l : h->lanes) {
@@ -230,7 +253,8 @@ void lane_forest(rsfk_ctx* l, int lane, int G, const float* d_points, int N, int
 {
     Context& c = l->c;
     cudaSetDevice(c.device);
-    c.keep_index = d_queries != nullptr;
+    const bool keep_before = c.keep_index;
+    c.keep_index = keep_before || d_queries != nullptr;
     bool ok = true;
     for (int i = lane; i < n_trees && ok; i += G) {
         const int t = first_tree + i * tree_stride;
@@ -245,13 +269,7 @@ void lane_forest(rsfk_ctx* l, int lane, int G, const float* d_points, int N, int
         ok = d_queries ? rsfk::ann_bucket_knn(c, d_points, N, d_queries, NQ, D, K, l->tree, idx, dist)
                        : rsfk::bucket_knn(c, d_points, N, D, K, l->tree, idx, dist);
         cudaEventRecord((*ev)[2 * i + 1], c.stream);
-        if (log_forest) {
-            log_forest[0 * n_trees + i] = (float)l->tree.levels;
-            log_forest[1 * n_trees + i] = (float)l->tree.max_leaf;
-            log_forest[2 * n_trees + i] = (float)l->tree.min_leaf;
-            log_forest[3 * n_trees + i] = (float)l->tree.n_leaves;
-            log_forest[5 * n_trees + i] = (float)(tb1 - tb0);
-        }
+        log_tree(log_forest, n_trees, i, l->tree, tb1 - tb0);
         if (verbose >= 2)
             printf("tree %d: depth %d, leaves %d, leaf size %d..%d, build %.6f s\n", t, l->tree.levels,
                    l->tree.n_leaves, l->tree.min_leaf, l->tree.max_leaf, tb1 - tb0);
@@ -259,7 +277,7 @@ void lane_forest(rsfk_ctx* l, int lane, int G, const float* d_points, int N, int
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest lane");
     ok = ok && c.check_error_flag();
     c.resolve_ann_events();
-    c.keep_index = false;
+    c.keep_index = keep_before;
 }
 
 bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, int K, int n_trees,
@@ -296,7 +314,11 @@ bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, i
         rsfk_ctx* l = h->lanes[g];
         l->c.status = RSFK_OK;
         l->c.message.clear();
-        l->c.keep_index = false;
+        // a lane builds its trees as the caller's context would
+        l->c.keep_index = c.keep_index;
+        l->c.tc_mode = c.tc_mode;
+        l->c.route_step_limit = c.route_step_limit;
+        l->c.level_wait_ms = c.level_wait_ms;
         cudaStreamWaitEvent(l->c.stream, h->lane_ready, 0);
         if (g == 0) continue; // lane 0 runs on the calling thread
         workers.emplace_back(lane_forest, l, g, G, d_points, N, D, K, n_trees, first_tree, tree_stride,
@@ -313,9 +335,11 @@ bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, i
         c.stats.add(lc.stats);
         lc.stats = rsfk::Stats();
     }
-    // the context's tree is the last one its first lane built
+    // the context's tree is the last one its first lane built; hyperplanes the context
+    // materialised for an earlier tree do not belong to it
     h->tree = h->lanes[0]->tree;
     h->has_tree = ok && h->lanes[0]->has_tree;
+    c.planes_ready = false;
     // the caller's lists take part from here on only
     if (lists_ready != nullptr && !(*lists_ready)()) ok = false;
     if (ok) {
@@ -355,8 +379,7 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
 {
     Context& c = h->c;
     {
-        static const bool single = getenv("RSFK_TIMELINE") != nullptr;
-        const int G = single ? 1 : forest_lanes(h, n_trees, (size_t)N, D, (size_t)N, K);
+        const int G = forest_lanes(h, n_trees, (size_t)N, D, (size_t)N, K);
         if (G > 1)
             return run_forest_lanes(h, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
                                     max_children, max_depth, seed, d_idx, d_dist, log_forest, verbose,
@@ -366,14 +389,6 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
     std::vector<cudaEvent_t> ev(2 * (size_t)n_trees);
     for (auto& e : ev) cudaEventCreate(&e);
     if (log_forest) memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
-    const bool timeline = getenv("RSFK_TIMELINE") != nullptr;
-    cudaEvent_t ev_start = nullptr;
-    std::vector<double> tl;
-    if (timeline) {
-        cudaEventCreate(&ev_start);
-        cudaStreamSynchronize(c.stream);
-        cudaEventRecord(ev_start, c.stream);
-    }
     const double t0 = now_s();
     bool ok = true;
     for (int i = 0; i < n_trees && ok; ++i) {
@@ -384,34 +399,17 @@ bool run_forest(rsfk_ctx* h, const float* d_points, int N, int D, int K, int n_t
         h->has_tree = ok;
         const double tb1 = now_s();
         c.stats.tree_build_us += (tb1 - tb0) * 1e6;
-        if (timeline) { tl.push_back((tb0 - t0) * 1e3); tl.push_back((tb1 - t0) * 1e3); }
         if (!ok) break;
         cudaEventRecord(ev[2 * i], c.stream);
         ok = rsfk::bucket_knn(c, d_points, N, D, K, h->tree, d_idx, d_dist);
         cudaEventRecord(ev[2 * i + 1], c.stream);
-        if (log_forest) {
-            log_forest[0 * n_trees + i] = (float)h->tree.levels;
-            log_forest[1 * n_trees + i] = (float)h->tree.max_leaf;
-            log_forest[2 * n_trees + i] = (float)h->tree.min_leaf;
-            log_forest[3 * n_trees + i] = (float)h->tree.n_leaves;
-            log_forest[5 * n_trees + i] = (float)(tb1 - tb0);
-        }
+        log_tree(log_forest, n_trees, i, h->tree, tb1 - tb0);
         if (verbose >= 2)
             printf("tree %d: depth %d, leaves %d, leaf size %d..%d, build %.6f s\n", t, h->tree.levels,
                    h->tree.n_leaves, h->tree.min_leaf, h->tree.max_leaf, tb1 - tb0);
     }
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
     ok = ok && c.check_error_flag();
-    if (ok && timeline) {
-        for (int i = 0; i < n_trees && i < 6; ++i) {
-            float a = 0, b = 0;
-            cudaEventElapsedTime(&a, ev_start, ev[2 * i]);
-            cudaEventElapsedTime(&b, ev_start, ev[2 * i + 1]);
-            fprintf(stderr, "timeline tree %d: build host %.3f..%.3f ms, knn device %.3f..%.3f ms\n", i, tl[2 * i],
-                    tl[2 * i + 1], a, b);
-        }
-    }
-    if (ev_start) cudaEventDestroy(ev_start);
     if (ok)
         for (int i = 0; i < n_trees; ++i) {
             float ms = 0.0f;
@@ -773,13 +771,29 @@ int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
             !c.check(cudaStreamSynchronize(c.stream), "stats"))
             return c.status;
     }
+    unsigned long long tc_pairs[2] = {0, 0};
+    if (c.slots[Context::TC_STATS].ptr) {
+        if (!c.check(cudaMemcpyAsync(tc_pairs, c.slots[Context::TC_STATS].ptr, sizeof(tc_pairs),
+                                     cudaMemcpyDeviceToHost, c.stream), "stats D2H") ||
+            !c.check(cudaStreamSynchronize(c.stream), "stats"))
+            return c.status;
+    }
+    for (rsfk_ctx* l : ctx->lanes) { // lanes keep device counters of their own
+        unsigned long long lp[2] = {0, 0};
+        if (l->c.slots[Context::TC_STATS].ptr &&
+            cudaMemcpy(lp, l->c.slots[Context::TC_STATS].ptr, sizeof(lp), cudaMemcpyDeviceToHost) == cudaSuccess) {
+            tc_pairs[0] += lp[0];
+            tc_pairs[1] += lp[1];
+        }
+    }
     c.resolve_ann_events();
-    const double v[13] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+    const double v[17] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
                          c.stats.bucket_knn_us, (double)evaluated, c.stats.subtree_us,
                          (double)c.stats.sub_active_points, (double)c.stats.sub_nodes, c.stats.tree_build_us,
                          c.stats.project_us, (double)c.stats.project_launches, c.stats.route_us,
-                         c.stats.query_update_us};
-    for (int i = 0; i < n && i < 13; ++i) out[i] = v[i];
+                         c.stats.query_update_us, (double)c.stats.tc_launches, c.stats.tc_gram_flops,
+                         (double)tc_pairs[0], (double)tc_pairs[1]};
+    for (int i = 0; i < n && i < 17; ++i) out[i] = v[i];
     return RSFK_OK;
 }
 
@@ -869,6 +883,7 @@ int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, int N, int D
     t.leaf_count = d_leaf_count;
     t.n_leaves = n_leaves;
     t.max_leaf = max_leaf;
+    t.sum_leaf_sq = -1.0; // not known for a caller's table
     rsfk::bucket_knn(ctx->c, d_points, N, D, K, t, d_idx, d_dist);
     return ctx->c.status;
 }
@@ -877,6 +892,21 @@ int rsfk_ctx_set_lanes(rsfk_ctx* ctx, int lanes)
 {
     if (!ctx || lanes < 0 || lanes > 4) return RSFK_ERR_ARG;
     ctx->lanes_wanted = lanes;
+    return RSFK_OK;
+}
+
+int rsfk_ctx_set_tc(rsfk_ctx* ctx, int mode)
+{
+    if (!ctx || mode < -1 || mode > 1) return RSFK_ERR_ARG;
+    ctx->c.tc_mode = mode;
+    return RSFK_OK;
+}
+
+int rsfk_ctx_set_wait_limits(rsfk_ctx* ctx, int route_max_steps, int level_wait_ms)
+{
+    if (!ctx) return RSFK_ERR_ARG;
+    ctx->c.route_step_limit = route_max_steps;
+    ctx->c.level_wait_ms = level_wait_ms;
     return RSFK_OK;
 }
 

@@ -2,54 +2,170 @@
 // cores (tcgen05, sm_100a).  Included by rsfk_knn.cu.
 //
 // For D >= 64 the all-pairs distances of a bucket are a dense contraction:
-// d2(i,j) = |xi|^2 + |xj|^2 - 2 xi.xj.  The Gram tile X X^T is computed by
-// tcgen05.mma kind::tf32 with a 3xTF32 split (x = big + small, three products
-// big.big + big.small + small.big, fp32 accumulation in tensor memory), which
-// keeps about 21 mantissa bits.  That value is used ONLY to decide which pairs
-// can possibly enter a K-list: a pair passes when its approximate distance,
-// lowered by a safety margin that covers the split and accumulation error, is
-// below the row's current K-th distance.  Every passing candidate is then
-// evaluated again in the reference's exact summation order (the same routine
-// the exploration sweep uses) and merged with the usual list rule, so the
-// stored distances and the selected indices are the ones the SIMT path gives.
+// d2(i,j) = |yi|^2 + |yj|^2 - 2 yi.yj.  The tensor cores compute the Gram tile
+// Y Y^T in TF32 with fp32 accumulation in tensor memory.  That value is used ONLY
+// to decide which pairs can possibly enter a K-list: a pair passes when its
+// approximate distance, lowered by a margin that covers the TF32 and accumulation
+// error, is below the row's current K-th distance.  Every passing candidate is
+// then evaluated again on the original coordinates in the reference's exact
+// summation order (the routine the exploration sweep uses) and merged with the
+// usual list rule, so the stored distances and the selected indices are the ones
+// the SIMT kernel gives, bit for bit.
 //
-// One CTA per leaf.  The leaf's rows are cut into blocks of 128; for a block
-// pair (I, J) the 128 x 128 Gram tile accumulates in tensor memory over K-chunks
-// of 32 dimensions.  Operands are staged by the threads themselves (rows are
-// gathered through the permutation, so no 2-D TMA tile exists): a chunk is split
-// into big/small TF32 and stored in the K-major, no-swizzle core-matrix layout
-// the UMMA shared-memory descriptor addresses (8 rows x 16 bytes per core
-// matrix).  After all J the rows of block I hold one pass bit per leaf member.
+// Data path.  Once per tree k_tc_rows writes the points in leaf order, centred on
+// the first point of their leaf (y = x - x_first: distances are unchanged, norms
+// and with them the error margin shrink from |x|^2 to the leaf's spread), rows
+// padded to a multiple of 32 floats, plus |y|^2 per row.  A work item ("tile") is a
+// block of 128 consecutive rows of one leaf against all the rows of that leaf, taken
+// in column groups of 256.  The kernel is persistent, one CTA per SM, and
+// warp-specialised:
+//
+//   warp 0    one thread issues 2-D TMA tile loads (cp.async.bulk.tensor, 128-byte
+//             swizzle, no multicast) of 32-dimension chunks of the 128 A rows and
+//             the 256 B rows into a ring of shared-memory stages;
+//   warp 1    one thread issues tcgen05.mma (kind::tf32, M=128, N=256, K=8) on the
+//             stages as they fill, frees a stage with tcgen05.commit, and hands a
+//             finished 128 x 256 accumulator (one of two in tensor memory) to the
+//             epilogue with another commit;
+//   warps 2-9 read the accumulator with tcgen05.ld, turn it into one pass bit per
+//             pair, and evaluate the passing pairs exactly -- while the tensor
+//             cores already work on the next column group.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises an abort flag
+// that all roles poll, the MMA thread drains its outstanding work with a last
+// commit before tensor memory is released, the producer waits (bounded) for the
+// loads still in flight, and the kernel sets the context's error flag.
 #pragma once
+
+#include <cuda.h>
 
 namespace tc {
 
-constexpr int TC_ROWS = 128;            // MMA M and N: rows of one leaf block
-constexpr int TC_KC = 32;               // dimensions staged per chunk
-constexpr int TC_LBO = 128;             // bytes between K-adjacent core matrices
-constexpr int TC_SBO = (TC_KC / 4) * 128; // bytes between 8-row groups
-constexpr int TC_OPERAND_BYTES = TC_ROWS * TC_KC * 4; // one of big / small
-constexpr unsigned TC_WAIT_LIMIT = 1u << 22;          // polls before a wait gives up
+constexpr int BM = 128;                 // rows of a tile (MMA M)
+constexpr int BN = 256;                 // columns of a group (MMA N)
+constexpr int KC = 32;                  // dimensions per stage: 32 floats = one 128-byte swizzle row
+constexpr int STAGES = 3;
+constexpr int A_BYTES = BM * KC * 4;    // 16 KiB
+constexpr int B_BYTES = BN * KC * 4;    // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 32 * (2 + EPI_WARPS);
+constexpr int MAX_LEAF = 2048;          // pass bits of a row: one per leaf member
+constexpr int TMEM_COLS = 512;          // two 128 x 256 fp32 accumulators
+constexpr unsigned WAIT_LIMIT = 1u << 22; // polls before a wait gives up
+
+struct Tile {
+    int row0;   // first row of the leaf in leaf order
+    int m;      // rows of the leaf
+    int i0;     // first row of this tile inside the leaf
+    int pad;
+};
+
+// Relative error bound of the TF32 Gram distance, as a fraction of |yi|^2+|yj|^2.
+// Each operand carries 10 explicit mantissa bits (relative error below 2^-10
+// whether the unit truncates or rounds), so a product is off by less than 2^-9 of
+// |a||b| and the dot product by less than 2^-9 |yi||yj| <= 2^-10 (|yi|^2+|yj|^2);
+// d2 = nn - 2g doubles that: 2^-9 = 1.95e-3.  fp32 accumulation of D products,
+// allowing two units in the last place per addition, adds 2 * D * 2^-23 on the same
+// scale.  Centring itself costs 2^-22 (y = fl(x - c) is exact to 2^-24 relative per
+// coordinate).  The margin used is 1.25 times the sum.
+__host__ __device__ inline float filter_margin(int D)
+{
+    return 1.25f * (1.953125e-3f + 2.4e-7f * (float)D + 2.4e-7f);
+}
+
+struct Layout {
+    int pass_words;                 // 32-bit words of pass bits per row
+    int off_pass, off_xp, off_queue, off_thr, off_nrm_a, off_nrm_b, off_bar, total;
+    int xp_floats;
+};
+__host__ __device__ inline Layout layout_for(int D, int max_leaf)
+{
+    Layout l;
+    const int groups = (max_leaf + BN - 1) / BN;
+    l.pass_words = groups * (BN / 32);
+    l.xp_floats = (D + 3) & ~3;
+    int o = STAGES * STAGE_BYTES;
+    l.off_pass = o;  o += BM * l.pass_words * 4;
+    l.off_xp = o;    o += EPI_WARPS * l.xp_floats * 4;
+    l.off_queue = o; o += EPI_WARPS * EXP_QUEUE * 4;
+    l.off_thr = o;   o += BM * 4;
+    l.off_nrm_a = o; o += BM * 4;
+    l.off_nrm_b = o; o += 2 * BN * 4;
+    l.off_bar = o;   o += 128;
+    l.total = o + 1024; // slack to align the stages to 1024 bytes
+    return l;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 
-// K-major, no swizzle: start address, leading (K) byte offset, stride (8-row
-// group) byte offset, all in 16-byte units; descriptor version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr)
+// ---- mbarrier ---------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)(TC_LBO >> 4) << 16) |
-           ((uint64_t)(TC_SBO >> 4) << 32) | (1ull << 46);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P1;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait; gives up when the limit runs out (and then raises the abort flag)
+// or when another role has raised it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 31u) == 31u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
 }
 
-// kind::tf32, fp32 accumulator, both operands K-major, M = N = 128.
-__device__ __forceinline__ uint32_t umma_idesc()
+// ---- TMA --------------------------------------------------------------------
+// One 2-D tile (the box of the tensor map: 32 floats x 128 rows) at column x, row y
+// into shared memory; completion is counted in bytes on the mbarrier.  x must be a
+// multiple of 4 floats (16 bytes); rows outside the tensor read as zeros.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
 {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_ROWS >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
 }
 
+// ---- tcgen05 ----------------------------------------------------------------
+// Shared-memory operand descriptor: K-major, 128-byte swizzle (the layout a TMA box of
+// 128-byte rows produces): 8-row groups 1024 bytes apart, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr)
+{
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+// kind::tf32, fp32 accumulator, both operands K-major.
+__device__ __forceinline__ uint32_t umma_idesc(int M, int N)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate)
 {
@@ -63,31 +179,10 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
         : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
-
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-
-// Bounded wait on an mbarrier phase; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t phase)
-{
-    for (unsigned it = 0; it < TC_WAIT_LIMIT; ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t"
-            ".reg .pred P1;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, P1;\n\t"
-            "}"
-            : "=r"(done)
-            : "r"(bar), "r"(phase)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v)
 {
     uint32_t r[32];
@@ -104,299 +199,319 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v)
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-
-// Relative safety margin of the 3xTF32 Gram distance, applied to |xi|^2+|xj|^2:
-// dropped small.small terms and truncated small parts (each below 2^-20 of the
-// product) plus fp32 accumulation over up to 3*D terms.
-constexpr float TC_MARGIN = 1.5e-4f;
-
-constexpr int TC_MAX_BLOCKS = 16; // leaves of up to 2048 points
-
-// Shared-memory layout of one CTA (bytes).  Leaves that fit one block need a
-// single operand pair (the Gram tile is X_I X_I^T); larger leaves also stage the
-// J block.
-struct Layout {
-    int two_operands, pass_words; // pass_words: 32-bit words of pass bits per row
-    int off_b, off_norm, off_ids, off_pass, off_xp, off_queue, off_misc, total;
-};
-__host__ __device__ inline Layout layout_for(int D, int max_leaf)
+// barrier of the epilogue warps only (hardware barrier 1)
+__device__ __forceinline__ void epi_barrier()
 {
-    Layout l;
-    const int n_blocks = (max_leaf + TC_ROWS - 1) / TC_ROWS;
-    l.two_operands = n_blocks > 1;
-    l.pass_words = n_blocks * (TC_ROWS / 32);
-    int o = 2 * TC_OPERAND_BYTES;
-    l.off_b = o;     o += l.two_operands ? 2 * TC_OPERAND_BYTES : 0;
-    l.off_norm = o;  o += 2 * TC_ROWS * 4;
-    l.off_ids = o;   o += 2 * TC_ROWS * 4;
-    l.off_pass = o;  o += TC_ROWS * l.pass_words * 4;
-    // the per-warp copy of a row (exact distances, row phase) reuses the operand
-    // area, which is idle then, when it fits there
-    const int xp_bytes = KNN_WARPS * ((D + 3) & ~3) * 4;
-    const int operand_area = (l.two_operands ? 4 : 2) * TC_OPERAND_BYTES;
-    if (xp_bytes <= operand_area) l.off_xp = 0;
-    else { l.off_xp = o; o += xp_bytes; }
-    l.off_queue = o; o += KNN_WARPS * EXP_QUEUE * 4;
-    l.off_misc = o;  o += 64;
-    l.total = o;
-    return l;
+    asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
 }
 
-// Stages dimensions [k0, k0+TC_KC) of the 128 rows whose ids are in sIds (-1 =
-// padding row, staged as zeros) as big/small TF32 in the core-matrix layout,
-// and adds this thread's share of |x|^2 to nrm[0..1].
-// Thread map: lane = 8*q + t handles row 8*rg + t and dimensions 4*q.. of every
-// 16-dimension step, so the 8 lanes with equal q write one 128-byte core matrix.
-template <bool VEC4>
-__device__ __forceinline__ void stage_chunk(const float* __restrict__ pts, int D, const int* sIds, int k0,
-                                            unsigned char* sBig, unsigned char* sSmall, float* nrm, int warp,
-                                            int lane)
+// ---------------------------------------------------------------------------
+// Tile list of a tree: every leaf contributes ceil(m / 128) consecutive tiles.
+// ---------------------------------------------------------------------------
+__global__ void k_tc_tiles(const int* __restrict__ leaf_start, const int* __restrict__ leaf_count, int n_leaves,
+                           int max_leaf, Tile* __restrict__ tiles, int tile_cap, int* __restrict__ n_tiles)
 {
-    const int t = lane & 7, q = lane >> 3;
-#pragma unroll
-    for (int g2 = 0; g2 < 2; ++g2) {
-        const int rg = warp + g2 * KNN_WARPS; // 16 groups of 8 rows
-        const int id = sIds[rg * 8 + t];
-        const float* src = pts + (size_t)(id < 0 ? 0 : id) * D;
-#pragma unroll
-        for (int kk = 0; kk < TC_KC; kk += 16) {
-            const int k = k0 + kk + 4 * q;
-            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (id >= 0) {
-                if (VEC4) {
-                    if (k < D) x = __ldg(reinterpret_cast<const float4*>(src + k));
-                } else {
-                    if (k + 0 < D) x.x = __ldg(src + k + 0);
-                    if (k + 1 < D) x.y = __ldg(src + k + 1);
-                    if (k + 2 < D) x.z = __ldg(src + k + 2);
-                    if (k + 3 < D) x.w = __ldg(src + k + 3);
-                }
+    const int leaf = blockIdx.x * blockDim.x + threadIdx.x;
+    if (leaf >= n_leaves) return;
+    const int m = min(leaf_count[leaf], max_leaf);
+    const int nb = (m + BM - 1) / BM;
+    const int base = atomicAdd(n_tiles, nb);
+    for (int b = 0; b < nb; ++b)
+        if (base + b < tile_cap) tiles[base + b] = Tile{leaf_start[leaf], m, b * BM, 0};
+}
+
+// ---------------------------------------------------------------------------
+// Leaf-ordered, centred copy of the points: rows[r][0..Dp) = x[perm[r]] - x[perm[row0]]
+// (zeros beyond D), norms[r] = |row|^2.  One CTA per tile, one warp per row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ perm,
+          const Tile* __restrict__ tiles, const int* __restrict__ n_tiles_ptr, int tile_cap,
+          float* __restrict__ rows, float* __restrict__ norms)
+{
+    extern __shared__ float4 smem4[];
+    float* centre = reinterpret_cast<float*>(smem4); // [D]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int n_tiles = min(*n_tiles_ptr, tile_cap);
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const Tile tl = tiles[t];
+        __syncthreads();
+        const float* c = pts + (size_t)perm[tl.row0] * D;
+        for (int k = threadIdx.x; k < D; k += blockDim.x) centre[k] = __ldg(c + k);
+        __syncthreads();
+        const int n = min(BM, tl.m - tl.i0);
+        for (int r = warp; r < n; r += n_warps) {
+            const size_t row = (size_t)tl.row0 + tl.i0 + r;
+            const float* x = pts + (size_t)perm[row] * D;
+            float* y = rows + row * Dp;
+            float nrm = 0.0f;
+            for (int k = lane; k < Dp; k += 32) {
+                const float v = k < D ? __fsub_rn(__ldg(x + k), centre[k]) : 0.0f;
+                y[k] = v;
+                nrm = __fmaf_rn(v, v, nrm);
             }
-            nrm[g2] = __fmaf_rn(x.x, x.x, nrm[g2]);
-            nrm[g2] = __fmaf_rn(x.y, x.y, nrm[g2]);
-            nrm[g2] = __fmaf_rn(x.z, x.z, nrm[g2]);
-            nrm[g2] = __fmaf_rn(x.w, x.w, nrm[g2]);
-            float4 b, s;
-            b.x = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u); s.x = x.x - b.x;
-            b.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u); s.y = x.y - b.y;
-            b.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u); s.z = x.z - b.z;
-            b.w = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u); s.w = x.w - b.w;
-            s.x = __uint_as_float(__float_as_uint(s.x) & 0xffffe000u);
-            s.y = __uint_as_float(__float_as_uint(s.y) & 0xffffe000u);
-            s.z = __uint_as_float(__float_as_uint(s.z) & 0xffffe000u);
-            s.w = __uint_as_float(__float_as_uint(s.w) & 0xffffe000u);
-            const int off = rg * TC_SBO + ((kk >> 2) + q) * TC_LBO + t * 16;
-            *reinterpret_cast<float4*>(sBig + off) = b;
-            *reinterpret_cast<float4*>(sSmall + off) = s;
+#pragma unroll
+            for (int s = 16; s >= 1; s >>= 1) nrm += __shfl_xor_sync(RSFK_FULL, nrm, s);
+            if (lane == 0) norms[row] = nrm;
         }
     }
 }
 
-// |x|^2 of the 128 staged rows from the per-thread shares (lanes t, t+8, t+16,
-// t+24 hold the four quarters of a row).
-__device__ __forceinline__ void store_norms(const float* nrm, float* sNorm, int warp, int lane)
-{
-#pragma unroll
-    for (int g2 = 0; g2 < 2; ++g2) {
-        float v = nrm[g2];
-        v += __shfl_xor_sync(RSFK_FULL, v, 8);
-        v += __shfl_xor_sync(RSFK_FULL, v, 16);
-        if ((lane >> 3) == 0) sNorm[(warp + g2 * KNN_WARPS) * 8 + (lane & 7)] = v;
-    }
-}
-
+// ---------------------------------------------------------------------------
+// The pipeline kernel.  stats[0] += pairs that passed the filter, stats[1] += pairs
+// looked at.
+// ---------------------------------------------------------------------------
 template <int KPL, bool VEC4>
-__global__ void __launch_bounds__(KNN_THREADS)
-k_bucket_knn_tc(const float* __restrict__ pts, int D, int K, const int* __restrict__ perm,
-                const int* __restrict__ leaf_start, const int* __restrict__ leaf_count,
-                int* __restrict__ knn_idx, float* __restrict__ knn_dist, int max_leaf,
+__global__ void __launch_bounds__(THREADS, 1)
+k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict__ pts, int D, int Dp, int K,
+                const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
+                const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
+                float* __restrict__ knn_dist, int max_leaf, float margin, unsigned long long* __restrict__ stats,
                 int* __restrict__ error_flag)
 {
-    extern __shared__ float4 smem4[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(smem4);
+    extern __shared__ unsigned char smem_raw[];
+    // the swizzled operand tiles want 1024-byte alignment
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const Layout L0 = layout_for(D, max_leaf);
-    unsigned char* sBigA = smem;
-    unsigned char* sSmallA = smem + TC_OPERAND_BYTES;
-    unsigned char* sBigB = L0.two_operands ? smem + L0.off_b : sBigA;
-    unsigned char* sSmallB = L0.two_operands ? smem + L0.off_b + TC_OPERAND_BYTES : sSmallA;
-    float* sNormA = reinterpret_cast<float*>(smem + L0.off_norm);
-    float* sNormB = sNormA + TC_ROWS;
-    int* sIdsA = reinterpret_cast<int*>(smem + L0.off_ids);
-    int* sIdsB = sIdsA + TC_ROWS;
     unsigned* sPass = reinterpret_cast<unsigned*>(smem + L0.off_pass);
-    uint64_t* sBar = reinterpret_cast<uint64_t*>(smem + L0.off_misc);
-    uint32_t* sTmem = reinterpret_cast<uint32_t*>(smem + L0.off_misc + 16);
-    int* sFail = reinterpret_cast<int*>(smem + L0.off_misc + 32);
+    float* sThr = reinterpret_cast<float*>(smem + L0.off_thr);
+    float* sNrmA = reinterpret_cast<float*>(smem + L0.off_nrm_a);
+    float* sNrmB = reinterpret_cast<float*>(smem + L0.off_nrm_b);
+    uint64_t* sBar = reinterpret_cast<uint64_t*>(smem + L0.off_bar);
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain
+    const uint32_t bar_full = smem_u32(sBar), bar_empty = smem_u32(sBar + STAGES);
+    const uint32_t bar_acc_full = smem_u32(sBar + 2 * STAGES), bar_acc_empty = smem_u32(sBar + 2 * STAGES + 2);
+    const uint32_t bar_drain = smem_u32(sBar + 2 * STAGES + 4);
+    uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 2 * STAGES + 5);
+    volatile int* sAbort = reinterpret_cast<volatile int*>(sTmem + 1);
     const int PW = L0.pass_words;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float* xp = reinterpret_cast<float*>(smem + L0.off_xp) + (size_t)warp * ((D + 3) & ~3);
-    int* queue = reinterpret_cast<int*>(smem + L0.off_queue) + warp * EXP_QUEUE;
+    const int n_tiles = min(*n_tiles_ptr, tile_cap);
+    const int n_chunks = Dp / KC;
 
-    const int leaf = blockIdx.x;
-    const int m = leaf_count[leaf];
-    const int* ids = perm + leaf_start[leaf];
-    const int n_blocks = (m + TC_ROWS - 1) / TC_ROWS;
-
-    // ---- set-up: barrier and tensor memory --------------------------------
     if (threadIdx.x == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(sBar)), "r"(1) : "memory");
+        for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, EPI_WARPS); }
+        mbar_init(bar_drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        *sFail = 0;
+        *sAbort = 0;
     }
-    if (warp == 0) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sTmem)),
-                     "r"((uint32_t)TC_ROWS)
+                     "r"((uint32_t)TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = *sTmem;
-    const uint32_t bar = smem_u32(sBar);
-    const uint32_t idesc = umma_idesc();
-    const int n_chunks = (D + TC_KC - 1) / TC_KC;
-    uint32_t phase = 0;
-    bool failed = false;
+    const uint32_t tmem_base = *sTmem;
 
-    for (int bi = 0; bi < n_blocks && !failed; ++bi) {
-        const int i0 = bi * TC_ROWS;
-        __syncthreads(); // the previous block's row phase has finished with sIdsA / sPass
-        for (int r = threadIdx.x; r < TC_ROWS; r += blockDim.x) sIdsA[r] = i0 + r < m ? ids[i0 + r] : -1;
-        for (int w = threadIdx.x; w < TC_ROWS * PW; w += blockDim.x) sPass[w] = 0u;
-        __syncthreads();
-        // this thread's epilogue row: tensor-memory lane 32*(warp%4)+lane
-        const int erow = 32 * (warp & 3) + lane;
-        const int eid = sIdsA[erow];
-        const int mI = min(TC_ROWS, m - i0);
-
-        for (int bj = 0; bj < n_blocks && !failed; ++bj) {
-            const int j0 = bj * TC_ROWS;
-            const bool diag = (bj == bi);
-            __syncthreads(); // the previous tile's row phase used the operand area for its row copies
-            if (!diag) {
-                for (int r = threadIdx.x; r < TC_ROWS; r += blockDim.x) sIdsB[r] = j0 + r < m ? ids[j0 + r] : -1;
-                __syncthreads();
-            }
-            // ---- Gram tile (I, J) over K chunks ---------------------------
-            float nrmA[2] = {0.0f, 0.0f}, nrmB[2] = {0.0f, 0.0f};
-            for (int ch = 0; ch < n_chunks; ++ch) {
-                stage_chunk<VEC4>(pts, D, sIdsA, ch * TC_KC, sBigA, sSmallA, nrmA, warp, lane);
-                if (!diag) stage_chunk<VEC4>(pts, D, sIdsB, ch * TC_KC, sBigB, sSmallB, nrmB, warp, lane);
-                // generic-proxy writes must be visible to the tensor core (async proxy)
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncthreads();
-                if (threadIdx.x == 0) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t aB = smem_u32(sBigA), aS = smem_u32(sSmallA);
-                    const uint32_t bB = diag ? aB : smem_u32(sBigB), bS = diag ? aS : smem_u32(sSmallB);
-#pragma unroll
-                    for (int pass = 0; pass < 3; ++pass) {
-                        const uint32_t a = (pass == 2) ? aS : aB; // big.big, big.small, small.big
-                        const uint32_t b = (pass == 1) ? bS : bB;
-#pragma unroll
-                        for (int s8 = 0; s8 < TC_KC / 8; ++s8)
-                            umma_tf32(tmem_d, umma_desc(a + s8 * 2 * TC_LBO), umma_desc(b + s8 * 2 * TC_LBO), idesc,
-                                      (ch > 0 || pass > 0 || s8 > 0) ? 1u : 0u);
-                    }
-                    umma_commit(bar);
-                }
-                // the operands may be overwritten only after the MMAs have read them
-                if (!mbar_wait(bar, phase)) *sFail = 1;
-                phase ^= 1u;
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncthreads();
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (*sFail) { failed = true; break; }
-            }
-            if (failed) break;
-            store_norms(nrmA, sNormA, warp, lane);
-            if (!diag) store_norms(nrmB, sNormB, warp, lane);
-            __syncthreads();
-            // ---- epilogue: pass bits of rows I against columns J ------------
-            // warp w reads tensor-memory lanes 32*(w%4).. (rows) and columns 64*(w/4)..
-            {
-                // current K-th distance of the row (rows flushed after earlier tiles have tightened it)
-                const float thr = eid >= 0 ? __ldcg(knn_dist + (size_t)eid * K + (K - 1)) : -1.0f;
-                const float* nJ = diag ? sNormA : sNormB;
-                const float n_row = sNormA[erow];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int c0 = 64 * (warp >> 2) + 32 * half;
-                    float g[32];
-                    tmem_ld32(tmem_d + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, g);
-                    unsigned word = 0;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int j = c0 + c;
-                        const float nn = n_row + nJ[j];
-                        const float d2 = __fmaf_rn(-2.0f, g[c], nn) - TC_MARGIN * nn;
-                        // !(d2 >= thr) keeps the candidate when anything is not a number
-                        if (j0 + j < m && j0 + j != i0 + erow && !(d2 >= thr)) word |= 1u << c;
-                    }
-                    if (eid >= 0) sPass[erow * PW + bj * (TC_ROWS / 32) + (c0 >> 5)] = word;
-                }
-            }
-            // the next tile's MMAs overwrite tensor memory and sIdsB: order after the loads
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncthreads();
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-            // ---- rows of block I: exact distances of passing candidates ----
-            // A row is flushed as soon as 32 candidates wait (its K-th distance then
-            // tightens the filter of the following tiles) and after the last tile.
-            const bool last_tile = (bj == n_blocks - 1);
-            const int n_words = min((m + 31) >> 5, (bj + 1) * (TC_ROWS / 32));
-            for (int r = warp; r < mI; r += KNN_WARPS) {
-                int pending = 0;
-                for (int w = lane; w < n_words; w += 32) pending += __popc(sPass[r * PW + w]);
-#pragma unroll
-                for (int sft = 16; sft >= 1; sft >>= 1) pending += __shfl_xor_sync(RSFK_FULL, pending, sft);
-                if (pending == 0 || (pending < 32 && !last_tile)) continue;
-                const int self = sIdsA[r];
-                __syncwarp();
-                for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)self * D + k);
-                WarpList<KPL> L;
-                L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
-                __syncwarp();
-                bool changed = false;
-                int qn = 0;
-                for (int w = 0; w < n_words; ++w) {
-                    const unsigned bits = sPass[r * PW + w];
-                    if (bits == 0) continue;
-                    __syncwarp();
-                    if (lane == 0) sPass[r * PW + w] = 0u;
-                    const bool ok = (bits >> lane) & 1u;
-                    if (ok) queue[qn + __popc(bits & ((1u << lane) - 1u))] = ids[32 * w + lane];
-                    qn += __popc(bits);
-                    __syncwarp();
-                    if (qn >= 32) {
-                        explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
-                        __syncwarp();
-                        const int rest = qn - 32;
-                        const int tmp = lane < rest ? queue[32 + lane] : -1;
-                        __syncwarp();
-                        if (lane < rest) queue[lane] = tmp;
-                        qn = rest;
-                        __syncwarp();
+    if (warp == 0) {
+        // ================= producer =================
+        if (lane == 0) {
+            unsigned it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const Tile tl = tiles[t];
+                const int n_groups = (tl.m + BN - 1) / BN;
+                for (int g = 0; g < n_groups && ok; ++g) {
+                    for (int c = 0; c < n_chunks; ++c, ++it) {
+                        const int s = it % STAGES;
+                        if (!mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1u) ^ 1u, sAbort)) { ok = false; break; }
+                        const uint32_t dst = smem_u32(smem + s * STAGE_BYTES);
+                        mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
+                        tma_load_2d(dst, &map, c * KC, tl.row0 + tl.i0, bar_full + 8 * s);
+                        tma_load_2d(dst + A_BYTES, &map, c * KC, tl.row0 + g * BN, bar_full + 8 * s);
+                        tma_load_2d(dst + 2 * A_BYTES, &map, c * KC, tl.row0 + g * BN + BM, bar_full + 8 * s);
                     }
                 }
-                if (qn > 0) explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
-                if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+            }
+            // The MMA thread waits for every stage that was filled unless the kernel aborts;
+            // then the loads still in flight are waited for here (bounded) so that nothing
+            // writes shared memory after the CTA has left.
+            if (!ok || *sAbort) {
+                for (unsigned back = 0; back < (unsigned)STAGES && back < it; ++back) {
+                    const unsigned j = it - 1 - back;
+                    for (unsigned p = 0; p < WAIT_LIMIT; ++p)
+                        if (mbar_try(bar_full + 8 * (j % STAGES), (j / STAGES) & 1u)) break;
+                }
             }
         }
-        if (failed) break;
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BM, BN);
+            unsigned it = 0, gc = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const Tile tl = tiles[t];
+                const int n_groups = (tl.m + BN - 1) / BN;
+                for (int g = 0; g < n_groups && ok; ++g, ++gc) {
+                    const int ab = gc & 1;
+                    // the epilogue has read this accumulator's previous contents
+                    if (!mbar_wait(bar_acc_empty + 8 * ab, ((gc >> 1) & 1u) ^ 1u, sAbort)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(ab * BN);
+                    for (int c = 0; c < n_chunks; ++c, ++it) {
+                        const int s = it % STAGES;
+                        if (!mbar_wait(bar_full + 8 * s, (it / STAGES) & 1u, sAbort)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+                        for (int k8 = 0; k8 < KC / 8; ++k8)
+                            umma_tf32(tmem_d, umma_desc_sw128(a + k8 * 32), umma_desc_sw128(b + k8 * 32), idesc,
+                                      (c > 0 || k8 > 0) ? 1u : 0u);
+                        umma_commit(bar_empty + 8 * s); // the stage is free once these MMAs have read it
+                    }
+                    if (ok) umma_commit(bar_acc_full + 8 * ab);
+                }
+            }
+            // nothing may still write tensor memory or read shared memory when the CTA ends:
+            // a last commit completes after everything issued before it
+            umma_commit(bar_drain);
+            for (unsigned p = 0; p < WAIT_LIMIT; ++p)
+                if (mbar_try(bar_drain, 0)) break;
+        }
+    } else {
+        // ================= epilogue + exact evaluation =================
+        const int ew = warp - 2;                  // 0..7
+        const int quarter = warp & 3;             // tensor-memory lanes this warp may read
+        const int half = ew >> 2;                 // which 128 of the group's 256 columns
+        const int erow = 32 * quarter + lane;     // this thread's row of the tile
+        const int et = threadIdx.x - 64;          // 0..255
+        float* xp = reinterpret_cast<float*>(smem + L0.off_xp) + (size_t)ew * L0.xp_floats;
+        int* queue = reinterpret_cast<int*>(smem + L0.off_queue) + ew * EXP_QUEUE;
+        unsigned gc = 0;
+        bool ok = true;
+        unsigned long long n_passed = 0, n_pairs = 0;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const Tile tl = tiles[t];
+            const int n_groups = (tl.m + BN - 1) / BN;
+            const int mI = min(BM, tl.m - tl.i0);
+            const int* ids = perm + tl.row0;      // the leaf's members in leaf order
+            epi_barrier();                        // the previous tile's rows are done with sPass / sThr
+            for (int w = et; w < BM * PW; w += EPI_WARPS * 32) sPass[w] = 0u;
+            if (et < BM) {
+                float thr = -1.0f, nrm = 0.0f;
+                if (et < mI) {
+                    const int id = ids[tl.i0 + et];
+                    thr = __ldcg(knn_dist + (size_t)id * K + (K - 1));
+                    nrm = norms[tl.row0 + tl.i0 + et];
+                }
+                sThr[et] = thr;
+                sNrmA[et] = nrm;
+            }
+            for (int g = 0; g < n_groups && ok; ++g, ++gc) {
+                const int ab = gc & 1;
+                const int j0 = g * BN;
+                float* nB = sNrmB + ab * BN;
+                nB[et] = (j0 + et < tl.m) ? norms[tl.row0 + j0 + et] : 0.0f;
+                // the wait of every thread is bounded; whether to go on is decided together
+                // after the barrier, so that no warp leaves the others at a barrier
+                mbar_wait(bar_acc_full + 8 * ab, (gc >> 1) & 1u, sAbort);
+                epi_barrier();                    // also: sThr (row phase), sNrm*, cleared sPass
+                if (*sAbort) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                {
+                    const float thr = sThr[erow];
+                    const float n_row = sNrmA[erow];
+                    const bool live = erow < mI;
+#pragma unroll 1
+                    for (int sb = 0; sb < 4; ++sb) {
+                        const int c0 = 128 * half + 32 * sb;
+                        float gv[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(ab * BN + c0), gv);
+                        unsigned word = 0;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const int j = j0 + c0 + c;
+                            const float nn = n_row + nB[c0 + c];
+                            const float d2 = __fmaf_rn(-2.0f, gv[c], nn) - margin * nn;
+                            // !(d2 >= thr) keeps the candidate when anything is not a number
+                            if (j < tl.m && j != tl.i0 + erow && !(d2 >= thr)) word |= 1u << c;
+                        }
+                        if (live) {
+                            sPass[erow * PW + (j0 >> 5) + (c0 >> 5)] = word;
+                            n_passed += __popc(word);
+                            n_pairs += max(0, min(32, tl.m - (j0 + c0)));
+                        }
+                    }
+                }
+                // the accumulator may be overwritten once every warp has read its part
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
+                epi_barrier();                    // pass words of this group complete
+
+                // ---- rows of the tile: exact distances of passing candidates ----
+                // A row is flushed as soon as 32 candidates wait (its K-th distance then
+                // tightens the filter of the following groups) and after the last group.
+                const bool last_group = (g == n_groups - 1);
+                const int n_words = min((tl.m + 31) >> 5, (g + 1) * (BN / 32));
+                for (int r = ew; r < mI; r += EPI_WARPS) {
+                    int pending = 0;
+                    for (int w = lane; w < n_words; w += 32) pending += __popc(sPass[r * PW + w]);
+#pragma unroll
+                    for (int sft = 16; sft >= 1; sft >>= 1) pending += __shfl_xor_sync(RSFK_FULL, pending, sft);
+                    if (pending == 0 || (pending < 32 && !last_group)) continue;
+                    const int self = ids[tl.i0 + r];
+                    __syncwarp();
+                    for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)self * D + k);
+                    WarpList<KPL> L;
+                    L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                    __syncwarp();
+                    bool changed = false;
+                    int qn = 0;
+                    for (int w = 0; w < n_words; ++w) {
+                        const unsigned bits = sPass[r * PW + w];
+                        if (bits == 0) continue;
+                        __syncwarp();
+                        if (lane == 0) sPass[r * PW + w] = 0u;
+                        const bool pass = (bits >> lane) & 1u;
+                        if (pass) queue[qn + __popc(bits & ((1u << lane) - 1u))] = ids[32 * w + lane];
+                        qn += __popc(bits);
+                        __syncwarp();
+                        if (qn >= 32) {
+                            explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
+                            __syncwarp();
+                            const int rest = qn - 32;
+                            const int tmp = lane < rest ? queue[32 + lane] : -1;
+                            __syncwarp();
+                            if (lane < rest) queue[lane] = tmp;
+                            qn = rest;
+                            __syncwarp();
+                        }
+                    }
+                    if (qn > 0) explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
+                    if (changed) {
+                        L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+                        if (lane == 0) sThr[r] = L.thr_d;
+                    }
+                }
+            }
+        }
+        if (stats != nullptr) {
+#pragma unroll
+            for (int sft = 16; sft >= 1; sft >>= 1) {
+                n_passed += __shfl_xor_sync(RSFK_FULL, n_passed, sft);
+                n_pairs += __shfl_xor_sync(RSFK_FULL, n_pairs, sft);
+            }
+            if (lane == 0 && n_pairs) {
+                atomicAdd(&stats[0], n_passed);
+                atomicAdd(&stats[1], n_pairs);
+            }
+        }
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TC_ROWS)
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
                      : "memory");
     }
-    if (failed && threadIdx.x == 0) atomicExch(error_flag, 1);
+    if (threadIdx.x == 0 && *sAbort) atomicExch(error_flag, 1);
 }
 
 } // namespace tc

@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <atomic>
+#include <chrono>
 #include <string>
 #include <vector>
 
@@ -35,19 +36,29 @@ struct Node {
     int rec;        // row of the node in the tree index (when one is kept)
 };
 
+// Sizes of one tree level: how many open nodes it splits, how many work chunks
+// they make, how many points they hold.
+struct LevelState {
+    int n_nodes, n_chunks, active, pad;
+};
+
 struct LevelCounters {
-    int n_nodes_next;
-    int n_chunks_next;
+    // Level L reads lvl[L % 3], collects the next level in lvl[(L+1) % 3] and clears
+    // lvl[(L+2) % 3], so that a batch of levels can be enqueued without the host.
+    LevelState lvl[3];
     int n_leaves;
     int max_leaf;
     int min_leaf;
     int error;
-    int active_next; // points of the next level's open nodes
     int n_small;     // nodes handed to the in-CTA subtree kernel
     int max_level;   // deepest level any subtree reached
     int n_recs;      // rows of the tree index handed out so far
+    int last_depth;  // 1 + the deepest level the level kernels split
     unsigned long long sub_active; // points projected inside subtree CTAs (all levels)
     unsigned long long sub_nodes;  // nodes split inside subtree CTAs
+    unsigned long long lvl_active; // points projected by the level kernels (all levels)
+    unsigned long long lvl_nodes;  // nodes split by the level kernels
+    unsigned long long leaf_sq;    // sum over leaves of count^2
 };
 
 // Per-level mailbox in pinned, device-mapped host memory: the scatter kernel of a
@@ -78,9 +89,19 @@ struct Stats {
         project_launches += o.project_launches; tree_build_us += o.tree_build_us;
         sub_active_points += o.sub_active_points; sub_nodes += o.sub_nodes;
         route_us += o.route_us; query_update_us += o.query_update_us;
+        tc_launches += o.tc_launches; tc_gram_flops += o.tc_gram_flops;
     }
     double route_us = 0.0;            // query path: device time of hyperplanes + descent + grouping by leaf
     double query_update_us = 0.0;     // query path: device time of the query-bucket kernels
+    long long tc_launches = 0;        // bucket-KNN launches that took the tensor-core kernel
+    double tc_gram_flops = 0.0;       // 2*D*sum(m_b^2) over the leaves of those launches
+};
+
+// Host-observed and device-measured parts of one tree build, in seconds; they fill
+// the per-tree rows of the forest log.
+struct TreeTimes {
+    float init_s = 0, build_s = 0, project_s = 0, decide_s = 0, scatter_s = 0, wait_s = 0, alloc_s = 0,
+          subtree_s = 0, end_s = 0;
 };
 
 struct TreeResult {
@@ -96,6 +117,8 @@ struct TreeResult {
     // a ref < 0 names the leaf slot -1-ref.  Row 0 is the root.
     const int4* records = nullptr;
     int n_records = 0;
+    TreeTimes times;
+    double sum_leaf_sq = 0.0; // sum over leaves of (points in the leaf)^2
 };
 
 struct Context {
@@ -107,38 +130,64 @@ struct Context {
     std::string message;
 
     enum Slot {
-        PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT,
+        PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT, NODE_DONE,
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
         SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
         RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
-        LANE_IDX, LANE_DIST, SYM_DEGREE, SYM_BLOCKS,
+        LANE_IDX, LANE_DIST, SYM_DEGREE, SYM_BLOCKS, TC_ROWS, TC_NORMS, TC_TILES, TC_COUNT, TC_STATS,
         N_SLOTS
     };
     // When set, tree_build keeps the tree index (TreeResult::records) that the
     // query path descends.
     bool keep_index = false;
     bool planes_ready = false; // hyperplanes of the current tree index are materialised
+    // Bucket KNN on the tensor cores: 1 always (where the shape allows it), 0 never,
+    // -1 the library's choice.
+    int tc_mode = -1;
+    // Limits of the bounded waits (negative: the built-in value).  route_step_limit is the
+    // number of tree levels a query may descend before its kernel gives up and raises the
+    // error flag; level_wait_ms is how long the host waits for a tree level's mailbox.
+    int route_step_limit = -1;
+    int level_wait_ms = -1;
+    double alloc_seconds = 0.0; // host time spent growing scratch buffers
     Stats stats;
     Buffer slots[N_SLOTS];
     LevelCounters* host_counters = nullptr; // pinned
     LevelMail* mail = nullptr;              // pinned + mapped
     cudaEvent_t sub_ev[2] = {nullptr, nullptr};
-    cudaEvent_t ann_ev[3] = {nullptr, nullptr, nullptr}; // query path: before routing, after grouping, after the update
-    bool ann_ev_pending = false;
-    // adds the last query update's device times to the stats (waits for its last event)
+    // Query path: three events per query update (before routing, after grouping, after the
+    // update), taken from a pool and turned into times only when somebody asks for the stats
+    // or the forest ends, so that no tree waits for the previous tree's update.
+    std::vector<cudaEvent_t> ann_ev;
+    size_t ann_ev_used = 0;
+    cudaEvent_t* next_ann_events()
+    {
+        if (ann_ev_used + 3 > 3 * 256) resolve_ann_events();
+        while (ann_ev.size() < ann_ev_used + 3) {
+            cudaEvent_t e = nullptr;
+            if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+            ann_ev.push_back(e);
+        }
+        cudaEvent_t* p = &ann_ev[ann_ev_used];
+        ann_ev_used += 3;
+        return p;
+    }
+    // adds the pending query updates' device times to the stats (waits for the last event)
     void resolve_ann_events()
     {
-        if (!ann_ev_pending) return;
-        ann_ev_pending = false;
-        float a = 0.0f, b = 0.0f;
-        if (cudaEventSynchronize(ann_ev[2]) == cudaSuccess &&
-            cudaEventElapsedTime(&a, ann_ev[0], ann_ev[1]) == cudaSuccess &&
-            cudaEventElapsedTime(&b, ann_ev[1], ann_ev[2]) == cudaSuccess) {
-            stats.route_us += a * 1e3;
-            stats.query_update_us += b * 1e3;
+        for (size_t i = 0; i + 3 <= ann_ev_used; i += 3) {
+            float a = 0.0f, b = 0.0f;
+            if (cudaEventSynchronize(ann_ev[i + 2]) == cudaSuccess &&
+                cudaEventElapsedTime(&a, ann_ev[i], ann_ev[i + 1]) == cudaSuccess &&
+                cudaEventElapsedTime(&b, ann_ev[i + 1], ann_ev[i + 2]) == cudaSuccess) {
+                stats.route_us += a * 1e3;
+                stats.query_update_us += b * 1e3;
+            }
         }
+        ann_ev_used = 0;
     }
-    std::vector<cudaEvent_t> level_ev; // two per tree level, reused by every tree
+    std::vector<cudaEvent_t> level_ev; // three per tree level, reused by every tree
+    int level_hint = 0;                // levels the previous tree of this context needed
     bool fail(int code, const std::string& msg)
     {
         if (status == RSFK_OK) { status = code; message = msg; }
@@ -155,12 +204,14 @@ struct Context {
     {
         Buffer& b = slots[s];
         if (b.bytes >= bytes && b.ptr) return b.ptr;
+        const auto t0 = std::chrono::steady_clock::now();
         if (b.ptr) cudaFree(b.ptr);
         b.ptr = nullptr;
         b.bytes = 0;
         size_t want = bytes + bytes / 8 + 256;
         if (!check(cudaMalloc(&b.ptr, want), "cudaMalloc(scratch)")) { status = RSFK_ERR_NOMEM; return nullptr; }
         b.bytes = want;
+        alloc_seconds += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
         return b.ptr;
     }
     // device counter of candidates evaluated by exploration sweeps (zeroed once)
@@ -169,6 +220,14 @@ struct Context {
         const bool fresh = slots[EXPLORE_COUNT].ptr == nullptr;
         auto* p = (unsigned long long*)scratch(EXPLORE_COUNT, sizeof(unsigned long long));
         if (p && fresh) cudaMemsetAsync(p, 0, sizeof(unsigned long long), stream);
+        return p;
+    }
+    // device counters of the tensor-core bucket kernel: pairs passed by its filter, pairs seen
+    unsigned long long* tc_counters()
+    {
+        const bool fresh = slots[TC_STATS].ptr == nullptr;
+        auto* p = (unsigned long long*)scratch(TC_STATS, 2 * sizeof(unsigned long long));
+        if (p && fresh) cudaMemsetAsync(p, 0, 2 * sizeof(unsigned long long), stream);
         return p;
     }
     // device word a kernel sets when one of its bounded waits gave up (zeroed once)
@@ -200,8 +259,9 @@ struct Context {
         if (host_counters) { cudaFreeHost(host_counters); host_counters = nullptr; }
         if (mail) { cudaFreeHost(mail); mail = nullptr; }
         for (auto& e : sub_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
-        for (auto& e : ann_ev) { if (e) cudaEventDestroy(e); e = nullptr; }
-        ann_ev_pending = false;
+        for (auto& e : ann_ev) cudaEventDestroy(e);
+        ann_ev.clear();
+        ann_ev_used = 0;
         for (auto& e : level_ev) cudaEventDestroy(e);
         level_ev.clear();
         if (owns_stream && stream) { cudaStreamDestroy(stream); stream = nullptr; }

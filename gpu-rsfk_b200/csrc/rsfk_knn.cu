@@ -947,6 +947,75 @@ bool sort_rows(Context& ctx, int* d_idx, float* d_dist, long long rows, int K)
     return ctx.check(cudaGetLastError(), "sort_rows launch");
 }
 
+// The driver's tensor-map encoder, looked up once (the library does not link libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tensor_map_encoder()
+{
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// Bucket KNN on the tensor cores: leaf-ordered centred copy of the points, tile list,
+// then the persistent pipeline kernel (rsfk_bucket_tc.cuh).
+static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
+                          int* d_idx, float* d_dist)
+{
+    cudaStream_t st = ctx.stream;
+    const int Dp = (D + tc::KC - 1) / tc::KC * tc::KC;
+    const int tile_cap = N / tc::BM + tree.n_leaves + 1;
+    float* rows = (float*)ctx.scratch(Context::TC_ROWS, sizeof(float) * (size_t)N * Dp);
+    float* norms = (float*)ctx.scratch(Context::TC_NORMS, sizeof(float) * (size_t)N);
+    tc::Tile* tiles = (tc::Tile*)ctx.scratch(Context::TC_TILES, sizeof(tc::Tile) * (size_t)tile_cap);
+    int* n_tiles = (int*)ctx.scratch(Context::TC_COUNT, sizeof(int));
+    unsigned long long* counters = ctx.tc_counters();
+    int* flag = ctx.error_flag();
+    if (!rows || !norms || !tiles || !n_tiles || !counters || !flag) return false;
+    EncodeTiledFn encode = tensor_map_encoder();
+    if (!encode) return ctx.fail(RSFK_ERR_CUDA, "bucket_knn: the driver offers no cuTensorMapEncodeTiled");
+    // rows[N][Dp] fp32; a box is 32 floats (128 bytes, the swizzle span) by 128 rows
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)Dp, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)Dp * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)tc::KC, (cuuint32_t)tc::BM};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, rows, dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return ctx.fail(RSFK_ERR_CUDA, "bucket_knn: cuTensorMapEncodeTiled failed");
+
+    if (!ctx.check(cudaMemsetAsync(n_tiles, 0, sizeof(int), st), "clear tile count")) return false;
+    tc::k_tc_tiles<<<(tree.n_leaves + 255) / 256, 256, 0, st>>>(tree.leaf_start, tree.leaf_count, tree.n_leaves,
+                                                               tree.max_leaf, tiles, tile_cap, n_tiles);
+    int row_grid = tile_cap < ctx.sm_count * 8 ? tile_cap : ctx.sm_count * 8;
+    tc::k_tc_rows<<<row_grid, 256, sizeof(float) * (size_t)D, st>>>(d_points, D, Dp, tree.perm, tiles, n_tiles,
+                                                                   tile_cap, rows, norms);
+    const tc::Layout lay = tc::layout_for(D, tree.max_leaf);
+    const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
+    const float margin = tc::filter_margin(D);
+    const int grid = tile_cap < ctx.sm_count ? tile_cap : ctx.sm_count;
+    RSFK_DISPATCH_KPL(K, {
+        auto kern = vec4 ? tc::k_bucket_knn_tc<KPL, true> : tc::k_bucket_knn_tc<KPL, false>;
+        if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
+                       "bucket_knn_tc smem attribute"))
+            return false;
+        kern<<<grid, tc::THREADS, lay.total, st>>>(map, d_points, D, Dp, K, tree.perm, norms, tiles, n_tiles,
+                                                   tile_cap, d_idx, d_dist, tree.max_leaf, margin, counters, flag);
+    });
+    count_launches(3);
+    ctx.stats.tc_launches++;
+    if (tree.sum_leaf_sq > 0) ctx.stats.tc_gram_flops += 2.0 * D * tree.sum_leaf_sq;
+    return ctx.check(cudaGetLastError(), "bucket_knn_tc launch");
+}
+
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
                 int* d_idx, float* d_dist)
 {
@@ -973,30 +1042,13 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     auto bytes = [&](int B, int two) {
         return sizeof(float) * ((size_t)B * (B + 1) + (size_t)(two ? 2 : 1) * B * D) + sizeof(int) * (size_t)(two ? 2 : 1) * B;
     };
-    // D >= 64: Gram tiles on the tensor cores (RSFK_TC=1 always, =0 never; by
-    // default where a leaf no longer fits the SIMT kernel's single shared-memory
+    // D >= 64: Gram tiles on the tensor cores (the context's tc_mode: 1 always, 0 never;
+    // by default where a leaf no longer fits the SIMT kernel's single shared-memory
     // block, which is where that kernel re-stages rows many times)
-    static const int tc_mode = [] { const char* e = getenv("RSFK_TC"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
     const bool simt_single_block = bytes((tree.max_leaf + 3) & ~3, 0) <= budget;
-    const bool want_tc = tc_mode == 1 || (tc_mode == -1 && !simt_single_block);
-    if (want_tc && D >= 64 && tree.max_leaf <= tc::TC_ROWS * tc::TC_MAX_BLOCKS) {
-        const tc::Layout lay = tc::layout_for(D, tree.max_leaf);
-        if (lay.total <= 220 * 1024) {
-            int* flag = ctx.error_flag();
-            if (!flag) return false;
-            const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
-            RSFK_DISPATCH_KPL(K, {
-                auto kern = vec4 ? tc::k_bucket_knn_tc<KPL, true> : tc::k_bucket_knn_tc<KPL, false>;
-                if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
-                               "bucket_knn_tc smem attribute"))
-                    return false;
-                kern<<<tree.n_leaves, KNN_THREADS, lay.total, launch_stream>>>(
-                    d_points, D, K, tree.perm, tree.leaf_start, tree.leaf_count, d_idx, d_dist, tree.max_leaf, flag);
-            });
-            count_launches(1);
-            return ctx.check(cudaGetLastError(), "bucket_knn_tc launch");
-        }
-    }
+    const bool want_tc = ctx.tc_mode == 1 || (ctx.tc_mode == -1 && !simt_single_block);
+    if (want_tc && D >= 64 && tree.max_leaf <= tc::MAX_LEAF && tc::layout_for(D, tree.max_leaf).total <= 227 * 1024)
+        return bucket_knn_tc(ctx, d_points, N, D, K, tree, d_idx, d_dist);
     // block size: the whole leaf when it fits, else the largest that fits twice
     int B = (tree.max_leaf + 3) & ~3;
     if (B < 4) B = 4;
@@ -1062,10 +1114,9 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
     int* q_order = (int*)ctx.scratch(Context::QUERY_ORDER, sizeof(int) * (size_t)NQ);
     int* leaf_queries = (int*)ctx.scratch(Context::LEAF_QUERIES, sizeof(int) * (size_t)(tree.n_leaves + 1));
     if (ctx.status != RSFK_OK) return false;
-    ctx.resolve_ann_events();
-    for (auto& e : ctx.ann_ev)
-        if (!e && !ctx.check(cudaEventCreate(&e), "cudaEventCreate")) return false;
-    cudaEventRecord(ctx.ann_ev[0], st);
+    cudaEvent_t* ev = ctx.next_ann_events();
+    if (!ev) return ctx.fail(RSFK_ERR_CUDA, "ann_bucket_knn: cudaEventCreate failed");
+    cudaEventRecord(ev[0], st);
     if (!ctx.check(cudaMemsetAsync(leaf_queries, 0, sizeof(int) * (size_t)(tree.n_leaves + 1), st),
                    "clear leaf counts"))
         return false;
@@ -1075,7 +1126,7 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
     if (grid > ctx.sm_count * 16) grid = ctx.sm_count * 16;
     k_place_queries<<<grid, 256, 0, st>>>(q_leaf, NQ, leaf_queries, q_order);
     count_launches(2);
-    cudaEventRecord(ctx.ann_ev[1], st);
+    cudaEventRecord(ev[1], st);
     // leaf_queries[n_leaves] = number of queries that reached a leaf = entries of q_order
     const size_t smem = sizeof(float) * (size_t)KNN_WARPS * D;
     if (smem > 200 * 1024) return ctx.fail(RSFK_ERR_UNSUPPORTED, "ann_bucket_knn: D too large");
@@ -1097,8 +1148,7 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
                                                                 tree.max_leaf, d_idx, d_dist);
         });
         count_launches(1);
-        cudaEventRecord(ctx.ann_ev[2], st);
-        ctx.ann_ev_pending = true;
+        cudaEventRecord(ev[2], st);
         return ctx.check(cudaGetLastError(), "query leaf launch");
     }
     RSFK_DISPATCH_KPL(K, {
@@ -1112,8 +1162,7 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
                                                      leaf_queries + tree.n_leaves, d_idx, d_dist);
     });
     count_launches(1);
-    cudaEventRecord(ctx.ann_ev[2], st);
-    ctx.ann_ev_pending = true;
+    cudaEventRecord(ev[2], st);
     return ctx.check(cudaGetLastError(), "query bucket launch");
 }
 

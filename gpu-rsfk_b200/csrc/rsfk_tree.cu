@@ -3,15 +3,20 @@
 // The points of a node are one contiguous segment of a permutation array; a
 // split is a stable partition of that segment (left side first), so a leaf's
 // bucket is simply perm[start, start+count) and no per-point parent/depth
-// bookkeeping exists.  Each level runs three kernels over the level's work
+// bookkeeping exists.  Each level runs two kernels over the level's work
 // chunks (CHUNK consecutive positions of one node):
 //
 //   project : side bit of every active point (n.x < c  =>  right) as one
-//             32-bit mask per 32 positions, plus the chunk's left count;
-//   decide  : per node, the left total and the per-chunk exclusive prefix;
-//             children, leaves and next level's chunk list;
+//             32-bit mask per 32 positions, plus the chunk's left count; the
+//             CTA that finishes the last chunk of a node then decides the node:
+//             left total and per-chunk exclusive prefix, children, leaves and
+//             the next level's chunk list;
 //   scatter : stable partition into the other permutation buffer; points
 //             whose child is a leaf are also written to the final array.
+//
+// The sizes of a level (nodes, chunks) live in device memory and the kernels
+// loop over them, so the host enqueues several levels at a time and looks at
+// the level mailbox once per batch.
 //
 // The rules (which side is right, when a child is a leaf, when a small child
 // dissolves into its sibling) follow the reference's level kernels:
@@ -183,124 +188,7 @@ __device__ __forceinline__ unsigned project_group(const float* __restrict__ pts,
 }
 
 // ---------------------------------------------------------------------------
-// project, any D: one warp per point, four points in flight per warp.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(TREE_THREADS)
-k_project_wide(const float* __restrict__ pts, int D, const int* __restrict__ perm,
-               const Node* __restrict__ nodes, const int* __restrict__ chunk_node,
-               unsigned* __restrict__ side_bits, int* __restrict__ chunk_left,
-               const int4* __restrict__ table, int n_table, int seed, int level, int vec4,
-               int4* __restrict__ records)
-{
-    extern __shared__ float4 smem4[];
-    float* sN = reinterpret_cast<float*>(smem4);
-    __shared__ float sC;
-    __shared__ int sPair[2];
-    __shared__ int sLeft;
-
-    const int chunk = blockIdx.x;
-    const Node nd = nodes[chunk_node[chunk]];
-    const int off = (chunk - nd.chunk_base) * CHUNK;
-    const int cnt = min(CHUNK, nd.count - off);
-    if (threadIdx.x == 0) {
-        int p1, p2;
-        node_pair(nd, perm, table, n_table, seed, level, p1, p2);
-        sPair[0] = p1;
-        sPair[1] = p2;
-        sLeft = 0;
-        if (records != nullptr && off == 0) { // the node's first chunk files the split pair
-            records[nd.rec].x = p1;
-            records[nd.rec].y = p2;
-        }
-    }
-    __syncthreads();
-    const float c = load_hyperplane(pts, D, sPair[0], sPair[1], level == 0, sN, &sC);
-
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    const int* ids = perm + nd.start + off;
-    int left_total = 0;
-    for (int w = warp; w * 32 < cnt; w += n_warps) {
-        const int base = w * 32;
-        const int here = min(32, cnt - base);
-        const int my_id = lane < here ? ids[base + lane] : -1;
-        const unsigned mask = project_group(pts, D, vec4 != 0, sN, c, my_id, here, lane);
-        if (lane == 0) {
-            side_bits[(size_t)chunk * CHUNK_WORDS + w] = mask;
-            left_total += here - __popc(mask);
-        }
-    }
-    if (lane == 0 && left_total) atomicAdd(&sLeft, left_total);
-    __syncthreads();
-    if (threadIdx.x == 0) chunk_left[chunk] = sLeft;
-}
-
-// ---------------------------------------------------------------------------
-// project, D <= 16: one thread per point.  Lanes >= D of the reference's
-// 32-lane sum hold zero, and adding zero changes no comparison, so only
-// VL = next power of two >= D partial sums are kept and combined in the
-// butterfly's order.
-// ---------------------------------------------------------------------------
-template <int VL>
-__global__ void __launch_bounds__(TREE_THREADS)
-k_project_small(const float* __restrict__ pts, int D, const int* __restrict__ perm,
-                const Node* __restrict__ nodes, const int* __restrict__ chunk_node,
-                unsigned* __restrict__ side_bits, int* __restrict__ chunk_left,
-                const int4* __restrict__ table, int n_table, int seed, int level,
-                int4* __restrict__ records)
-{
-    __shared__ float sN[VL];
-    __shared__ float sC;
-    __shared__ int sPair[2];
-    __shared__ int sLeft;
-
-    const int chunk = blockIdx.x;
-    const Node nd = nodes[chunk_node[chunk]];
-    const int off = (chunk - nd.chunk_base) * CHUNK;
-    const int cnt = min(CHUNK, nd.count - off);
-    if (threadIdx.x == 0) {
-        int p1, p2;
-        node_pair(nd, perm, table, n_table, seed, level, p1, p2);
-        sPair[0] = p1;
-        sPair[1] = p2;
-        sLeft = 0;
-        if (records != nullptr && off == 0) { // the node's first chunk files the split pair
-            records[nd.rec].x = p1;
-            records[nd.rec].y = p2;
-        }
-    }
-    __syncthreads();
-    const float c = load_hyperplane(pts, D, sPair[0], sPair[1], level == 0, sN, &sC);
-
-    const int lane = threadIdx.x & 31;
-    const int* ids = perm + nd.start + off;
-    int left_total = 0;
-    for (int base = (threadIdx.x >> 5) * 32; base < cnt; base += blockDim.x) {
-        const int i = base + lane;
-        bool right = false;
-        if (i < cnt) {
-            const float* x = pts + (size_t)ids[i] * D;
-            float acc[VL];
-#pragma unroll
-            for (int k = 0; k < VL; ++k) acc[k] = k < D ? __fmaf_rn(sN[k], __ldg(x + k), 0.0f) : 0.0f;
-#pragma unroll
-            for (int stride = 1; stride < VL; stride <<= 1)
-#pragma unroll
-                for (int k = 0; k < VL; k += 2 * stride) acc[k] = __fadd_rn(acc[k], acc[k + stride]);
-            right = acc[0] < c;
-        }
-        const unsigned mask = __ballot_sync(RSFK_FULL, right);
-        if (lane == 0) {
-            side_bits[(size_t)chunk * CHUNK_WORDS + (base >> 5)] = mask;
-            left_total += min(32, cnt - base) - __popc(mask);
-        }
-    }
-    if (lane == 0 && left_total) atomicAdd(&sLeft, left_total);
-    __syncthreads();
-    if (threadIdx.x == 0) chunk_left[chunk] = sLeft;
-}
-
-// ---------------------------------------------------------------------------
-// decide: one warp per node.
+// decide: what becomes of a node once all its chunks are projected (one warp).
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int emit_leaf(int start, int count, int* leaf_start, int* leaf_count,
                                          int leaf_cap, LevelCounters* cnt)
@@ -314,6 +202,7 @@ __device__ __forceinline__ int emit_leaf(int start, int count, int* leaf_start, 
     }
     atomicMax(&cnt->max_leaf, count);
     atomicMin(&cnt->min_leaf, count);
+    atomicAdd(&cnt->leaf_sq, (unsigned long long)count * (unsigned long long)count);
     return slot;
 }
 
@@ -388,65 +277,84 @@ __device__ __forceinline__ int child_table_row(const int4* __restrict__ table, i
     return side ? t.w : t.z;
 }
 
-__global__ void __launch_bounds__(TREE_THREADS)
-k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_left,
-         Node* __restrict__ nodes_out, int node_cap, int* __restrict__ chunk_node_out, int chunk_cap,
-         NodeSplit* __restrict__ split, int* __restrict__ leaf_start, int* __restrict__ leaf_count,
-         int leaf_cap, Node* __restrict__ small_nodes, int small_cap, int small_limit, int child_level,
-         LevelCounters* __restrict__ cnt, const int4* __restrict__ table, int n_table,
-         int min_children, int max_children, int4* __restrict__ records, int rec_cap)
-{
-    const int lane = threadIdx.x & 31;
-    const int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (node >= n_nodes) return;
-    const Node nd = nodes[node];
-    const int n_chunks = (nd.count + CHUNK - 1) / CHUNK;
+// Everything a level kernel needs besides the points.
+struct LevelArgs {
+    const int* perm;            // this level's permutation
+    const Node* nodes;          // this level's open nodes
+    const int* chunk_node;      // node of every work chunk
+    unsigned* side_bits;
+    int* chunk_left;            // left count per chunk, then the exclusive prefix inside the node
+    int* node_done;             // chunks of a node projected so far (all zero between levels)
+    Node* nodes_out;
+    int node_cap;
+    int* chunk_node_out;
+    int chunk_cap;
+    NodeSplit* split;
+    int* leaf_start;
+    int* leaf_count;
+    int leaf_cap;
+    Node* small_nodes;
+    int small_cap, small_limit;
+    LevelCounters* cnt;
+    const int4* table;
+    int n_table;
+    int seed, level;
+    int min_children, max_children;
+    int4* records;
+    int rec_cap;
+};
 
+// One warp; every chunk of the node has posted its left count.
+__device__ __forceinline__ void decide_node(const LevelArgs& a, int node, const Node& nd, int lane)
+{
+    LevelCounters* cnt = a.cnt;
+    LevelState* next = &cnt->lvl[(a.level + 1) % 3];
+    const int n_chunks = (nd.count + CHUNK - 1) / CHUNK;
     // left total; chunk_left becomes the exclusive prefix inside the node
     int carry = 0;
     for (int c0 = 0; c0 < n_chunks; c0 += 32) {
         const int c = c0 + lane;
-        int v = c < n_chunks ? chunk_left[nd.chunk_base + c] : 0;
+        int v = c < n_chunks ? __ldcg(a.chunk_left + nd.chunk_base + c) : 0;
         int incl = v;
 #pragma unroll
         for (int s = 1; s < 32; s <<= 1) {
             int t = __shfl_up_sync(RSFK_FULL, incl, s);
             if (lane >= s) incl += t;
         }
-        if (c < n_chunks) chunk_left[nd.chunk_base + c] = carry + incl - v;
+        if (c < n_chunks) a.chunk_left[nd.chunk_base + c] = carry + incl - v;
         carry += __shfl_sync(RSFK_FULL, incl, 31);
     }
     const int nL = carry;
-    const Children ch = decide_children(nd.start, nd.count, nL, min_children, max_children);
+    const Children ch = decide_children(nd.start, nd.count, nL, a.min_children, a.max_children);
 
     // a child's points are final (copied to perm_final by the scatter) when it
     // is a leaf or small enough to be finished inside one CTA
     int flags = 0;
     int ref[2] = {0, 0}; // lane 0: where each child went (row, or -1-leaf slot)
     for (int k = 0; k < ch.n; ++k) {
-        const bool small = !ch.leaf[k] && ch.count[k] <= small_limit;
+        const bool small = !ch.leaf[k] && ch.count[k] <= a.small_limit;
         const bool fin = ch.leaf[k] || small;
         if (fin) flags |= (ch.n == 2) ? (1 << k) : 3;
         if (ch.leaf[k]) {
             if (lane == 0)
-                ref[k] = -1 - emit_leaf(ch.start[k], ch.count[k], leaf_start, leaf_count, leaf_cap, cnt);
+                ref[k] = -1 - emit_leaf(ch.start[k], ch.count[k], a.leaf_start, a.leaf_count, a.leaf_cap, cnt);
             continue;
         }
         Node o;
         o.start = ch.start[k];   o.count = ch.count[k];
         o.pstart = ch.pstart[k]; o.pcount = ch.pcount[k];
-        o.tbl = child_table_row(table, n_table, nd.tbl, ch.side[k]);
+        o.tbl = child_table_row(a.table, a.n_table, nd.tbl, ch.side[k]);
         o.chunk_base = 0;
-        o.level = child_level;
+        o.level = a.level + 1;
         o.rec = 0;
         // an only child takes over its parent's row: both sides of the parent lead to it, so a
         // query loses nothing by starting at the child's split, and a node that fails to split
         // again and again (coincident points) does not use up a row per attempt
-        if (lane == 0) ref[k] = o.rec = (ch.n == 1) ? nd.rec : new_record(records, rec_cap, cnt);
+        if (lane == 0) ref[k] = o.rec = (ch.n == 1) ? nd.rec : new_record(a.records, a.rec_cap, cnt);
         if (small) {
             if (lane == 0) {
                 const int slot = atomicAdd(&cnt->n_small, 1);
-                if (slot < small_cap) small_nodes[slot] = o;
+                if (slot < a.small_cap) a.small_nodes[slot] = o;
                 else cnt->error = RSFK_ERR_OVERFLOW;
             }
             continue;
@@ -454,26 +362,181 @@ k_decide(const Node* __restrict__ nodes, int n_nodes, int* __restrict__ chunk_le
         const int nch = (ch.count[k] + CHUNK - 1) / CHUNK;
         int slot = 0, cb = 0;
         if (lane == 0) {
-            slot = atomicAdd(&cnt->n_nodes_next, 1);
-            cb = atomicAdd(&cnt->n_chunks_next, nch);
-            atomicAdd(&cnt->active_next, ch.count[k]);
+            slot = atomicAdd(&next->n_nodes, 1);
+            cb = atomicAdd(&next->n_chunks, nch);
+            atomicAdd(&next->active, ch.count[k]);
         }
         slot = __shfl_sync(RSFK_FULL, slot, 0);
         cb = __shfl_sync(RSFK_FULL, cb, 0);
-        if (slot >= node_cap || cb + nch > chunk_cap) {
+        if (slot >= a.node_cap || cb + nch > a.chunk_cap) {
             if (lane == 0) cnt->error = RSFK_ERR_OVERFLOW;
             continue;
         }
         if (lane == 0) {
             o.chunk_base = cb;
-            nodes_out[slot] = o;
+            a.nodes_out[slot] = o;
         }
-        for (int c = lane; c < nch; c += 32) chunk_node_out[cb + c] = slot;
+        for (int c = lane; c < nch; c += 32) a.chunk_node_out[cb + c] = slot;
     }
     if (lane == 0) {
-        split[node].n_left = nL;
-        split[node].flags = flags;
-        if (ch.n == 2 || ch.leaf[0]) file_refs(records, nd.rec, ch.n, ref); // else the child rewrites the row
+        a.split[node].n_left = nL;
+        a.split[node].flags = flags;
+        if (ch.n == 2 || ch.leaf[0]) file_refs(a.records, nd.rec, ch.n, ref); // else the child rewrites the row
+    }
+}
+
+// Start of a level kernel: the sizes of this level; one thread clears the state two
+// levels ahead (nobody reads or writes it during this level) and books the level.
+__device__ __forceinline__ LevelState level_begin(const LevelArgs& a)
+{
+    LevelCounters* cnt = a.cnt;
+    const LevelState ls = cnt->lvl[a.level % 3];
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        LevelState* far = &cnt->lvl[(a.level + 2) % 3];
+        far->n_nodes = 0; far->n_chunks = 0; far->active = 0;
+        if (ls.n_nodes > 0) {
+            cnt->lvl_active += (unsigned long long)ls.active;
+            cnt->lvl_nodes += (unsigned long long)ls.n_nodes;
+            cnt->last_depth = a.level + 1;
+        }
+    }
+    return ls;
+}
+
+// End of a chunk (all threads): post the chunk's left count; the CTA that posts the
+// last chunk of a node decides the node.  sLast is a shared flag.
+__device__ __forceinline__ void chunk_done(const LevelArgs& a, int chunk, int node, const Node& nd, int left,
+                                           int* sLast)
+{
+    if (threadIdx.x == 0) {
+        a.chunk_left[chunk] = left;
+        __threadfence();
+        const int nch = (nd.count + CHUNK - 1) / CHUNK;
+        *sLast = (atomicAdd(&a.node_done[node], 1) == nch - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (*sLast && threadIdx.x < 32) {
+        __threadfence();
+        decide_node(a, node, nd, threadIdx.x);
+        if (threadIdx.x == 0) a.node_done[node] = 0;
+    }
+    __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+// project, any D: one warp per point, four (or sixteen) points in flight per warp.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(TREE_THREADS)
+k_project_wide(const float* __restrict__ pts, int D, int vec4, LevelArgs a)
+{
+    extern __shared__ float4 smem4[];
+    float* sN = reinterpret_cast<float*>(smem4);
+    __shared__ float sC;
+    __shared__ int sPair[2];
+    __shared__ int sLeft;
+    __shared__ int sLast;
+
+    const LevelState ls = level_begin(a);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int chunk = blockIdx.x; chunk < ls.n_chunks; chunk += gridDim.x) {
+        const int node = a.chunk_node[chunk];
+        const Node nd = a.nodes[node];
+        const int off = (chunk - nd.chunk_base) * CHUNK;
+        const int cnt = min(CHUNK, nd.count - off);
+        if (threadIdx.x == 0) {
+            int p1, p2;
+            node_pair(nd, a.perm, a.table, a.n_table, a.seed, a.level, p1, p2);
+            sPair[0] = p1;
+            sPair[1] = p2;
+            sLeft = 0;
+            if (a.records != nullptr && off == 0) { // the node's first chunk files the split pair
+                a.records[nd.rec].x = p1;
+                a.records[nd.rec].y = p2;
+            }
+        }
+        __syncthreads();
+        const float c = load_hyperplane(pts, D, sPair[0], sPair[1], a.level == 0, sN, &sC);
+
+        const int* ids = a.perm + nd.start + off;
+        int left_total = 0;
+        for (int w = warp; w * 32 < cnt; w += n_warps) {
+            const int base = w * 32;
+            const int here = min(32, cnt - base);
+            const int my_id = lane < here ? ids[base + lane] : -1;
+            const unsigned mask = project_group(pts, D, vec4 != 0, sN, c, my_id, here, lane);
+            if (lane == 0) {
+                a.side_bits[(size_t)chunk * CHUNK_WORDS + w] = mask;
+                left_total += here - __popc(mask);
+            }
+        }
+        if (lane == 0 && left_total) atomicAdd(&sLeft, left_total);
+        __syncthreads();
+        chunk_done(a, chunk, node, nd, sLeft, &sLast);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// project, D <= 16: one thread per point.  Lanes >= D of the reference's
+// 32-lane sum hold zero, and adding zero changes no comparison, so only
+// VL = next power of two >= D partial sums are kept and combined in the
+// butterfly's order.
+// ---------------------------------------------------------------------------
+template <int VL>
+__global__ void __launch_bounds__(TREE_THREADS)
+k_project_small(const float* __restrict__ pts, int D, LevelArgs a)
+{
+    __shared__ float sN[VL];
+    __shared__ float sC;
+    __shared__ int sPair[2];
+    __shared__ int sLeft;
+    __shared__ int sLast;
+
+    const LevelState ls = level_begin(a);
+    const int lane = threadIdx.x & 31;
+    for (int chunk = blockIdx.x; chunk < ls.n_chunks; chunk += gridDim.x) {
+        const int node = a.chunk_node[chunk];
+        const Node nd = a.nodes[node];
+        const int off = (chunk - nd.chunk_base) * CHUNK;
+        const int cnt = min(CHUNK, nd.count - off);
+        if (threadIdx.x == 0) {
+            int p1, p2;
+            node_pair(nd, a.perm, a.table, a.n_table, a.seed, a.level, p1, p2);
+            sPair[0] = p1;
+            sPair[1] = p2;
+            sLeft = 0;
+            if (a.records != nullptr && off == 0) { // the node's first chunk files the split pair
+                a.records[nd.rec].x = p1;
+                a.records[nd.rec].y = p2;
+            }
+        }
+        __syncthreads();
+        const float c = load_hyperplane(pts, D, sPair[0], sPair[1], a.level == 0, sN, &sC);
+
+        const int* ids = a.perm + nd.start + off;
+        int left_total = 0;
+        for (int base = (threadIdx.x >> 5) * 32; base < cnt; base += blockDim.x) {
+            const int i = base + lane;
+            bool right = false;
+            if (i < cnt) {
+                const float* x = pts + (size_t)ids[i] * D;
+                float acc[VL];
+#pragma unroll
+                for (int k = 0; k < VL; ++k) acc[k] = k < D ? __fmaf_rn(sN[k], __ldg(x + k), 0.0f) : 0.0f;
+#pragma unroll
+                for (int stride = 1; stride < VL; stride <<= 1)
+#pragma unroll
+                    for (int k = 0; k < VL; k += 2 * stride) acc[k] = __fadd_rn(acc[k], acc[k + stride]);
+                right = acc[0] < c;
+            }
+            const unsigned mask = __ballot_sync(RSFK_FULL, right);
+            if (lane == 0) {
+                a.side_bits[(size_t)chunk * CHUNK_WORDS + (base >> 5)] = mask;
+                left_total += min(32, cnt - base) - __popc(mask);
+            }
+        }
+        if (lane == 0 && left_total) atomicAdd(&sLeft, left_total);
+        __syncthreads();
+        chunk_done(a, chunk, node, nd, sLeft, &sLast);
     }
 }
 
@@ -484,63 +547,65 @@ __global__ void __launch_bounds__(TREE_THREADS)
 k_scatter(const int* __restrict__ perm_in, int* __restrict__ perm_out, int* __restrict__ perm_final,
           const Node* __restrict__ nodes, const int* __restrict__ chunk_node,
           const unsigned* __restrict__ side_bits, const int* __restrict__ chunk_lprefix,
-          const NodeSplit* __restrict__ split, LevelCounters* counters, volatile LevelMail* mail, int seq)
+          const NodeSplit* __restrict__ split, const LevelCounters* counters, int level,
+          volatile LevelMail* mail, int seq)
 {
     __shared__ unsigned sMask[CHUNK_WORDS];
     __shared__ int sWordLeft[CHUNK_WORDS];
 
-    // The decide kernel has finished (stream order): post the next level's sizes to
-    // the host mailbox and clear the per-level counters for the next decide kernel.
+    // Every node of the level is decided (stream order): post the next level's sizes
+    // to the host mailbox.
     if (blockIdx.x == 0 && threadIdx.x == 0) {
-        mail->n_nodes = counters->n_nodes_next;
-        mail->n_chunks = counters->n_chunks_next;
-        mail->active = counters->active_next;
+        const LevelState* next = &counters->lvl[(level + 1) % 3];
+        mail->n_nodes = next->n_nodes;
+        mail->n_chunks = next->n_chunks;
+        mail->active = next->active;
         mail->n_small = counters->n_small;
         mail->error = counters->error;
         __threadfence_system();
         mail->seq = seq;
-        counters->n_nodes_next = 0;
-        counters->n_chunks_next = 0;
-        counters->active_next = 0;
     }
 
-    const int chunk = blockIdx.x;
-    const int node = chunk_node[chunk];
-    const Node nd = nodes[node];
-    const NodeSplit sp = split[node];
-    const int off = (chunk - nd.chunk_base) * CHUNK;
-    const int cnt = min(CHUNK, nd.count - off);
-    const int lprefix = chunk_lprefix[chunk];
+    const int n_chunks = counters->lvl[level % 3].n_chunks;
+    for (int chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+        const int node = chunk_node[chunk];
+        const Node nd = nodes[node];
+        const NodeSplit sp = split[node];
+        const int off = (chunk - nd.chunk_base) * CHUNK;
+        const int cnt = min(CHUNK, nd.count - off);
+        const int lprefix = chunk_lprefix[chunk];
 
-    if (threadIdx.x < 32) {
-        const int w = threadIdx.x;
-        const int here = max(0, min(32, cnt - w * 32));
-        const unsigned valid = here >= 32 ? 0xffffffffu : ((1u << here) - 1u);
-        const unsigned m = here > 0 ? (side_bits[(size_t)chunk * CHUNK_WORDS + w] & valid) : 0u;
-        const int lefts = __popc(~m & valid);
-        int incl = lefts;
+        if (threadIdx.x < 32) {
+            const int w = threadIdx.x;
+            const int here = max(0, min(32, cnt - w * 32));
+            const unsigned valid = here >= 32 ? 0xffffffffu : ((1u << here) - 1u);
+            const unsigned m = here > 0 ? (side_bits[(size_t)chunk * CHUNK_WORDS + w] & valid) : 0u;
+            const int lefts = __popc(~m & valid);
+            int incl = lefts;
 #pragma unroll
-        for (int s = 1; s < 32; s <<= 1) {
-            int t = __shfl_up_sync(RSFK_FULL, incl, s);
-            if (w >= s) incl += t;
+            for (int s = 1; s < 32; s <<= 1) {
+                int t = __shfl_up_sync(RSFK_FULL, incl, s);
+                if (w >= s) incl += t;
+            }
+            if (w < CHUNK_WORDS) { // the scan runs on all 32 lanes; a chunk has CHUNK_WORDS words
+                sMask[w] = m;
+                sWordLeft[w] = incl - lefts;
+            }
         }
-        if (w < CHUNK_WORDS) { // the scan runs on all 32 lanes; a chunk has CHUNK_WORDS words
-            sMask[w] = m;
-            sWordLeft[w] = incl - lefts;
+        __syncthreads();
+        for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+            const int w = i >> 5, b = i & 31;
+            const unsigned m = sMask[w];
+            const bool right = (m >> b) & 1u;
+            const int lrank = sWordLeft[w] + __popc(~m & ((1u << b) - 1u));
+            const int lefts_before = lprefix + lrank;
+            const int dest = right ? nd.start + sp.n_left + (off + i - lefts_before)
+                                   : nd.start + lefts_before;
+            const int id = perm_in[nd.start + off + i];
+            perm_out[dest] = id;
+            if (sp.flags & (right ? 2 : 1)) perm_final[dest] = id;
         }
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
-        const int w = i >> 5, b = i & 31;
-        const unsigned m = sMask[w];
-        const bool right = (m >> b) & 1u;
-        const int lrank = sWordLeft[w] + __popc(~m & ((1u << b) - 1u));
-        const int lefts_before = lprefix + lrank;
-        const int dest = right ? nd.start + sp.n_left + (off + i - lefts_before)
-                               : nd.start + lefts_before;
-        const int id = perm_in[nd.start + off + i];
-        perm_out[dest] = id;
-        if (sp.flags & (right ? 2 : 1)) perm_final[dest] = id;
+        __syncthreads();
     }
 }
 
@@ -754,26 +819,27 @@ k_subtree(const float* __restrict__ pts, int D, int* __restrict__ perm_final,
 
 // Depth limit reached: every open node becomes leaves of at most max_children
 // points (consecutive pieces of its segment).
-__global__ void k_force_leaves(const Node* __restrict__ nodes, int n_nodes, const int* __restrict__ perm,
-                               int* __restrict__ perm_final, int* __restrict__ leaf_start,
-                               int* __restrict__ leaf_count, int leaf_cap, LevelCounters* cnt,
-                               int max_children, int4* __restrict__ records)
+__global__ void k_force_leaves(const Node* __restrict__ nodes, const LevelCounters* counters, int level,
+                               const int* __restrict__ perm, int* __restrict__ perm_final,
+                               int* __restrict__ leaf_start, int* __restrict__ leaf_count, int leaf_cap,
+                               LevelCounters* cnt, int max_children, int4* __restrict__ records)
 {
-    const int node = blockIdx.x;
-    if (node >= n_nodes) return;
-    const Node nd = nodes[node];
-    for (int i = threadIdx.x; i < nd.count; i += blockDim.x) perm_final[nd.start + i] = perm[nd.start + i];
-    if (threadIdx.x == 0) {
-        const int piece = max(1, max_children);
-        const int q = (nd.count + piece - 1) / piece;
-        int first = 0;
-        for (int i = 0; i < q; ++i) {
-            int a = (int)((long long)nd.count * i / q), b = (int)((long long)nd.count * (i + 1) / q);
-            const int slot = emit_leaf(nd.start + a, b - a, leaf_start, leaf_count, leaf_cap, cnt);
-            if (i == 0) first = slot;
+    const int n_nodes = counters->lvl[level % 3].n_nodes;
+    for (int node = blockIdx.x; node < n_nodes; node += gridDim.x) {
+        const Node nd = nodes[node];
+        for (int i = threadIdx.x; i < nd.count; i += blockDim.x) perm_final[nd.start + i] = perm[nd.start + i];
+        if (threadIdx.x == 0) {
+            const int piece = max(1, max_children);
+            const int q = (nd.count + piece - 1) / piece;
+            int first = 0;
+            for (int i = 0; i < q; ++i) {
+                int a = (int)((long long)nd.count * i / q), b = (int)((long long)nd.count * (i + 1) / q);
+                const int slot = emit_leaf(nd.start + a, b - a, leaf_start, leaf_count, leaf_cap, cnt);
+                if (i == 0) first = slot;
+            }
+            if (records != nullptr) // no split: queries go to the first piece
+                records[nd.rec] = make_int4(-1, -1, -1 - first, -1 - first);
         }
-        if (records != nullptr) // no split: queries go to the first piece
-            records[nd.rec] = make_int4(-1, -1, -1 - first, -1 - first);
     }
 }
 
@@ -782,8 +848,17 @@ __global__ void k_iota(int* p, int n)
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) p[i] = i;
 }
 
-__global__ void k_tree_init(Node* nodes, int* chunk_node, int n_chunks, int N, int has_table,
-                            LevelCounters* cnt)
+__device__ __forceinline__ void clear_counters(LevelCounters* cnt)
+{
+    for (int l = 0; l < 3; ++l) { cnt->lvl[l].n_nodes = 0; cnt->lvl[l].n_chunks = 0; cnt->lvl[l].active = 0; cnt->lvl[l].pad = 0; }
+    cnt->n_leaves = 0; cnt->max_leaf = 0; cnt->min_leaf = 0x7fffffff; cnt->error = 0;
+    cnt->n_small = 0; cnt->max_level = 0; cnt->n_recs = 1; // row 0 is the root
+    cnt->last_depth = 0;
+    cnt->sub_active = 0; cnt->sub_nodes = 0; cnt->lvl_active = 0; cnt->lvl_nodes = 0; cnt->leaf_sq = 0;
+}
+
+__global__ void k_tree_init(Node* nodes, int* chunk_node, int* node_done, int node_cap, int n_chunks, int N,
+                            int has_table, LevelCounters* cnt)
 {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t == 0) {
@@ -792,45 +867,70 @@ __global__ void k_tree_init(Node* nodes, int* chunk_node, int n_chunks, int N, i
         r.tbl = has_table ? 0 : -1;
         r.chunk_base = 0; r.level = 0; r.rec = 0;
         nodes[0] = r;
-        cnt->n_recs = 1; // row 0 is the root
-        cnt->n_nodes_next = 0; cnt->n_chunks_next = 0; cnt->n_leaves = 0;
-        cnt->max_leaf = 0; cnt->min_leaf = 0x7fffffff; cnt->error = 0; cnt->active_next = 0;
-        cnt->n_small = 0; cnt->max_level = 0; cnt->sub_active = 0; cnt->sub_nodes = 0;
+        clear_counters(cnt);
+        cnt->lvl[0].n_nodes = 1; cnt->lvl[0].n_chunks = n_chunks; cnt->lvl[0].active = N;
     }
     for (int c = t; c < n_chunks; c += gridDim.x * blockDim.x) chunk_node[c] = 0;
+    for (int c = t; c < node_cap; c += gridDim.x * blockDim.x) node_done[c] = 0;
 }
 
 __global__ void k_single_leaf(int* leaf_start, int* leaf_count, int N, LevelCounters* cnt, int4* records)
 {
     leaf_start[0] = 0;
     leaf_count[0] = N;
-    cnt->n_recs = 1;
+    clear_counters(cnt);
     if (records != nullptr) records[0] = make_int4(-1, -1, -1, -1); // every query: leaf slot 0
-    cnt->n_leaves = 1; cnt->max_leaf = N; cnt->min_leaf = N; cnt->error = 0;
-    cnt->n_nodes_next = 0; cnt->n_chunks_next = 0;
-    cnt->n_small = 0; cnt->max_level = 0; cnt->sub_active = 0; cnt->sub_nodes = 0; cnt->active_next = 0;
+    cnt->n_leaves = 1; cnt->max_leaf = N; cnt->min_leaf = N;
+    cnt->leaf_sq = (unsigned long long)N * (unsigned long long)N;
 }
 
 // ---------------------------------------------------------------------------
-static void launch_project(Context& ctx, const float* pts, int D, const int* perm, const Node* nodes,
-                           const int* chunk_node, int n_chunks, unsigned* side_bits, int* chunk_left,
-                           const int4* table, int n_table, int seed, int level, int4* records)
+static void launch_project(Context& ctx, const float* pts, int D, int grid, const LevelArgs& a)
 {
     cudaStream_t st = ctx.stream;
-#define RSFK_SMALL(VL)                                                                              \
-    k_project_small<VL><<<n_chunks, TREE_THREADS, 0, st>>>(pts, D, perm, nodes, chunk_node,         \
-                                                           side_bits, chunk_left, table, n_table,   \
-                                                           seed, level, records)
-    if (D <= 2) RSFK_SMALL(2);
-    else if (D <= 4) RSFK_SMALL(4);
-    else if (D <= 8) RSFK_SMALL(8);
-    else if (D <= 16) RSFK_SMALL(16);
+    if (D <= 2) k_project_small<2><<<grid, TREE_THREADS, 0, st>>>(pts, D, a);
+    else if (D <= 4) k_project_small<4><<<grid, TREE_THREADS, 0, st>>>(pts, D, a);
+    else if (D <= 8) k_project_small<8><<<grid, TREE_THREADS, 0, st>>>(pts, D, a);
+    else if (D <= 16) k_project_small<16><<<grid, TREE_THREADS, 0, st>>>(pts, D, a);
     else
-        k_project_wide<<<n_chunks, TREE_THREADS, (size_t)D * sizeof(float), st>>>(
-            pts, D, perm, nodes, chunk_node, side_bits, chunk_left, table, n_table, seed, level,
-            (D % 4 == 0 && ((uintptr_t)pts & 15) == 0) ? 1 : 0, records);
-#undef RSFK_SMALL
+        k_project_wide<<<grid, TREE_THREADS, (size_t)D * sizeof(float), st>>>(
+            pts, D, (D % 4 == 0 && ((uintptr_t)pts & 15) == 0) ? 1 : 0, a);
     count_launches(1);
+}
+
+static double host_now()
+{
+    return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// Waits (bounded) until the scatter kernel of tree depth `depth` has posted the level
+// mailbox.  limit_ms == 0 gives up at once, without looking.
+static bool wait_for_level(Context& ctx, int depth, int limit_ms)
+{
+    cudaStream_t st = ctx.stream;
+    volatile LevelMail* mail = ctx.mail;
+    const auto t_start = std::chrono::steady_clock::now();
+    unsigned spins = 0;
+    bool got = false;
+    if (limit_ms != 0) {
+        while (!(got = (mail->seq == depth))) {
+            if ((++spins & 0x3ff) == 0) {
+                const cudaError_t q = cudaStreamQuery(st);
+                if (q != cudaErrorNotReady) { // finished or failed: the mail is there now or never
+                    got = (mail->seq == depth);
+                    if (!got) ctx.check(q == cudaSuccess ? cudaErrorUnknown : q, "tree level");
+                    break;
+                }
+                if (std::chrono::steady_clock::now() - t_start > std::chrono::milliseconds(limit_ms)) break;
+            }
+        }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    if (!got) {
+        cudaStreamSynchronize(st); // nothing of this tree is left in flight when the call returns
+        return ctx.fail(RSFK_ERR_CUDA, "tree_build: the level mailbox did not arrive within its time limit");
+    }
+    return true;
 }
 
 bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_children,
@@ -843,6 +943,8 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     if (min_children < 0 || max_children < 1)
         return ctx.fail(RSFK_ERR_ARG, "tree_build: invalid min/max_tree_children");
     cudaStream_t st = ctx.stream;
+    const double t_enter = host_now();
+    const double alloc_before = ctx.alloc_seconds;
 
     // capacities: an open node holds more than max_children-2 points, a leaf
     // normally at least min_children
@@ -861,6 +963,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     chunk_node[0] = (int*)ctx.scratch(Context::CHUNK_NODE_A, sizeof(int) * (size_t)chunk_cap);
     chunk_node[1] = (int*)ctx.scratch(Context::CHUNK_NODE_B, sizeof(int) * (size_t)chunk_cap);
     int* chunk_left = (int*)ctx.scratch(Context::CHUNK_LEFT, sizeof(int) * (size_t)chunk_cap);
+    int* node_done = (int*)ctx.scratch(Context::NODE_DONE, sizeof(int) * (size_t)node_cap);
     Node* nodes[2];
     nodes[0] = (Node*)ctx.scratch(Context::NODES_A, sizeof(Node) * (size_t)node_cap);
     nodes[1] = (Node*)ctx.scratch(Context::NODES_B, sizeof(Node) * (size_t)node_cap);
@@ -872,7 +975,6 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     if (small_limit > node_room) small_limit = (int)node_room;
     const size_t sub_smem = sizeof(float) * (size_t)(TREE_THREADS / 32) * D;
     if (small_limit < max_children - 1 || sub_smem > 64 * 1024) small_limit = 0; // nothing would qualify
-    if (const char* e = getenv("RSFK_SUBTREE_LIMIT")) small_limit = atoi(e) < small_limit ? atoi(e) : small_limit;
     const int small_cap = node_cap;
     Node* small_nodes = (Node*)ctx.scratch(Context::SMALL_NODES, sizeof(Node) * (size_t)small_cap);
     int* leaf_start = (int*)ctx.scratch(Context::LEAF_START, sizeof(int) * (size_t)leaf_cap);
@@ -893,91 +995,93 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     }
     memset(ctx.mail, 0, sizeof(LevelMail)); // seq 0 is never a loop depth
     const int4* table = (const int4*)d_table;
+    const int wait_ms = ctx.level_wait_ms >= 0 ? ctx.level_wait_ms : 30000;
 
     const int grid_n = (int)(((long long)N + 255) / 256 < 4096 ? ((long long)N + 255) / 256 : 4096);
     k_iota<<<grid_n, 256, 0, st>>>(perm[0], N);
     count_launches(1);
 
-    int levels = 0;
-    int n_nodes = 1, n_chunks = (N + CHUNK - 1) / CHUNK;
-    int cur = 0;
+    const int n_chunks0 = (N + CHUNK - 1) / CHUNK;
+    bool open = true;
     if (N == 1) {
         k_iota<<<1, 32, 0, st>>>(perm_final, 1);
         k_single_leaf<<<1, 1, 0, st>>>(leaf_start, leaf_count, N, cnt, records);
         count_launches(2);
-        n_nodes = 0;
+        open = false;
     } else {
-        k_tree_init<<<(n_chunks + 255) / 256, 256, 0, st>>>(nodes[0], chunk_node[0], n_chunks, N,
-                                                            table != nullptr, cnt);
+        const int init_items = n_chunks0 > node_cap ? n_chunks0 : node_cap;
+        k_tree_init<<<(init_items + 255) / 256, 256, 0, st>>>(nodes[0], chunk_node[0], node_done, node_cap,
+                                                              n_chunks0, N, table != nullptr, cnt);
         count_launches(1);
     }
 
-    int depth = 1;
+    LevelArgs a;
+    a.side_bits = side_bits;     a.chunk_left = chunk_left;   a.node_done = node_done;
+    a.node_cap = node_cap;       a.chunk_cap = chunk_cap;     a.split = split;
+    a.leaf_start = leaf_start;   a.leaf_count = leaf_count;   a.leaf_cap = leaf_cap;
+    a.small_nodes = small_nodes; a.small_cap = small_cap;     a.small_limit = small_limit;
+    a.cnt = cnt;                 a.table = table;             a.n_table = n_table;
+    a.seed = seed;               a.min_children = min_children; a.max_children = max_children;
+    a.records = records;         a.rec_cap = rec_cap;
+
+    // The level kernels loop over as many chunks as the level turns out to have.
+    int level_grid = chunk_cap < ctx.sm_count * 8 ? chunk_cap : ctx.sm_count * 8;
+    if (level_grid < 1) level_grid = 1;
+
+    const double t_levels = host_now();
+    double wait_s = 0.0;
+    int depth = 1; // depth of the children the next level creates
+    int cur = 0;
     int timed_levels = 0;
     int n_small_seen = 0;
-    long long active = N;
-    for (; depth < max_depth && n_nodes > 0; ++depth) {
-        const int level = depth - 1; // level of the nodes being split
-        ctx.stats.tree_active_points += active;
-        ctx.stats.tree_nodes += n_nodes;
-        while ((int)ctx.level_ev.size() < 2 * (timed_levels + 1)) {
-            cudaEvent_t e;
-            cudaEventCreate(&e);
-            ctx.level_ev.push_back(e);
-        }
-        cudaEventRecord(ctx.level_ev[2 * timed_levels], st);
-        launch_project(ctx, d_points, D, perm[cur], nodes[cur], chunk_node[cur], n_chunks, side_bits,
-                       chunk_left, table, n_table, seed, level, records);
-        cudaEventRecord(ctx.level_ev[2 * timed_levels + 1], st);
-        timed_levels++;
-        k_decide<<<(n_nodes * 32 + TREE_THREADS - 1) / TREE_THREADS, TREE_THREADS, 0, st>>>(
-            nodes[cur], n_nodes, chunk_left, nodes[cur ^ 1], node_cap, chunk_node[cur ^ 1], chunk_cap,
-            split, leaf_start, leaf_count, leaf_cap, small_nodes, small_cap, small_limit, depth, cnt, table,
-            n_table, min_children, max_children, records, rec_cap);
-        k_scatter<<<n_chunks, TREE_THREADS, 0, st>>>(perm[cur], perm[cur ^ 1], perm_final, nodes[cur],
-                                                     chunk_node[cur], side_bits, chunk_left, split, cnt,
-                                                     ctx.mail, depth);
-        count_launches(2);
-        // wait for the mailbox (bounded): the scatter kernel posts it when it starts
-        {
-            volatile LevelMail* mail = ctx.mail;
-            const auto t_start = std::chrono::steady_clock::now();
-            unsigned spins = 0;
-            bool got = false;
-            while (!(got = (mail->seq == depth))) {
-                if ((++spins & 0x3ff) == 0) {
-                    const cudaError_t q = cudaStreamQuery(st);
-                    if (q != cudaErrorNotReady) { // finished or failed: the mail is there now or never
-                        got = (mail->seq == depth);
-                        if (!got) ctx.check(q == cudaSuccess ? cudaErrorUnknown : q, "tree level");
-                        break;
-                    }
-                    if (std::chrono::steady_clock::now() - t_start > std::chrono::seconds(30)) break;
-                }
+    // Levels are enqueued in batches; the host reads the mailbox of a batch's last level
+    // only.  The first batch is as long as the previous tree of this context was deep
+    // (less one), the following ones are short: a level enqueued after the tree has ended
+    // costs two empty launches.
+    int batch = ctx.level_hint > 3 ? ctx.level_hint - 1 : 4;
+    while (open && depth < max_depth) {
+        int enq = 0;
+        for (; enq < batch && depth < max_depth; ++enq, ++depth) {
+            a.level = depth - 1; // level of the nodes being split
+            a.perm = perm[cur];
+            a.nodes = nodes[cur];       a.chunk_node = chunk_node[cur];
+            a.nodes_out = nodes[cur ^ 1]; a.chunk_node_out = chunk_node[cur ^ 1];
+            while ((int)ctx.level_ev.size() < 3 * (timed_levels + 1)) {
+                cudaEvent_t e;
+                cudaEventCreate(&e);
+                ctx.level_ev.push_back(e);
             }
-            std::atomic_thread_fence(std::memory_order_acquire);
-            if (!got) {
-                cudaStreamSynchronize(st);
-                return ctx.fail(RSFK_ERR_CUDA, "tree_build: level mailbox never arrived");
-            }
+            cudaEventRecord(ctx.level_ev[3 * timed_levels], st);
+            launch_project(ctx, d_points, D, level_grid, a);
+            cudaEventRecord(ctx.level_ev[3 * timed_levels + 1], st);
+            k_scatter<<<level_grid, TREE_THREADS, 0, st>>>(perm[cur], perm[cur ^ 1], perm_final, nodes[cur],
+                                                           chunk_node[cur], side_bits, chunk_left, split, cnt,
+                                                           a.level, ctx.mail, depth);
+            cudaEventRecord(ctx.level_ev[3 * timed_levels + 2], st);
+            count_launches(1);
+            timed_levels++;
+            cur ^= 1;
         }
+        const double w0 = host_now();
+        const bool got = wait_for_level(ctx, depth - 1, wait_ms);
+        wait_s += host_now() - w0;
+        if (!got) return false;
         if (ctx.mail->error) {
             cudaStreamSynchronize(st);
             return ctx.fail(ctx.mail->error, "tree_build: internal table overflow");
         }
-        n_nodes = ctx.mail->n_nodes;
-        n_chunks = ctx.mail->n_chunks;
-        active = ctx.mail->active;
+        open = ctx.mail->n_nodes > 0;
         n_small_seen = ctx.mail->n_small;
-        cur ^= 1;
-        levels = depth;
+        batch = 2;
     }
-    if (n_nodes > 0) {
-        k_force_leaves<<<n_nodes, 256, 0, st>>>(nodes[cur], n_nodes, perm[cur], perm_final, leaf_start,
-                                                leaf_count, leaf_cap, cnt, max_children, records);
+    const double t_levels_end = host_now();
+    if (open) { // depth limit: nodes[cur] still holds open nodes (level depth-1)
+        int grid = node_cap < ctx.sm_count * 8 ? node_cap : ctx.sm_count * 8;
+        k_force_leaves<<<grid, 256, 0, st>>>(nodes[cur], cnt, depth - 1, perm[cur], perm_final, leaf_start,
+                                             leaf_count, leaf_cap, cnt, max_children, records);
         count_launches(1);
     }
-    const int n_small = (N > 1 && levels > 0) ? n_small_seen : 0;
+    const int n_small = N > 1 ? n_small_seen : 0;
     if (n_small > 0) {
         if (sub_smem > 16 * 1024 &&
             !ctx.check(cudaFuncSetAttribute(k_subtree, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sub_smem),
@@ -985,12 +1089,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
             return false;
         if (!ctx.sub_ev[0]) { cudaEventCreate(&ctx.sub_ev[0]); cudaEventCreate(&ctx.sub_ev[1]); }
         cudaEventRecord(ctx.sub_ev[0], st);
-        static const int sub_threads = [] {
-            const char* e = getenv("RSFK_SUBTREE_THREADS");
-            int v = e ? atoi(e) : TREE_THREADS;
-            return (v == 64 || v == 128 || v == 256) ? v : TREE_THREADS;
-        }();
-        k_subtree<<<n_small, sub_threads, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
+        k_subtree<<<n_small, TREE_THREADS, sub_smem, st>>>(d_points, D, perm_final, small_nodes, leaf_start,
                                                            leaf_count, leaf_cap, cnt, table, n_table, seed,
                                                            min_children, max_children, max_depth,
                                                            (D % 4 == 0 && ((uintptr_t)d_points & 15) == 0) ? 1 : 0,
@@ -998,38 +1097,52 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
         cudaEventRecord(ctx.sub_ev[1], st);
         count_launches(1);
     }
+    const double t_end0 = host_now();
     if (!ctx.check(cudaMemcpyAsync(ctx.host_counters, cnt, sizeof(LevelCounters),
                                    cudaMemcpyDeviceToHost, st), "counters D2H") ||
         !ctx.check(cudaStreamSynchronize(st), "tree end"))
         return false;
-    if (ctx.host_counters->error)
-        return ctx.fail(ctx.host_counters->error, "tree_build: internal table overflow");
+    const LevelCounters& hc = *ctx.host_counters;
+    if (hc.error) return ctx.fail(hc.error, "tree_build: internal table overflow");
 
+    float project_ms = 0.0f, scatter_ms = 0.0f;
     for (int l = 0; l < timed_levels; ++l) {
         float ms = 0.0f;
-        if (cudaEventElapsedTime(&ms, ctx.level_ev[2 * l], ctx.level_ev[2 * l + 1]) == cudaSuccess)
-            ctx.stats.project_us += ms * 1e3;
+        if (cudaEventElapsedTime(&ms, ctx.level_ev[3 * l], ctx.level_ev[3 * l + 1]) == cudaSuccess) project_ms += ms;
+        if (cudaEventElapsedTime(&ms, ctx.level_ev[3 * l + 1], ctx.level_ev[3 * l + 2]) == cudaSuccess) scatter_ms += ms;
     }
-    ctx.stats.project_launches += timed_levels;
+    int levels = hc.last_depth; // levels the level kernels split
+    ctx.level_hint = levels;
+    ctx.stats.project_us += project_ms * 1e3;
+    ctx.stats.project_launches += levels;
     ctx.stats.trees++;
-    ctx.stats.tree_active_points += (long long)ctx.host_counters->sub_active;
-    ctx.stats.tree_nodes += (long long)ctx.host_counters->sub_nodes;
-    ctx.stats.sub_active_points += (long long)ctx.host_counters->sub_active;
-    ctx.stats.sub_nodes += (long long)ctx.host_counters->sub_nodes;
-    if (n_small > 0) {
-        float ms = 0.0f;
-        if (cudaEventElapsedTime(&ms, ctx.sub_ev[0], ctx.sub_ev[1]) == cudaSuccess) ctx.stats.subtree_us += ms * 1e3;
-    }
-    if (ctx.host_counters->max_level > levels) levels = ctx.host_counters->max_level;
+    ctx.stats.tree_active_points += (long long)(hc.lvl_active + hc.sub_active);
+    ctx.stats.tree_nodes += (long long)(hc.lvl_nodes + hc.sub_nodes);
+    ctx.stats.sub_active_points += (long long)hc.sub_active;
+    ctx.stats.sub_nodes += (long long)hc.sub_nodes;
+    float sub_ms = 0.0f;
+    if (n_small > 0 && cudaEventElapsedTime(&sub_ms, ctx.sub_ev[0], ctx.sub_ev[1]) == cudaSuccess)
+        ctx.stats.subtree_us += sub_ms * 1e3;
+    if (hc.max_level > levels) levels = hc.max_level;
     out.perm = perm_final;
     out.leaf_start = leaf_start;
     out.leaf_count = leaf_count;
-    out.n_leaves = ctx.host_counters->n_leaves;
-    out.max_leaf = ctx.host_counters->max_leaf;
-    out.min_leaf = ctx.host_counters->min_leaf;
+    out.n_leaves = hc.n_leaves;
+    out.max_leaf = hc.max_leaf;
+    out.min_leaf = hc.min_leaf;
     out.levels = N == 1 ? 0 : levels + 1;
     out.records = records;
-    out.n_records = records ? ctx.host_counters->n_recs : 0;
+    out.n_records = records ? hc.n_recs : 0;
+    out.sum_leaf_sq = (double)hc.leaf_sq;
+    const double t_exit = host_now();
+    out.times.init_s = (float)(t_levels - t_enter);
+    out.times.build_s = (float)(t_levels_end - t_levels);
+    out.times.project_s = project_ms * 1e-3f;
+    out.times.scatter_s = scatter_ms * 1e-3f;
+    out.times.wait_s = (float)wait_s;
+    out.times.alloc_s = (float)(ctx.alloc_seconds - alloc_before);
+    out.times.subtree_s = sub_ms * 1e-3f;
+    out.times.end_s = (float)(t_exit - t_end0);
     return true;
 }
 
@@ -1204,8 +1317,10 @@ bool tree_route(Context& ctx, const float* d_points, int D, const TreeResult& tr
         return false;
     long long blocks = ((long long)NQ + ROUTE_WARPS * qpw - 1) / (ROUTE_WARPS * qpw);
     if (blocks > ctx.sm_count * 8) blocks = ctx.sm_count * 8;
+    // a descent takes at most one step per tree level; the limit bounds the kernel's loop
+    const int max_steps = ctx.route_step_limit >= 0 ? ctx.route_step_limit : tree.levels + 8;
     kern<<<(int)blocks, ROUTE_WARPS * 32, smem, st>>>(d_queries, NQ, D, tree.records, n_recs, normals, offsets,
-                                                       tree.levels + 8, tree.n_leaves, d_q_leaf, d_leaf_queries,
+                                                       max_steps, tree.n_leaves, d_q_leaf, d_leaf_queries,
                                                        error_flag);
     count_launches(1);
     return ctx.check(cudaGetLastError(), "route launch");

@@ -93,6 +93,10 @@ def load():
     L.rsfk_dev_merge_lists.argtypes = [vp, ll, i, i, vp, vp, vp, vp]
     L.rsfk_ctx_set_lanes.restype = i
     L.rsfk_ctx_set_lanes.argtypes = [vp, i]
+    L.rsfk_ctx_set_tc.restype = i
+    L.rsfk_ctx_set_tc.argtypes = [vp, i]
+    L.rsfk_ctx_set_wait_limits.restype = i
+    L.rsfk_ctx_set_wait_limits.argtypes = [vp, i, i]
     L.rsfk_ctx_keep_index.restype = i
     L.rsfk_ctx_keep_index.argtypes = [vp, i]
     L.rsfk_dev_route_queries.restype = i

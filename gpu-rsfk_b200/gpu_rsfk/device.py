@@ -112,6 +112,17 @@ class DeviceForest(object):
         The result does not depend on it."""
         _lib.raise_on_status(self._lib.rsfk_ctx_set_lanes(self._ctx, int(lanes)), "set_lanes")
 
+    def set_tc(self, mode):
+        """Bucket KNN on the tensor cores where D >= 64: 1 always, 0 never, -1 the
+        library's choice.  The lists do not depend on it."""
+        _lib.raise_on_status(self._lib.rsfk_ctx_set_tc(self._ctx, int(mode)), "set_tc")
+
+    def set_wait_limits(self, route_max_steps=-1, level_wait_ms=-1):
+        """Limits of the bounded waits (negative: built-in): tree levels a query may
+        descend, milliseconds the host waits for a batch of tree levels."""
+        _lib.raise_on_status(self._lib.rsfk_ctx_set_wait_limits(self._ctx, int(route_max_steps),
+                                                                int(level_wait_ms)), "set_wait_limits")
+
     def forest(self, points, idx, dist, n_trees, min_children, max_children, max_depth=5000, seed=0,
                first_tree=0, tree_stride=1, want_log=False):
         _want(points, torch.float32, "points"); _want(idx, torch.int32, "idx"); _want(dist, torch.float32, "dist")
@@ -216,11 +227,12 @@ class DeviceForest(object):
 
     def stats(self):
         """Work counters of this context (synchronizes the stream)."""
-        out = (ctypes.c_double * 13)()
-        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 13), "stats")
+        out = (ctypes.c_double * 17)()
+        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 17), "stats")
         names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates",
                  "subtree_us", "sub_active_points", "sub_nodes", "tree_build_us",
-                 "project_us", "project_launches", "route_us", "query_update_us")
+                 "project_us", "project_launches", "route_us", "query_update_us",
+                 "tc_launches", "tc_gram_flops", "tc_pairs_passed", "tc_pairs_seen")
         return dict(zip(names, [float(v) for v in out]))
 
     def kernel_launches(self):

@@ -105,8 +105,11 @@ RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
  * the tree builds took as seen from the host, out[9] device microseconds spent in the
  * projection kernels of the tree levels and out[10] their launch count; query path:
  * out[11] device microseconds of hyperplanes + descent + grouping by leaf, out[12] of
- * the query-bucket kernels.  The reference's counterpart is its ForestLog of per-phase
- * wall-clock times (src/include/rsfk.h:274-392). */
+ * the query-bucket kernels; out[13] bucket-KNN launches that ran on the tensor cores and
+ * out[14] the Gram-matrix flops of those launches, 2*D*sum(leaf size^2), out[15] the pairs
+ * the tensor-core filter let through to the exact evaluation and out[16] the pairs it
+ * looked at.  The reference's
+ * counterpart is its ForestLog of per-phase wall-clock times (src/include/rsfk.h:274-392). */
 RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
 /* Orders every row by (distance, index), dropping repeated indices; the other
@@ -145,6 +148,23 @@ RSFK_EXPORT int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, 
  * on it.  No reference counterpart (the
  * reference builds its trees one after another, src/rsfk.cu:2073-2088). */
 RSFK_EXPORT int rsfk_ctx_set_lanes(rsfk_ctx* ctx, int lanes);
+
+/* Which kernel the bucket KNN of this context takes where D >= 64: 1 = the tensor-core
+ * (tcgen05) Gram filter wherever the shape allows it, 0 = never, -1 = the library's choice
+ * (tensor cores where a leaf no longer fits the SIMT kernel's shared-memory block).  Either
+ * way the lists are the same bit for bit.  No reference counterpart (the reference has one
+ * SIMT kernel, src/kernels/compute_knn_from_buckets.cu:998-1378). */
+RSFK_EXPORT int rsfk_ctx_set_tc(rsfk_ctx* ctx, int mode);
+
+/* Limits of the library's bounded waits; a negative value restores the built-in limit.
+ * route_max_steps: tree levels a query may descend (rsfk_dev_route_queries and the query
+ * updates) before the kernel gives up, marks the query as lost and the call returns
+ * RSFK_ERR_CUDA; built-in: the tree's depth + 8.  level_wait_ms: how long the host waits for
+ * the node counts of a batch of tree levels before rsfk_dev_tree_build returns RSFK_ERR_CUDA
+ * (0 = do not wait at all); built-in: 30 s.  After either failure the stream is idle and the
+ * context stays usable.  The reference has no counterpart: it blocks in
+ * cudaDeviceSynchronize and calls exit(1) on errors (src/rsfk.cu:40-50). */
+RSFK_EXPORT int rsfk_ctx_set_wait_limits(rsfk_ctx* ctx, int route_max_steps, int level_wait_ms);
 
 /* Trees first_tree, first_tree+tree_stride, ... (n_trees of them), tree t with
  * seed `seed`+t, each followed by its bucket KNN (reference: the tree loop of

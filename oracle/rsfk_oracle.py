@@ -31,13 +31,35 @@ def build_reference():
     """Compile the reference's own CUDA library into ``oracle/_ref`` when its
     sources are present on this machine; returns the path or None."""
     out = os.path.join(_HERE, "_ref", "librsfk_ref.so")
-    if os.path.exists(out):
+    tiles = os.path.join(_HERE, "_ref", "librsfk_ref_tiles.so")
+    wrapper = os.path.join(_HERE, "_ref", "ref_wrapper", "RSFK.py")
+    if os.path.exists(out) and os.path.exists(tiles) and os.path.exists(wrapper):
         return out
-    ref = os.environ.get("RSFK_REFERENCE_ROOT", "/root/reference")
+    ref = reference_root()
+    if ref is None:
+        return out if os.path.exists(out) else None
+    subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "ref_tiles", "ref_wrapper", "REF=" + ref])
+    return out
+
+
+def reference_wrapper_path():
+    """The reference's own ctypes wrapper (python/gpu_rsfk/RSFK.py of the reference project):
+    from its tree when that is on this machine, else the scratch copy the build left under
+    oracle/_ref; None when there is neither."""
+    ref = reference_root()
+    if ref is not None:
+        return os.path.join(ref, "python", "gpu_rsfk", "RSFK.py")
+    copy = os.path.join(_HERE, "_ref", "ref_wrapper", "RSFK.py")
+    return copy if os.path.exists(copy) else None
+
+
+def reference_root():
+    """Root of the reference project on this machine, or None: the environment variable
+    RSFK_REFERENCE_ROOT, else a directory ``reference`` beside this repository."""
+    ref = os.environ.get("RSFK_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
     if not os.path.exists(os.path.join(ref, "src", "python", "pymodule_ext.cu")):
         return None
-    subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "REF=" + ref])
-    return out
+    return os.path.abspath(ref)
 
 
 def lib():

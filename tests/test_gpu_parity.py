@@ -302,36 +302,6 @@ def test_reference_smoke_suite():
     gpu_rsfk.test()
 
 
-TC_CASES = [
-    # N, D, K, MIN, MAX  -- D >= 64 and leaves of at most 128 points: tensor-core Gram path
-    (6000, 100, 32, 33, 66),
-    (5000, 128, 16, 40, 128),
-    (4000, 64, 8, 9, 18),
-    (3000, 200, 30, 31, 128),
-    (2500, 99, 20, 21, 42),        # D not a multiple of 4: scalar staging
-    (2000, 960, 32, 33, 100),
-    (3000, 72, 64, 60, 128),       # lists longer than some buckets: empty slots survive
-]
-
-
-@pytest.mark.parametrize("N,D,K,MIN,MAX", TC_CASES)
-def test_bucket_knn_tensor_core_shapes_bit_exact(forest, oracle, N, D, K, MIN, MAX):
-    """Shapes that take the tcgen05 Gram path when it is enabled: the selected
-    indices and the stored distances must still be the oracle's, bit for bit."""
-    X = _clustered(N, D, 17, centers=12, sigma=0.4) if D != 100 else _uniform(N, D, 17)
-    idx, dist = oracle.init_lists(N, K)
-    d_idx, d_dist, d_X = _dev(idx), _dev(dist), _dev(X)
-    for t in range(4):
-        tr = oracle.build_tree(X, MIN, MAX, seed=50 + t)
-        assert tr["leaf_count"].max() <= 128
-        idx, dist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
-        forest.bucket_knn_table(d_X, _dev(tr["perm"]), _dev(tr["leaf_start"]), _dev(tr["leaf_count"]),
-                                int(tr["leaf_count"].max()), d_idx, d_dist)
-        forest.synchronize()
-        np.testing.assert_array_equal(d_idx.cpu().numpy(), idx)
-        np.testing.assert_array_equal(d_dist.cpu().numpy(), dist)
-
-
 def test_maximum_list_length_and_refusal_beyond_it(forest, oracle):
     """K = 256 is the largest list the kernels hold; 257 is refused with a status,
     not computed wrongly."""
