@@ -9,8 +9,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "gpu_rsfk", "librsfk.so")
-SOURCES = ["rsfk_api.cu", "rsfk_tree.cu", "rsfk_knn.cu", "rsfk_graph.cu"]
-HEADERS = ["rsfk_common.cuh", "rsfk_context.h", os.path.join("..", "..", "include", "rsfk_b200.h")]
+SOURCES = ["rsfk_api.cu", "rsfk_tree.cu", "rsfk_knn.cu", "rsfk_graph.cu", "rsfk_kmeans.cu"]
+HEADERS = ["rsfk_common.cuh", "rsfk_context.h", "rsfk_bucket_tc.cuh", os.path.join("..", "..", "include", "rsfk_b200.h")]
 FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

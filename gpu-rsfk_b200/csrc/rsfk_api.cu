@@ -743,6 +743,51 @@ void pymodule_rsfk_knn_ann(int n_trees, int num_neighbors, int N, int NQ, int D,
     publish(c);
 }
 
+void rsfk_kmeans(int N, int D, int C, int max_iter, int init_from_labels, float* points, float* centroids,
+                 int* labels, float* sq_dist, int* iterations)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    rsfk_ctx* h = default_ctx();
+    if (!h) {
+        g_last_status = RSFK_ERR_CUDA;
+        g_last_message = "no usable CUDA device";
+        return;
+    }
+    Context& c = h->c;
+    if (N <= 0 || D <= 0 || C <= 0 || C > N || max_iter < 0 || !points || !centroids || !labels || !sq_dist) {
+        c.fail(RSFK_ERR_ARG, "rsfk_kmeans: invalid argument");
+        publish(c);
+        return;
+    }
+    if (init_from_labels)
+        for (int p = 0; p < N; ++p)
+            if (labels[p] < 0 || labels[p] >= C) {
+                c.fail(RSFK_ERR_ARG, "rsfk_kmeans: a label is outside [0, n_clusters)");
+                publish(c);
+                return;
+            }
+    float* d_points = (float*)c.scratch(Context::KM_POINTS, sizeof(float) * (size_t)N * D);
+    float* d_cent = (float*)c.scratch(Context::KM_CENTROIDS, sizeof(float) * (size_t)C * D);
+    int* d_labels = (int*)c.scratch(Context::KM_LABELS, sizeof(int) * (size_t)N);
+    float* d_dist = (float*)c.scratch(Context::KM_DIST, sizeof(float) * (size_t)N);
+    bool ok = d_points && d_cent && d_labels && d_dist;
+    ok = ok && c.check(cudaMemcpyAsync(d_points, points, sizeof(float) * (size_t)N * D, cudaMemcpyHostToDevice, c.stream), "H2D points");
+    ok = ok && c.check(cudaMemcpyAsync(d_cent, centroids, sizeof(float) * (size_t)C * D, cudaMemcpyHostToDevice, c.stream), "H2D centroids");
+    if (init_from_labels)
+        ok = ok && c.check(cudaMemcpyAsync(d_labels, labels, sizeof(int) * (size_t)N, cudaMemcpyHostToDevice, c.stream), "H2D labels");
+    int done = 0;
+    ok = ok && rsfk::kmeans(c, d_points, N, D, C, max_iter, init_from_labels != 0, d_cent, d_labels, d_dist, &done);
+    // outputs are written only when every step succeeded
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "kmeans");
+    ok = ok && c.check(cudaMemcpyAsync(centroids, d_cent, sizeof(float) * (size_t)C * D, cudaMemcpyDeviceToHost, c.stream), "D2H centroids");
+    ok = ok && c.check(cudaMemcpyAsync(labels, d_labels, sizeof(int) * (size_t)N, cudaMemcpyDeviceToHost, c.stream), "D2H labels");
+    ok = ok && c.check(cudaMemcpyAsync(sq_dist, d_dist, sizeof(float) * (size_t)N, cudaMemcpyDeviceToHost, c.stream), "D2H distances");
+    ok = ok && c.check(cudaStreamSynchronize(c.stream), "D2H");
+    if (ok && iterations) *iterations = done;
+    cudaStreamSynchronize(c.stream);
+    publish(c);
+}
+
 // ------------------------------------------------------------------ part 3 --
 
 rsfk_ctx* rsfk_ctx_create(int device, void* stream) { return make_ctx(device, stream, false); }
@@ -787,13 +832,13 @@ int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
         }
     }
     c.resolve_ann_events();
-    const double v[17] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+    const double v[18] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
                          c.stats.bucket_knn_us, (double)evaluated, c.stats.subtree_us,
                          (double)c.stats.sub_active_points, (double)c.stats.sub_nodes, c.stats.tree_build_us,
                          c.stats.project_us, (double)c.stats.project_launches, c.stats.route_us,
                          c.stats.query_update_us, (double)c.stats.tc_launches, c.stats.tc_gram_flops,
-                         (double)tc_pairs[0], (double)tc_pairs[1]};
-    for (int i = 0; i < n && i < 17; ++i) out[i] = v[i];
+                         (double)tc_pairs[0], (double)tc_pairs[1], (double)c.stats.filter_launches};
+    for (int i = 0; i < n && i < 18; ++i) out[i] = v[i];
     return RSFK_OK;
 }
 
@@ -1010,6 +1055,19 @@ int rsfk_dev_symmetrize_fill(rsfk_ctx* ctx, int N, int K, const int* d_idx, cons
 {
     RSFK_ENTER(ctx);
     rsfk::symmetrize_fill(ctx->c, d_idx, d_dist, N, K, d_offsets, d_sym_idx, d_sym_dist);
+    return ctx->c.status;
+}
+
+int rsfk_dev_kmeans(rsfk_ctx* ctx, const float* d_points, int N, int D, int C, int max_iter,
+                    int init_from_labels, float* d_centroids, int* d_labels, float* d_sq_dist, int* iterations)
+{
+    RSFK_ENTER(ctx);
+    if (!d_points || !d_centroids || !d_labels || !d_sq_dist) {
+        ctx->c.fail(RSFK_ERR_ARG, "rsfk_dev_kmeans: invalid argument");
+        return ctx->c.status;
+    }
+    rsfk::kmeans(ctx->c, d_points, N, D, C, max_iter, init_from_labels != 0, d_centroids, d_labels, d_sq_dist,
+                 iterations);
     return ctx->c.status;
 }
 

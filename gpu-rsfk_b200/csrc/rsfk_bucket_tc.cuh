@@ -76,7 +76,7 @@ __host__ __device__ inline float filter_margin(int D)
 
 struct Layout {
     int pass_words;                 // 32-bit words of pass bits per row
-    int off_pass, off_xp, off_queue, off_thr, off_nrm_a, off_nrm_b, off_bar, total;
+    int off_pass, off_xp, off_queue, off_thr, off_nrm_a, off_nrm_b, off_boot, off_bar, total;
     int xp_floats;
 };
 __host__ __device__ inline Layout layout_for(int D, int max_leaf)
@@ -92,6 +92,7 @@ __host__ __device__ inline Layout layout_for(int D, int max_leaf)
     l.off_thr = o;   o += BM * 4;
     l.off_nrm_a = o; o += BM * 4;
     l.off_nrm_b = o; o += 2 * BN * 4;
+    l.off_boot = o;  o += 4 * BM * 4;
     l.off_bar = o;   o += 128;
     l.total = o + 1024; // slack to align the stages to 1024 bytes
     return l;
@@ -262,7 +263,7 @@ k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ 
 // looked at.
 // ---------------------------------------------------------------------------
 template <int KPL, bool VEC4>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __maxnreg__(200)
 k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict__ pts, int D, int Dp, int K,
                 const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
                 const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
@@ -284,6 +285,9 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
     const uint32_t bar_drain = smem_u32(sBar + 2 * STAGES + 4);
     uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 2 * STAGES + 5);
     volatile int* sAbort = reinterpret_cast<volatile int*>(sTmem + 1);
+    volatile int* sOpen = sAbort + 1; // [2]: does the tile (by parity) have a row whose list is not full?
+    float* sBootT = reinterpret_cast<float*>(smem + L0.off_boot); // [2][BM] per column half
+    float* sBootN = sBootT + 2 * BM;                              // [2][BM]
     const int PW = L0.pass_words;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -296,6 +300,8 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
         mbar_init(bar_drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *sAbort = 0;
+        sOpen[0] = 0;
+        sOpen[1] = 0;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sTmem)),
@@ -386,19 +392,22 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
         unsigned gc = 0;
         bool ok = true;
         unsigned long long n_passed = 0, n_pairs = 0;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        int tile_parity = 0;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, tile_parity ^= 1) {
             const Tile tl = tiles[t];
             const int n_groups = (tl.m + BN - 1) / BN;
             const int mI = min(BM, tl.m - tl.i0);
             const int* ids = perm + tl.row0;      // the leaf's members in leaf order
             epi_barrier();                        // the previous tile's rows are done with sPass / sThr
             for (int w = et; w < BM * PW; w += EPI_WARPS * 32) sPass[w] = 0u;
+            if (et == 0) sOpen[tile_parity ^ 1] = 0; // the next tile's flag; nobody looks at it during this tile
             if (et < BM) {
                 float thr = -1.0f, nrm = 0.0f;
                 if (et < mI) {
                     const int id = ids[tl.i0 + et];
                     thr = __ldcg(knn_dist + (size_t)id * K + (K - 1));
                     nrm = norms[tl.row0 + tl.i0 + et];
+                    if (thr == CUDART_INF_F) sOpen[tile_parity] = 1;
                 }
                 sThr[et] = thr;
                 sNrmA[et] = nrm;
@@ -415,9 +424,64 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                 if (*sAbort) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 {
-                    const float thr = sThr[erow];
+                    float thr = sThr[erow];
                     const float n_row = sNrmA[erow];
                     const bool live = erow < mI;
+                    // Rows whose list is not full yet have no threshold, and every pair of the first
+                    // column group would go on to the exact evaluation.  The approximate distances
+                    // themselves give one: with T the larger of the two column halves'
+                    // ceil(K/2)-th smallest approximate distance, at least K candidates lie within
+                    // T + margin, so no pair beyond that (by its lowered distance) can end up among
+                    // the K nearest.  T is found by bisection over the tile row in tensor memory.
+                    if (g == 0 && sOpen[tile_parity]) { // the same decision in every epilogue warp
+                        const uint32_t trow = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(ab * BN + 128 * half);
+                        const int need = (K + 1) >> 1;
+                        int n_valid = 0;
+                        float vmin = CUDART_INF_F, vmax = -CUDART_INF_F, nbmax = 0.0f;
+#pragma unroll 1
+                        for (int sb = 0; sb < 4; ++sb) {
+                            float gv[32];
+                            tmem_ld32(trow + (uint32_t)(32 * sb), gv);
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) {
+                                const int j = j0 + 128 * half + 32 * sb + c;
+                                const float nb = nB[128 * half + 32 * sb + c];
+                                const float v = __fmaf_rn(-2.0f, gv[c], n_row + nb);
+                                if (j < tl.m && j != tl.i0 + erow) {
+                                    n_valid++;
+                                    vmin = fminf(vmin, v);
+                                    vmax = fmaxf(vmax, v);
+                                    nbmax = fmaxf(nbmax, nb);
+                                }
+                            }
+                        }
+                        float lo = vmin, hi = vmax;
+#pragma unroll 1
+                        for (int it = 0; it < 12; ++it) { // every lane takes part in the loads
+                            const float mid = 0.5f * (lo + hi);
+                            int below = 0;
+#pragma unroll 1
+                            for (int sb = 0; sb < 4; ++sb) {
+                                float gv[32];
+                                tmem_ld32(trow + (uint32_t)(32 * sb), gv);
+#pragma unroll
+                                for (int c = 0; c < 32; ++c) {
+                                    const int j = j0 + 128 * half + 32 * sb + c;
+                                    const float v = __fmaf_rn(-2.0f, gv[c], n_row + nB[128 * half + 32 * sb + c]);
+                                    below += (j < tl.m && j != tl.i0 + erow && v <= mid) ? 1 : 0;
+                                }
+                            }
+                            if (below >= need) hi = mid; else lo = mid;
+                        }
+                        // hi always has at least `need` candidates at or below it (it starts at the maximum)
+                        sBootT[half * BM + erow] = n_valid >= need ? hi : CUDART_INF_F;
+                        sBootN[half * BM + erow] = nbmax;
+                        epi_barrier();
+                        const float T = fmaxf(sBootT[erow], sBootT[BM + erow]);
+                        const float nb_most = fmaxf(sBootN[erow], sBootN[BM + erow]);
+                        if (thr == CUDART_INF_F && T < CUDART_INF_F)
+                            thr = (T + margin * (n_row + nb_most)) * 1.000001f + 1e-30f;
+                    }
 #pragma unroll 1
                     for (int sb = 0; sb < 4; ++sb) {
                         const int c0 = 128 * half + 32 * sb;
@@ -469,12 +533,20 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                         if (bits == 0) continue;
                         __syncwarp();
                         if (lane == 0) sPass[r * PW + w] = 0u;
-                        const bool pass = (bits >> lane) & 1u;
-                        if (pass) queue[qn + __popc(bits & ((1u << lane) - 1u))] = ids[32 * w + lane];
-                        qn += __popc(bits);
+                        // a member of the list that sits in this leaf passes the filter by
+                        // construction: it is dropped here, before its row would be fetched
+                        const int cid = ((bits >> lane) & 1u) ? ids[32 * w + lane] : -1;
+                        bool known = false;
+#pragma unroll
+                        for (int q = 0; q < KPL; ++q)
+                            for (int sft = 0; sft < 32; ++sft)
+                                known |= (__shfl_sync(RSFK_FULL, L.i[q], (lane + sft) & 31) == cid);
+                        const unsigned fresh = __ballot_sync(RSFK_FULL, cid >= 0 && !known);
+                        if ((fresh >> lane) & 1u) queue[qn + __popc(fresh & ((1u << lane) - 1u))] = cid;
+                        qn += __popc(fresh);
                         __syncwarp();
                         if (qn >= 32) {
-                            explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
+                            explore_flush<KPL, VEC4, 2>(L, pts, D, xp, queue, 32, K, lane, changed);
                             __syncwarp();
                             const int rest = qn - 32;
                             const int tmp = lane < rest ? queue[32 + lane] : -1;
@@ -484,7 +556,7 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                             __syncwarp();
                         }
                     }
-                    if (qn > 0) explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
+                    if (qn > 0) explore_flush<KPL, VEC4, 2>(L, pts, D, xp, queue, qn, K, lane, changed);
                     if (changed) {
                         L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
                         if (lane == 0) sThr[r] = L.thr_d;

@@ -210,4 +210,70 @@ struct WarpList {
     }
 };
 
+// ---------------------------------------------------------------------------
+// Squared distances from the query (xq, shared memory) to rows row0 .. row0+n-1
+// (n <= 32) of X[.][D] in shared memory, in the summation order of
+// explore_dist32_*; lane l returns the distance of row row0 + item.
+__device__ __forceinline__ float leaf_dist32_scalar(const float* X, int D, const float* xq, int row0, int n,
+                                                    int lane, int& item)
+{
+    float acc[32];
+    const float* row[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+        acc[c] = 0.0f;
+        row[c] = X + (size_t)(row0 + min(c, n - 1)) * D;
+    }
+    for (int k = lane; k < D; k += 32) {
+        const float x = xq[k];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            const float df = __fsub_rn(row[c][k], x);
+            acc[c] = __fmaf_rn(df, df, acc[c]);
+        }
+    }
+    const float dsum = transposed_sum32(acc, lane);
+    item = item32_of_lane(lane);
+    return dsum;
+}
+
+__device__ __forceinline__ float leaf_dist32_vec4(const float* X, int D, const float* xq, int row0, int n,
+                                                  int lane, int& item)
+{
+    const int g = lane >> 3, t = lane & 7;
+    const float4* xq4 = reinterpret_cast<const float4*>(xq);
+    const int D4 = D >> 2;
+    float acc[8][4];
+    const float4* row[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        row[j] = reinterpret_cast<const float4*>(X) + (size_t)(row0 + min(4 * j + g, n - 1)) * D4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[j][q] = 0.0f;
+    }
+    for (int k4 = t; k4 < D4; k4 += 8) {
+        const float4 x = xq4[k4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 v = row[j][k4];
+            float df;
+            df = __fsub_rn(v.x, x.x); acc[j][0] = __fmaf_rn(df, df, acc[j][0]);
+            df = __fsub_rn(v.y, x.y); acc[j][1] = __fmaf_rn(df, df, acc[j][1]);
+            df = __fsub_rn(v.z, x.z); acc[j][2] = __fmaf_rn(df, df, acc[j][2]);
+            df = __fsub_rn(v.w, x.w); acc[j][3] = __fmaf_rn(df, df, acc[j][3]);
+        }
+    }
+    float mine = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float s = __fadd_rn(__fadd_rn(acc[j][0], acc[j][1]), __fadd_rn(acc[j][2], acc[j][3]));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 1));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 2));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 4));
+        if (j == t) mine = s;
+    }
+    item = 4 * t + g;
+    return mine;
+}
+
 } // namespace rsfk

@@ -36,6 +36,8 @@ struct Node {
     int rec;        // row of the node in the tree index (when one is kept)
 };
 
+constexpr int LEVEL_HISTORY = 64;
+
 // Sizes of one tree level: how many open nodes it splits, how many work chunks
 // they make, how many points they hold.
 struct LevelState {
@@ -59,6 +61,7 @@ struct LevelCounters {
     unsigned long long lvl_active; // points projected by the level kernels (all levels)
     unsigned long long lvl_nodes;  // nodes split by the level kernels
     unsigned long long leaf_sq;    // sum over leaves of count^2
+    int level_chunks[LEVEL_HISTORY]; // work chunks of the first levels (sizes the next tree's grids)
 };
 
 // Per-level mailbox in pinned, device-mapped host memory: the scatter kernel of a
@@ -89,10 +92,11 @@ struct Stats {
         project_launches += o.project_launches; tree_build_us += o.tree_build_us;
         sub_active_points += o.sub_active_points; sub_nodes += o.sub_nodes;
         route_us += o.route_us; query_update_us += o.query_update_us;
-        tc_launches += o.tc_launches; tc_gram_flops += o.tc_gram_flops;
+        tc_launches += o.tc_launches; tc_gram_flops += o.tc_gram_flops; filter_launches += o.filter_launches;
     }
     double route_us = 0.0;            // query path: device time of hyperplanes + descent + grouping by leaf
     double query_update_us = 0.0;     // query path: device time of the query-bucket kernels
+    long long filter_launches = 0;    // bucket-KNN launches that took the small-bucket Gram-filter kernel
     long long tc_launches = 0;        // bucket-KNN launches that took the tensor-core kernel
     double tc_gram_flops = 0.0;       // 2*D*sum(m_b^2) over the leaves of those launches
 };
@@ -135,6 +139,7 @@ struct Context {
         SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
         RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
         LANE_IDX, LANE_DIST, SYM_DEGREE, SYM_BLOCKS, TC_ROWS, TC_NORMS, TC_TILES, TC_COUNT, TC_STATS,
+        KM_IOTA, KM_KEYS, KM_ORDER, KM_START, KM_TEMP, KM_CHANGED, KM_POINTS, KM_CENTROIDS, KM_LABELS, KM_DIST,
         N_SLOTS
     };
     // When set, tree_build keeps the tree index (TreeResult::records) that the
@@ -188,6 +193,8 @@ struct Context {
     }
     std::vector<cudaEvent_t> level_ev; // three per tree level, reused by every tree
     int level_hint = 0;                // levels the previous tree of this context needed
+    int level_chunks_hint[LEVEL_HISTORY] = {}; // and the work chunks of its first levels (0: unknown)
+    long long hint_points = 0;         // the N those hints belong to
     bool fail(int code, const std::string& msg)
     {
         if (status == RSFK_OK) { status = code; message = msg; }
@@ -294,6 +301,10 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
 bool symmetrize_count(Context& ctx, const int* d_idx, int N, int K, long long* d_offsets, long long* nnz_host);
 bool symmetrize_fill(Context& ctx, const int* d_idx, const float* d_dist, int N, int K, const long long* d_offsets,
                      int* d_sym_idx, float* d_sym_dist);
+// rsfk_kmeans.cu: Lloyd iterations from d_centroids (or from the means of the groups in
+// d_labels); stops after max_iter iterations or when two assignments in a row agree
+bool kmeans(Context& ctx, const float* d_points, int N, int D, int C, int max_iter, bool init_from_labels,
+            float* d_centroids, int* d_labels, float* d_sq_dist, int* iterations);
 bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,
                  const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist);
 

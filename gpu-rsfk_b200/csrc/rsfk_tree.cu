@@ -399,6 +399,7 @@ __device__ __forceinline__ LevelState level_begin(const LevelArgs& a)
             cnt->lvl_nodes += (unsigned long long)ls.n_nodes;
             cnt->last_depth = a.level + 1;
         }
+        if (a.level < LEVEL_HISTORY) cnt->level_chunks[a.level] = ls.n_chunks;
     }
     return ls;
 }
@@ -855,6 +856,7 @@ __device__ __forceinline__ void clear_counters(LevelCounters* cnt)
     cnt->n_small = 0; cnt->max_level = 0; cnt->n_recs = 1; // row 0 is the root
     cnt->last_depth = 0;
     cnt->sub_active = 0; cnt->sub_nodes = 0; cnt->lvl_active = 0; cnt->lvl_nodes = 0; cnt->leaf_sq = 0;
+    for (int l = 0; l < LEVEL_HISTORY; ++l) cnt->level_chunks[l] = 0;
 }
 
 __global__ void k_tree_init(Node* nodes, int* chunk_node, int* node_done, int node_cap, int n_chunks, int N,
@@ -1024,9 +1026,29 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     a.seed = seed;               a.min_children = min_children; a.max_children = max_children;
     a.records = records;         a.rec_cap = rec_cap;
 
-    // The level kernels loop over as many chunks as the level turns out to have.
-    int level_grid = chunk_cap < ctx.sm_count * 8 ? chunk_cap : ctx.sm_count * 8;
-    if (level_grid < 1) level_grid = 1;
+    // The level kernels loop over as many chunks as the level turns out to have, so any grid is
+    // correct; one CTA per chunk is fastest.  The grid of a level is sized from the chunks the
+    // previous tree of this context had at that level (trees over the same points are alike),
+    // else from what the level can hold at most.
+    if (ctx.hint_points != N) {
+        for (int l = 0; l < LEVEL_HISTORY; ++l) ctx.level_chunks_hint[l] = 0;
+        ctx.level_hint = 0;
+        ctx.hint_points = N;
+    }
+    auto grid_of_level = [&](int level) {
+        long long g;
+        if (level < LEVEL_HISTORY && ctx.level_chunks_hint[level] > 0) {
+            g = ctx.level_chunks_hint[level] + ctx.level_chunks_hint[level] / 4 + 16;
+        } else if (ctx.level_hint > 0 && level >= ctx.level_hint) {
+            g = 64; // deeper than the previous tree went: most likely nothing is left to split
+        } else {
+            const long long nodes_most = level < 30 ? (1LL << level) : (long long)node_cap;
+            g = (long long)n_chunks0 + (nodes_most < node_cap ? nodes_most : node_cap);
+        }
+        if (g > chunk_cap) g = chunk_cap;
+        if (g > ctx.sm_count * 32) g = ctx.sm_count * 32;
+        return (int)(g < 1 ? 1 : g);
+    };
 
     const double t_levels = host_now();
     double wait_s = 0.0;
@@ -1051,6 +1073,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
                 cudaEventCreate(&e);
                 ctx.level_ev.push_back(e);
             }
+            const int level_grid = grid_of_level(a.level);
             cudaEventRecord(ctx.level_ev[3 * timed_levels], st);
             launch_project(ctx, d_points, D, level_grid, a);
             cudaEventRecord(ctx.level_ev[3 * timed_levels + 1], st);
@@ -1113,6 +1136,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
     }
     int levels = hc.last_depth; // levels the level kernels split
     ctx.level_hint = levels;
+    for (int l = 0; l < LEVEL_HISTORY; ++l) ctx.level_chunks_hint[l] = hc.level_chunks[l];
     ctx.stats.project_us += project_ms * 1e3;
     ctx.stats.project_launches += levels;
     ctx.stats.trees++;

@@ -267,6 +267,58 @@ class RSFK(object):
         return n_leaves, width, buckets, sizes
 
 
+    # -------------------------------------------------------------- k-means
+    def cluster_by_kmeans(self, points, n_clusters=None, max_iter=25, init="sample_tree",
+                          min_tree_children=32, max_tree_children=128, max_tree_depth=5000, verbose=0):
+        """k-means clustering on the GPU (Lloyd iterations), by default refining the
+        partition of a random sample tree.
+
+        ``init="sample_tree"``: one sample tree is built (``cluster_by_sample_tree`` with the
+        given ``min/max_tree_children``), its buckets are the starting groups and their
+        number is the number of clusters (``n_clusters`` must be None).
+        ``init="points"``: ``n_clusters`` distinct points drawn with ``random_state`` are the
+        starting centroids.
+
+        Returns ``(centroids float32 [C, D], labels int32 [N], squared_dist float32 [N])``;
+        ``n_iter_`` holds the iterations run.  The reference package has no counterpart
+        (its k-means lives inside nvGRAPH's spectral clustering, which its code no longer
+        calls); ``cluster_by_sample_tree`` itself is unchanged by this method.
+        """
+        points = np.require(points, np.float32, ['CONTIGUOUS', 'ALIGNED'])
+        N, D = points.shape
+        labels = np.zeros(N, np.int32)
+        if init == "sample_tree":
+            if n_clusters is not None:
+                raise Exception('n_clusters is decided by the sample tree when init="sample_tree"')
+            n_leaves, width, buckets, sizes = self.cluster_by_sample_tree(
+                points, max_tree_depth=max_tree_depth, verbose=verbose, min_tree_children=min_tree_children,
+                max_tree_children=max_tree_children)
+            table = buckets.reshape(n_leaves, width)
+            for b in range(n_leaves):
+                labels[table[b, :sizes[b]]] = b
+            C = int(n_leaves)
+            centroids = np.zeros((C, D), np.float32)
+            from_labels = 1
+        elif init == "points":
+            C = int(n_clusters)
+            if C < 1 or C > N:
+                raise Exception('n_clusters = {} \t => must be between 1 and the number of points'.format(C))
+            pick = np.sort(np.random.RandomState(self.random_state).choice(N, C, replace=False))
+            centroids = points[pick].copy()
+            from_labels = 0
+        else:
+            raise Exception('init must be "sample_tree" or "points"')
+        sq_dist = np.empty(N, np.float32)
+        done = ctypes.c_int(0)
+        t_init = time.time()
+        self._lib.rsfk_kmeans(N, D, C, int(max_iter), from_labels, points, centroids, labels, sq_dist,
+                              ctypes.byref(done))
+        _lib.check_last("rsfk_kmeans")
+        self._last_cluster_time = time.time() - t_init
+        self.n_iter_ = int(done.value)
+        return centroids, labels, sq_dist
+
+
 def test():
     """Smoke checks in the spirit of the reference's ``test1``/``test2``
     (python/gpu_rsfk/RSFK.py:841-903): no slot may keep index -1, and a

@@ -52,6 +52,14 @@ def load():
         np.ctypeslib.ndpointer(np.float32, ndim=2, flags="ALIGNED, CONTIGUOUS, WRITEABLE"),
         np.ctypeslib.ndpointer(np.float32, ndim=1, flags="ALIGNED, CONTIGUOUS, WRITEABLE")]
 
+    L.rsfk_kmeans.restype = None
+    L.rsfk_kmeans.argtypes = [i] * 5 + [
+        np.ctypeslib.ndpointer(np.float32, ndim=2, flags="ALIGNED, CONTIGUOUS"),
+        np.ctypeslib.ndpointer(np.float32, ndim=2, flags="ALIGNED, CONTIGUOUS, WRITEABLE"),
+        np.ctypeslib.ndpointer(np.int32, ndim=1, flags="ALIGNED, CONTIGUOUS, WRITEABLE"),
+        np.ctypeslib.ndpointer(np.float32, ndim=1, flags="ALIGNED, CONTIGUOUS, WRITEABLE"),
+        _c_int_p]
+
     L.rsfk_last_status.restype = i
     L.rsfk_last_status.argtypes = []
     L.rsfk_last_message.restype = ctypes.c_char_p
@@ -109,6 +117,8 @@ def load():
     L.rsfk_dev_symmetrize_count.argtypes = [vp, i, i, vp, vp, ctypes.POINTER(ll)]
     L.rsfk_dev_symmetrize_fill.restype = i
     L.rsfk_dev_symmetrize_fill.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
+    L.rsfk_dev_kmeans.restype = i
+    L.rsfk_dev_kmeans.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, _c_int_p]
     L.rsfk_explore_sweep_static.restype = i
     L.rsfk_explore_sweep_static.argtypes = [vp, i, i, i, vp, vp, vp]
     _lib = L

@@ -205,6 +205,25 @@ class DeviceForest(object):
                                               ctypes.cast(dp, ctypes.c_void_p), _ptr(out_idx), _ptr(out_dist))
         _lib.raise_on_status(code, "merge_lists")
 
+    def kmeans(self, points, centroids, max_iter=25, labels=None):
+        """Lloyd iterations on the GPU from ``centroids`` ([C, D], updated in place) or, when
+        ``labels`` (int32 [N], values in [0, C)) is given, from the means of those groups.
+        Returns ``(labels int32 [N], squared distances float32 [N], iterations run)``."""
+        _want(points, torch.float32, "points"); _want(centroids, torch.float32, "centroids")
+        N, D = points.shape
+        C = centroids.shape[0]
+        from_labels = labels is not None
+        if from_labels:
+            _want(labels, torch.int32, "labels")
+        else:
+            labels = torch.empty(N, dtype=torch.int32, device=points.device)
+        dist = torch.empty(N, dtype=torch.float32, device=points.device)
+        done = ctypes.c_int(0)
+        code = self._lib.rsfk_dev_kmeans(self._ctx, _ptr(points), N, D, C, int(max_iter), 1 if from_labels else 0,
+                                         _ptr(centroids), _ptr(labels), _ptr(dist), ctypes.byref(done))
+        _lib.raise_on_status(code, "kmeans")
+        return labels, dist, done.value
+
     def symmetrize(self, idx, dist=None):
         """Symmetric closure of the K-NN graph ``idx`` ([N, K], -1 = empty) as CSR:
         ``(offsets int64 [N+1], indices int32 [nnz], values float32 [nnz] or None)``;
@@ -227,12 +246,12 @@ class DeviceForest(object):
 
     def stats(self):
         """Work counters of this context (synchronizes the stream)."""
-        out = (ctypes.c_double * 17)()
-        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 17), "stats")
+        out = (ctypes.c_double * 18)()
+        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 18), "stats")
         names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates",
                  "subtree_us", "sub_active_points", "sub_nodes", "tree_build_us",
                  "project_us", "project_launches", "route_us", "query_update_us",
-                 "tc_launches", "tc_gram_flops", "tc_pairs_passed", "tc_pairs_seen")
+                 "tc_launches", "tc_gram_flops", "tc_pairs_passed", "tc_pairs_seen", "filter_launches")
         return dict(zip(names, [float(v) for v in out]))
 
     def kernel_launches(self):

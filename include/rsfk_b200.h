@@ -63,6 +63,21 @@ RSFK_EXPORT void pymodule_rsfk_knn_ann(int n_trees, int num_neighbors, int N, in
                            float* points, float* query_points, int* knn_indices,
                            float* knn_sqr_distances, float* log_forest);
 
+/* k-means (Lloyd iterations) on host buffers, for clustering on top of a sample tree:
+ * the groups of pymodule_cluster_by_sample_tree as starting labels (init_from_labels = 1:
+ * centroids start as the means of the groups given in labels[N], values in [0, C)) or
+ * caller-chosen starting centroids (init_from_labels = 0: centroids[C*D] is read).
+ * Runs until two assignments in a row agree or max_iter iterations; writes the final
+ * centroids[C*D], labels[N], squared distance of every point to its centroid sq_dist[N]
+ * and the iterations run.  Nearest centroid by squared distance in the library's usual
+ * summation order, ties to the lower cluster index; a cluster that loses all its points
+ * keeps its centroid; the result is a pure function of the input.
+ * The reference has no such function: the k-means of its sample-tree clustering sits
+ * inside nvGRAPH's spectral clustering and is reached from commented-out code only
+ * (src/rsfk.cu:1521-1567, parameters at :1536-1539,1863-1868). */
+RSFK_EXPORT void rsfk_kmeans(int N, int D, int C, int max_iter, int init_from_labels,
+                 float* points, float* centroids, int* labels, float* sq_dist, int* iterations);
+
 /* ---------------------------------------------------------------- part 2 -- */
 
 /* Status of the most recent part-1 call on this thread's process (0 = ok).
@@ -107,8 +122,9 @@ RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
  * out[11] device microseconds of hyperplanes + descent + grouping by leaf, out[12] of
  * the query-bucket kernels; out[13] bucket-KNN launches that ran on the tensor cores and
  * out[14] the Gram-matrix flops of those launches, 2*D*sum(leaf size^2), out[15] the pairs
- * the tensor-core filter let through to the exact evaluation and out[16] the pairs it
- * looked at.  The reference's
+ * the Gram filters (tensor-core kernel and small-bucket kernel) let through to the exact
+ * evaluation and out[16] the pairs they looked at, out[17] bucket-KNN launches that took the
+ * small-bucket Gram-filter kernel.  The reference's
  * counterpart is its ForestLog of per-phase wall-clock times (src/include/rsfk.h:274-392). */
 RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
@@ -149,10 +165,11 @@ RSFK_EXPORT int rsfk_dev_bucket_knn_table(rsfk_ctx* ctx, const float* d_points, 
  * reference builds its trees one after another, src/rsfk.cu:2073-2088). */
 RSFK_EXPORT int rsfk_ctx_set_lanes(rsfk_ctx* ctx, int lanes);
 
-/* Which kernel the bucket KNN of this context takes where D >= 64: 1 = the tensor-core
- * (tcgen05) Gram filter wherever the shape allows it, 0 = never, -1 = the library's choice
- * (tensor cores where a leaf no longer fits the SIMT kernel's shared-memory block).  Either
- * way the lists are the same bit for bit.  No reference counterpart (the reference has one
+/* Which kernel the bucket KNN of this context takes where D >= 64: 1 = the tcgen05 Gram
+ * filter (128-row tiles, TMA-fed) wherever the shape allows it, 0 = the exact SIMT kernel
+ * only, -1 = the library's choice: the tcgen05 kernel where a leaf no longer fits one CTA's
+ * shared memory, else the small-bucket Gram filter (warp-level TF32 MMA tiles over the
+ * staged rows).  Either way the lists are the same bit for bit.  No reference counterpart (the reference has one
  * SIMT kernel, src/kernels/compute_knn_from_buckets.cu:998-1378). */
 RSFK_EXPORT int rsfk_ctx_set_tc(rsfk_ctx* ctx, int mode);
 
@@ -227,6 +244,12 @@ RSFK_EXPORT int rsfk_dev_symmetrize_count(rsfk_ctx* ctx, int N, int K, const int
                               long long* d_offsets, long long* nnz);
 RSFK_EXPORT int rsfk_dev_symmetrize_fill(rsfk_ctx* ctx, int N, int K, const int* d_idx, const float* d_dist,
                              const long long* d_offsets, int* d_sym_idx, float* d_sym_dist);
+
+/* rsfk_kmeans on device memory (same rules; d_labels is read only when
+ * init_from_labels is set; iterations is a host pointer and may be NULL). */
+RSFK_EXPORT int rsfk_dev_kmeans(rsfk_ctx* ctx, const float* d_points, int N, int D, int C, int max_iter,
+                    int init_from_labels, float* d_centroids, int* d_labels, float* d_sq_dist,
+                    int* iterations);
 
 /* out = the K smallest distinct entries of G canonical lists per row.
  * d_idx_lists/d_dist_lists are HOST arrays of G device pointers (G <= 16).

@@ -972,3 +972,59 @@ ORC_API int orc_find_leaf_separations(const float* points, int D, const int* ids
     (void)n_leaves;
     return found;
 }
+
+/* ------------------------------------------------------------------------- */
+/* k-means (Lloyd) for sample-tree clustering                                 */
+/* ------------------------------------------------------------------------- */
+/* PARITY UNPINNED: the reference has no k-means function.  The only k-means near its
+ * path is the one inside nvGRAPH's spectral clustering, which it calls from
+ * commented-out code (src/rsfk.cu:1521-1567, parameters at :1536-1539 and :1863-1868);
+ * nvGRAPH is neither part of the reference tree nor of current toolkits.  What follows
+ * states the rules the sm_100a kernels of this repository implement, so that they can
+ * be checked against something; it is not a restatement of reference code.
+ *
+ * Assignment: the nearest centroid by squared distance in the reference's summation
+ * order (orc_dist_sqr), ties to the lower centroid index.
+ * Update: centroid c = mean of its members; the sum runs in double precision over the
+ * members in ascending point index, member number j going to partial sum j mod 8, the
+ * eight partial sums added in order 0..7; a cluster without members keeps its centroid. */
+ORC_API void orc_kmeans_assign(const float* points, int N, int D, const float* centroids, int C,
+                               int* assign, float* dist)
+{
+#pragma omp parallel for schedule(static)
+    for (int p = 0; p < N; ++p) {
+        int best = -1;
+        float bd = INFINITY;
+        for (int c = 0; c < C; ++c) {
+            const float d = orc_dist_sqr(points + (size_t)p * D, centroids + (size_t)c * D, D);
+            if (best < 0 || d < bd) { bd = d; best = c; }
+        }
+        assign[p] = best;
+        dist[p] = bd;
+    }
+}
+
+ORC_API void orc_kmeans_update(const float* points, int N, int D, const int* assign, int C,
+                               float* centroids, int* counts)
+{
+    double* part = (double*)calloc((size_t)C * D * 8, sizeof(double));
+    int* seen = (int*)calloc((size_t)C, sizeof(int));
+    for (int p = 0; p < N; ++p) {
+        const int c = assign[p];
+        if (c < 0 || c >= C) continue;
+        double* dst = part + ((size_t)c * 8 + (size_t)(seen[c] & 7)) * D;
+        for (int k = 0; k < D; ++k) dst[k] += (double)points[(size_t)p * D + k];
+        seen[c]++;
+    }
+    for (int c = 0; c < C; ++c) {
+        if (counts) counts[c] = seen[c];
+        if (seen[c] == 0) continue;
+        for (int k = 0; k < D; ++k) {
+            double s = 0.0;
+            for (int w = 0; w < 8; ++w) s += part[((size_t)c * 8 + w) * D + k];
+            centroids[(size_t)c * D + k] = (float)(s / (double)seen[c]);
+        }
+    }
+    free(part);
+    free(seen);
+}

@@ -119,6 +119,10 @@ def lib():
         L.orc_bruteforce_ann.restype = None
         L.orc_bruteforce_ann.argtypes = [_f32, ctypes.c_int, _f32, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_int, _i32, _f32]
+        L.orc_kmeans_assign.restype = None
+        L.orc_kmeans_assign.argtypes = [_f32, ctypes.c_int, ctypes.c_int, _f32, ctypes.c_int, _i32, _f32]
+        L.orc_kmeans_update.restype = None
+        L.orc_kmeans_update.argtypes = [_f32, ctypes.c_int, ctypes.c_int, _i32, ctypes.c_int, _f32, _i32]
         _lib = L
     return _lib
 
@@ -240,6 +244,48 @@ def ann_forest(points, queries, K, n_trees, min_children, max_children, max_dept
         idx, dist = ann_bucket_knn(points, queries, K, tr["perm"], tr["q_start"], tr["q_count"],
                                    idx, dist)
     return idx, dist
+
+
+def kmeans_assign(points, centroids):
+    """(labels int32 [N], squared distance float32 [N]) of the nearest centroid, ties to
+    the lower centroid index (no reference counterpart: see the C source)."""
+    points, centroids = _pts(points), _pts(centroids)
+    N, D = points.shape
+    labels = np.empty(N, np.int32)
+    dist = np.empty(N, np.float32)
+    lib().orc_kmeans_assign(points, N, D, centroids, centroids.shape[0], labels, dist)
+    return labels, dist
+
+
+def kmeans_update(points, labels, centroids):
+    """(centroids float32 [C, D], counts int32 [C]): means of the members, empty clusters
+    keep their centroid."""
+    points = _pts(points)
+    N, D = points.shape
+    out = _pts(centroids).copy()
+    counts = np.zeros(out.shape[0], np.int32)
+    lib().orc_kmeans_update(points, N, D, np.ascontiguousarray(labels, np.int32), out.shape[0], out, counts)
+    return out, counts
+
+
+def kmeans(points, centroids, max_iter, labels=None):
+    """Lloyd iterations from the given centroids (or, with ``labels``, from the means of
+    those groups): stops after ``max_iter`` iterations or when no label changes.
+    Returns (centroids, labels, squared distances, iterations run)."""
+    cent = _pts(centroids).copy()
+    if labels is not None:
+        cent, _ = kmeans_update(points, labels, cent)
+    prev = None
+    done = 0
+    lab, dist = kmeans_assign(points, cent)
+    for it in range(max_iter):
+        done = it + 1
+        if prev is not None and np.array_equal(prev, lab):
+            break
+        prev = lab
+        cent, _ = kmeans_update(points, lab, cent)
+        lab, dist = kmeans_assign(points, cent)
+    return cent, lab, dist, done
 
 
 def symmetrize(idx, dist=None):

@@ -132,9 +132,24 @@ def test_filter_passes_a_small_share_once_lists_are_full(tc_forest, oracle):
     right lists, as a slow SIMT kernel)."""
     N, D, K = 8000, 128, 16
     X = _clustered(N, D, 41, centers=6, sigma=0.5)
-    _run_trees(tc_forest, oracle, X, K, 300, 900, trees=3, seed0=21)
-    passed, seen = _run_trees(tc_forest, oracle, X, K, 300, 900, trees=1, seed0=21)   # the same leaves again
-    assert seen > 0 and passed <= 0.10 * seen
+    idx, dist = oracle.init_lists(N, K)
+    d_idx, d_dist, d_X = _dev(idx), _dev(dist), _dev(X)
+    shares = []
+    for t in range(6):
+        tr = oracle.build_tree(X, 300, 900, seed=21 + t)
+        idx, dist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+        before = tc_forest.stats()
+        tc_forest.bucket_knn_table(d_X, _dev(tr["perm"]), _dev(tr["leaf_start"]), _dev(tr["leaf_count"]),
+                                   int(tr["leaf_count"].max()), d_idx, d_dist)
+        tc_forest.synchronize()
+        after = tc_forest.stats()
+        shares.append((after["tc_pairs_passed"] - before["tc_pairs_passed"]) /
+                      max(1.0, after["tc_pairs_seen"] - before["tc_pairs_seen"]))
+    np.testing.assert_array_equal(d_idx.cpu().numpy(), idx)
+    np.testing.assert_array_equal(d_dist.cpu().numpy().view(np.int32), dist.view(np.int32))
+    print("share of pairs passed, tree by tree:", ["%.4f" % v for v in shares])
+    # empty lists let every pair of the first column group through; full lists let few through
+    assert shares[0] > 0.2 and shares[-1] < 0.1 and shares[-1] < 0.25 * shares[0]
 
 
 def test_sampled_leaves_of_a_large_high_dimensional_tree(tc_forest, oracle):
@@ -187,3 +202,65 @@ def test_understated_max_leaf_is_clamped(tc_forest, oracle):
                                int(tr["leaf_count"].max()), d_idx, d_dist)
     tc_forest.synchronize()
     np.testing.assert_array_equal(d_idx.cpu().numpy(), ridx)
+
+
+FILTER_CASES = [
+    # N, D, K, MIN, MAX -- D >= 64, leaves that fit one CTA: the small-bucket Gram filter
+    (6000, 100, 32, 33, 66),
+    (4000, 128, 64, 65, 130),
+    (3000, 200, 30, 31, 128),
+    (2500, 99, 20, 21, 42),        # D not a multiple of 4 nor of 8
+    (1500, 960, 32, 33, 48),
+    (3000, 64, 100, 101, 202),     # K = 100: four registers per lane
+    (3000, 72, 64, 60, 128),
+]
+
+
+@pytest.mark.parametrize("mode", [-1, 0])
+@pytest.mark.parametrize("N,D,K,MIN,MAX", FILTER_CASES)
+def test_small_bucket_filter_and_exact_kernel_give_the_same_lists(forest, oracle, N, D, K, MIN, MAX, mode):
+    """Default choice for small buckets at D >= 64 (Gram filter on warp-level TF32 tiles, exact
+    re-evaluation of what passes) and the exact SIMT kernel (set_tc(0)): both must give the
+    oracle's lists bit for bit, over several trees so that full lists are filtered too."""
+    X = _clustered(N, D, 19) if D != 100 else _uniform(N, D, 19)
+    forest.set_tc(mode)
+    try:
+        idx, dist = oracle.init_lists(N, K)
+        d_idx, d_dist, d_X = _dev(idx), _dev(dist), _dev(X)
+        before = forest.stats()
+        for t in range(5):
+            tr = oracle.build_tree(X, MIN, MAX, seed=70 + t)
+            idx, dist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+            forest.bucket_knn_table(d_X, _dev(tr["perm"]), _dev(tr["leaf_start"]), _dev(tr["leaf_count"]),
+                                    int(tr["leaf_count"].max()), d_idx, d_dist)
+            forest.synchronize()
+            np.testing.assert_array_equal(d_idx.cpu().numpy(), idx)
+            np.testing.assert_array_equal(d_dist.cpu().numpy().view(np.int32), dist.view(np.int32))
+        after = forest.stats()
+        assert after["filter_launches"] - before["filter_launches"] == (5 if mode == -1 else 0)
+        assert after["tc_launches"] == before["tc_launches"]        # buckets of this size never go to tcgen05 by default
+    finally:
+        forest.set_tc(-1)
+
+
+def test_small_bucket_filter_on_integer_points_and_offsets(forest, oracle):
+    """Ties (integer coordinates, coincident points) and a large common offset on the
+    small-bucket filter."""
+    rng = np.random.default_rng(8)
+    N, D, K = 5000, 128, 64
+    c = rng.integers(0, 256, (20, D)).astype(np.float32)
+    X = np.clip(np.rint(c[rng.integers(0, 20, N)] + rng.normal(0, 12, (N, D))), 0, 255).astype(np.float32)
+    X[1::2] = X[::2]
+    for data in (X, (X + np.float32(4096.0)).astype(np.float32)):
+        idx, dist = oracle.init_lists(N, K)
+        d_idx, d_dist, d_X = _dev(idx), _dev(dist), _dev(data)
+        before = forest.stats()
+        for t in range(3):
+            tr = oracle.build_tree(data, 65, 130, seed=5 + t)
+            idx, dist = oracle.bucket_knn(data, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+            forest.bucket_knn_table(d_X, _dev(tr["perm"]), _dev(tr["leaf_start"]), _dev(tr["leaf_count"]),
+                                    int(tr["leaf_count"].max()), d_idx, d_dist)
+            forest.synchronize()
+            np.testing.assert_array_equal(d_idx.cpu().numpy(), idx)
+            np.testing.assert_array_equal(d_dist.cpu().numpy().view(np.int32), dist.view(np.int32))
+        assert forest.stats()["filter_launches"] - before["filter_launches"] == 3
