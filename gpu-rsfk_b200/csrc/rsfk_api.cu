@@ -832,13 +832,13 @@ int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n)
         }
     }
     c.resolve_ann_events();
-    const double v[18] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
+    const double v[17] = {(double)c.stats.trees, (double)c.stats.tree_active_points, (double)c.stats.tree_nodes,
                          c.stats.bucket_knn_us, (double)evaluated, c.stats.subtree_us,
                          (double)c.stats.sub_active_points, (double)c.stats.sub_nodes, c.stats.tree_build_us,
                          c.stats.project_us, (double)c.stats.project_launches, c.stats.route_us,
                          c.stats.query_update_us, (double)c.stats.tc_launches, c.stats.tc_gram_flops,
-                         (double)tc_pairs[0], (double)tc_pairs[1], (double)c.stats.filter_launches};
-    for (int i = 0; i < n && i < 18; ++i) out[i] = v[i];
+                         (double)tc_pairs[0], (double)tc_pairs[1]};
+    for (int i = 0; i < n && i < 17; ++i) out[i] = v[i];
     return RSFK_OK;
 }
 

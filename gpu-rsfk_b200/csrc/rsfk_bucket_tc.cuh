@@ -14,8 +14,9 @@
 //
 // Data path.  Once per tree k_tc_rows writes the points in leaf order, centred on
 // the first point of their leaf (y = x - x_first: distances are unchanged, norms
-// and with them the error margin shrink from |x|^2 to the leaf's spread), rows
-// padded to a multiple of 32 floats, plus |y|^2 per row.  A work item ("tile") is a
+// and with them the error margin shrink from |x| to the leaf's spread) and rounded
+// to the nearest TF32 value, rows padded to a multiple of 32 floats, plus the squared
+// norm of every (rounded) row.  A work item ("tile") is a
 // block of 128 consecutive rows of one leaf against all the rows of that leaf, taken
 // in column groups of 256.  The kernel is persistent, one CTA per SM, and
 // warp-specialised:
@@ -61,22 +62,26 @@ struct Tile {
     int pad;
 };
 
-// Relative error bound of the TF32 Gram distance, as a fraction of |yi|^2+|yj|^2.
-// Each operand carries 10 explicit mantissa bits (relative error below 2^-10
-// whether the unit truncates or rounds), so a product is off by less than 2^-9 of
-// |a||b| and the dot product by less than 2^-9 |yi||yj| <= 2^-10 (|yi|^2+|yj|^2);
-// d2 = nn - 2g doubles that: 2^-9 = 1.95e-3.  fp32 accumulation of D products,
-// allowing two units in the last place per addition, adds 2 * D * 2^-23 on the same
-// scale.  Centring itself costs 2^-22 (y = fl(x - c) is exact to 2^-24 relative per
-// coordinate).  The margin used is 1.25 times the sum.
-__host__ __device__ inline float filter_margin(int D)
+// How far the Gram distance can be from the true squared distance.  The rows the tensor
+// cores see are y~ = rn_tf32(fl(x - c)), off from the exact centred row by at most
+// 2^-11 (1 + 2^-12) of each coordinate, so |y~i - y~j| differs from the true distance d by
+// at most delta = DELTA_REL (|y~i| + |y~j|).  What the kernel forms is
+// t2 = |y~i|^2 + |y~j|^2 - 2 y~i.y~j = |y~i - y~j|^2 up to the fp32 accumulation of D
+// products in the tensor core and of the norms (two units in the last place per addition
+// allowed): e1 = acc_margin(D) (|y~i|^2 + |y~j|^2).  Hence
+//     d^2 >= (sqrt(t2 + e1) - delta)^2 >= t2 - e1 - 2 sqrt(t2 + e1) delta =: lowered(t2)
+//     d^2 <= (sqrt(t2 + e1) + delta)^2  =  t2 + e1 + 2 sqrt(t2 + e1) delta + delta^2
+// The first is what a pair is filtered by, the second bounds the true distance of pairs used
+// to derive a threshold for rows whose list is not full.
+constexpr float DELTA_REL = 4.8828125e-4f * 1.002f; // 2^-11 and the centring's own rounding
+__host__ __device__ inline float acc_margin(int D)
 {
-    return 1.25f * (1.953125e-3f + 2.4e-7f * (float)D + 2.4e-7f);
+    return 1.25f * (2.5e-7f * (float)D + 1e-6f);
 }
 
 struct Layout {
     int pass_words;                 // 32-bit words of pass bits per row
-    int off_pass, off_xp, off_queue, off_thr, off_nrm_a, off_nrm_b, off_boot, off_bar, total;
+    int off_pass, off_xp, off_queue, off_thr, off_nrm_a, off_nrm_b, off_sq_a, off_sq_b, off_boot, off_bar, total;
     int xp_floats;
 };
 __host__ __device__ inline Layout layout_for(int D, int max_leaf)
@@ -92,6 +97,8 @@ __host__ __device__ inline Layout layout_for(int D, int max_leaf)
     l.off_thr = o;   o += BM * 4;
     l.off_nrm_a = o; o += BM * 4;
     l.off_nrm_b = o; o += 2 * BN * 4;
+    l.off_sq_a = o;  o += BM * 4;
+    l.off_sq_b = o;  o += 2 * BN * 4;
     l.off_boot = o;  o += 4 * BM * 4;
     l.off_bar = o;   o += 128;
     l.total = o + 1024; // slack to align the stages to 1024 bytes
@@ -223,7 +230,7 @@ __global__ void k_tc_tiles(const int* __restrict__ leaf_start, const int* __rest
 
 // ---------------------------------------------------------------------------
 // Leaf-ordered, centred copy of the points: rows[r][0..Dp) = x[perm[r]] - x[perm[row0]]
-// (zeros beyond D), norms[r] = |row|^2.  One CTA per tile, one warp per row.
+// rounded to TF32 (zeros beyond D), norms[r] = |row|^2.  One CTA per tile, one warp per row.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ perm,
@@ -247,7 +254,9 @@ k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ 
             float* y = rows + row * Dp;
             float nrm = 0.0f;
             for (int k = lane; k < Dp; k += 32) {
-                const float v = k < D ? __fsub_rn(__ldg(x + k), centre[k]) : 0.0f;
+                float v = k < D ? __fsub_rn(__ldg(x + k), centre[k]) : 0.0f;
+                // nearest value with 10 explicit mantissa bits: what kind::tf32 reads anyway
+                v = __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
                 y[k] = v;
                 nrm = __fmaf_rn(v, v, nrm);
             }
@@ -263,11 +272,11 @@ k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ 
 // looked at.
 // ---------------------------------------------------------------------------
 template <int KPL, bool VEC4>
-__global__ void __maxnreg__(200)
+__global__ void __launch_bounds__(THREADS, 1)
 k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict__ pts, int D, int Dp, int K,
                 const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
                 const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
-                float* __restrict__ knn_dist, int max_leaf, float margin, unsigned long long* __restrict__ stats,
+                float* __restrict__ knn_dist, int max_leaf, float c_acc, unsigned long long* __restrict__ stats,
                 int* __restrict__ error_flag)
 {
     extern __shared__ unsigned char smem_raw[];
@@ -278,6 +287,8 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
     float* sThr = reinterpret_cast<float*>(smem + L0.off_thr);
     float* sNrmA = reinterpret_cast<float*>(smem + L0.off_nrm_a);
     float* sNrmB = reinterpret_cast<float*>(smem + L0.off_nrm_b);
+    float* sSqA = reinterpret_cast<float*>(smem + L0.off_sq_a);   // |y~| of the tile's rows
+    float* sSqB = reinterpret_cast<float*>(smem + L0.off_sq_b);   // and of the group's columns
     uint64_t* sBar = reinterpret_cast<uint64_t*>(smem + L0.off_bar);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain
     const uint32_t bar_full = smem_u32(sBar), bar_empty = smem_u32(sBar + STAGES);
@@ -411,12 +422,15 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                 }
                 sThr[et] = thr;
                 sNrmA[et] = nrm;
+                sSqA[et] = sqrtf(nrm);
             }
             for (int g = 0; g < n_groups && ok; ++g, ++gc) {
                 const int ab = gc & 1;
                 const int j0 = g * BN;
                 float* nB = sNrmB + ab * BN;
+                float* qB = sSqB + ab * BN;
                 nB[et] = (j0 + et < tl.m) ? norms[tl.row0 + j0 + et] : 0.0f;
+                qB[et] = sqrtf(nB[et]);
                 // the wait of every thread is bounded; whether to go on is decided together
                 // after the barrier, so that no warp leaves the others at a barrier
                 mbar_wait(bar_acc_full + 8 * ab, (gc >> 1) & 1u, sAbort);
@@ -426,13 +440,15 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                 {
                     float thr = sThr[erow];
                     const float n_row = sNrmA[erow];
+                    const float q_row = sSqA[erow];
                     const bool live = erow < mI;
                     // Rows whose list is not full yet have no threshold, and every pair of the first
                     // column group would go on to the exact evaluation.  The approximate distances
                     // themselves give one: with T the larger of the two column halves'
-                    // ceil(K/2)-th smallest approximate distance, at least K candidates lie within
-                    // T + margin, so no pair beyond that (by its lowered distance) can end up among
-                    // the K nearest.  T is found by bisection over the tile row in tensor memory.
+                    // ceil(K/2)-th smallest Gram distance, at least K candidates have a true distance
+                    // of at most upper(T), so no pair beyond that (by its lowered distance) can end
+                    // up among the K nearest.  T is found by bisection over the tile row in tensor
+                    // memory.
                     if (g == 0 && sOpen[tile_parity]) { // the same decision in every epilogue warp
                         const uint32_t trow = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(ab * BN + 128 * half);
                         const int need = (K + 1) >> 1;
@@ -479,8 +495,12 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                         epi_barrier();
                         const float T = fmaxf(sBootT[erow], sBootT[BM + erow]);
                         const float nb_most = fmaxf(sBootN[erow], sBootN[BM + erow]);
-                        if (thr == CUDART_INF_F && T < CUDART_INF_F)
-                            thr = (T + margin * (n_row + nb_most)) * 1.000001f + 1e-30f;
+                        if (thr == CUDART_INF_F && T < CUDART_INF_F) {
+                            const float e1 = c_acc * (n_row + nb_most);
+                            const float delta = DELTA_REL * (q_row + sqrtf(nb_most));
+                            const float root = sqrtf(fmaxf(T + e1, 0.0f)) + delta;
+                            thr = root * root * 1.000001f + 1e-30f;
+                        }
                     }
 #pragma unroll 1
                     for (int sb = 0; sb < 4; ++sb) {
@@ -492,9 +512,14 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                         for (int c = 0; c < 32; ++c) {
                             const int j = j0 + c0 + c;
                             const float nn = n_row + nB[c0 + c];
-                            const float d2 = __fmaf_rn(-2.0f, gv[c], nn) - margin * nn;
-                            // !(d2 >= thr) keeps the candidate when anything is not a number
-                            if (j < tl.m && j != tl.i0 + erow && !(d2 >= thr)) word |= 1u << c;
+                            const float t2 = __fmaf_rn(-2.0f, gv[c], nn);
+                            const float e1 = c_acc * nn;
+                            const float two_delta = (2.0f * DELTA_REL) * (q_row + qB[c0 + c]);
+                            const float d2 = t2 - e1 - sqrtf(fmaxf(t2 + e1, 0.0f)) * two_delta;
+                            // a pair whose lowered distance EQUALS the K-th distance passes too (the margin is zero
+                            // for coincident points, and a tie with a lower index enters the list);
+                            // !(d2 > thr) also keeps the candidate when anything is not a number
+                            if (j < tl.m && j != tl.i0 + erow && !(d2 > thr)) word |= 1u << c;
                         }
                         if (live) {
                             sPass[erow * PW + (j0 >> 5) + (c0 >> 5)] = word;
@@ -533,20 +558,12 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                         if (bits == 0) continue;
                         __syncwarp();
                         if (lane == 0) sPass[r * PW + w] = 0u;
-                        // a member of the list that sits in this leaf passes the filter by
-                        // construction: it is dropped here, before its row would be fetched
-                        const int cid = ((bits >> lane) & 1u) ? ids[32 * w + lane] : -1;
-                        bool known = false;
-#pragma unroll
-                        for (int q = 0; q < KPL; ++q)
-                            for (int sft = 0; sft < 32; ++sft)
-                                known |= (__shfl_sync(RSFK_FULL, L.i[q], (lane + sft) & 31) == cid);
-                        const unsigned fresh = __ballot_sync(RSFK_FULL, cid >= 0 && !known);
-                        if ((fresh >> lane) & 1u) queue[qn + __popc(fresh & ((1u << lane) - 1u))] = cid;
-                        qn += __popc(fresh);
+                        const bool pass = (bits >> lane) & 1u;
+                        if (pass) queue[qn + __popc(bits & ((1u << lane) - 1u))] = ids[32 * w + lane];
+                        qn += __popc(bits);
                         __syncwarp();
                         if (qn >= 32) {
-                            explore_flush<KPL, VEC4, 2>(L, pts, D, xp, queue, 32, K, lane, changed);
+                            explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
                             __syncwarp();
                             const int rest = qn - 32;
                             const int tmp = lane < rest ? queue[32 + lane] : -1;
@@ -556,7 +573,7 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                             __syncwarp();
                         }
                     }
-                    if (qn > 0) explore_flush<KPL, VEC4, 2>(L, pts, D, xp, queue, qn, K, lane, changed);
+                    if (qn > 0) explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
                     if (changed) {
                         L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
                         if (lane == 0) sThr[r] = L.thr_d;

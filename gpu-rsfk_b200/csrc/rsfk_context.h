@@ -92,11 +92,10 @@ struct Stats {
         project_launches += o.project_launches; tree_build_us += o.tree_build_us;
         sub_active_points += o.sub_active_points; sub_nodes += o.sub_nodes;
         route_us += o.route_us; query_update_us += o.query_update_us;
-        tc_launches += o.tc_launches; tc_gram_flops += o.tc_gram_flops; filter_launches += o.filter_launches;
+        tc_launches += o.tc_launches; tc_gram_flops += o.tc_gram_flops;
     }
     double route_us = 0.0;            // query path: device time of hyperplanes + descent + grouping by leaf
     double query_update_us = 0.0;     // query path: device time of the query-bucket kernels
-    long long filter_launches = 0;    // bucket-KNN launches that took the small-bucket Gram-filter kernel
     long long tc_launches = 0;        // bucket-KNN launches that took the tensor-core kernel
     double tc_gram_flops = 0.0;       // 2*D*sum(m_b^2) over the leaves of those launches
 };

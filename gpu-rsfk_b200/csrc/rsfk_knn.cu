@@ -456,9 +456,6 @@ __device__ __forceinline__ float explore_dist32_scalar(const float* __restrict__
 // (g = lane/8, t = lane%8) owns terms 4t..4t+3 (+32, ...) of rows 4j+g, j=0..7,
 // i.e. virtual lanes 4t..4t+3 of the reference's sum, and ends up with the
 // distance of candidate 4t+g.
-// DEPTH k-steps are loaded together (8 * DEPTH 16-byte loads in flight per lane) before they are
-// used; the sums are formed in the same order whatever DEPTH is.
-template <int DEPTH = 1>
 __device__ __forceinline__ float explore_dist32_vec4(const float* __restrict__ pts, int D, const float* xp,
                                                      const int* queue, int n, int lane, int& cand)
 {
@@ -473,25 +470,18 @@ __device__ __forceinline__ float explore_dist32_vec4(const float* __restrict__ p
 #pragma unroll
         for (int q = 0; q < 4; ++q) acc[j][q] = 0.0f;
     }
-    for (int k4 = t; k4 < D4; k4 += 8 * DEPTH) {
-        float4 v[DEPTH][8];
+    for (int k4 = t; k4 < D4; k4 += 8) {
+        const float4 x = xp4[k4];
+        float4 v[8];
 #pragma unroll
-        for (int u = 0; u < DEPTH; ++u)
+        for (int j = 0; j < 8; ++j) v[j] = __ldg(row[j] + k4);
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (DEPTH == 1 || k4 + 8 * u < D4) v[u][j] = __ldg(row[j] + k4 + 8 * u);
-#pragma unroll
-        for (int u = 0; u < DEPTH; ++u) {
-            if (DEPTH > 1 && k4 + 8 * u >= D4) break;
-            const float4 x = xp4[k4 + 8 * u];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float df;
-                df = __fsub_rn(v[u][j].x, x.x); acc[j][0] = __fmaf_rn(df, df, acc[j][0]);
-                df = __fsub_rn(v[u][j].y, x.y); acc[j][1] = __fmaf_rn(df, df, acc[j][1]);
-                df = __fsub_rn(v[u][j].z, x.z); acc[j][2] = __fmaf_rn(df, df, acc[j][2]);
-                df = __fsub_rn(v[u][j].w, x.w); acc[j][3] = __fmaf_rn(df, df, acc[j][3]);
-            }
+        for (int j = 0; j < 8; ++j) {
+            float df;
+            df = __fsub_rn(v[j].x, x.x); acc[j][0] = __fmaf_rn(df, df, acc[j][0]);
+            df = __fsub_rn(v[j].y, x.y); acc[j][1] = __fmaf_rn(df, df, acc[j][1]);
+            df = __fsub_rn(v[j].z, x.z); acc[j][2] = __fmaf_rn(df, df, acc[j][2]);
+            df = __fsub_rn(v[j].w, x.w); acc[j][3] = __fmaf_rn(df, df, acc[j][3]);
         }
     }
     float mine = 0.0f;
@@ -507,14 +497,14 @@ __device__ __forceinline__ float explore_dist32_vec4(const float* __restrict__ p
     return mine;
 }
 
-template <int KPL, bool VEC4, int DEPTH = 1>
+template <int KPL, bool VEC4>
 __device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __restrict__ pts, int D,
                                               const float* xp, const int* queue, int n, int K,
                                               int lane, bool& changed)
 {
     // n in [1,32] candidates at queue[0..n)
     int item;
-    const float dsum = VEC4 ? explore_dist32_vec4<DEPTH>(pts, D, xp, queue, n, lane, item)
+    const float dsum = VEC4 ? explore_dist32_vec4(pts, D, xp, queue, n, lane, item)
                             : explore_dist32_scalar(pts, D, xp, queue, n, lane, item);
     const int ci = item < n ? queue[item] : -1;
     unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(dsum, ci));
@@ -838,299 +828,6 @@ k_merge_lists(MergeArgs args, int G, long long rows, int K, int* __restrict__ ou
 #include "rsfk_bucket_tc.cuh"
 
 // ---------------------------------------------------------------------------
-// Leaf-bucket KNN for D >= 64 and leaves that fit one CTA's shared memory
-// (the 33..130-point buckets of the default parameters).
-//
-// Same idea as the tcgen05 kernel, sized for small buckets: the bucket's Gram
-// matrix only FILTERS.  The rows are staged once; Y Y^T (Y = rows centred on the
-// bucket's first row) is formed on the tensor cores in TF32 with warp-level
-// mma.sync tiles of 16 x 8 x 8 straight from the staged rows -- a 50-point
-// bucket is a handful of tiles, far below what a 128-row tcgen05 tile wants --
-// and a pair passes when its approximate squared distance, lowered by the TF32
-// error margin, is below the row's current K-th distance.  Only rows with a
-// passing pair load their list at all; their passing pairs are evaluated again
-// in the reference's exact summation order from the staged rows and merged with
-// the usual rule, so lists are identical to the exact kernel's.
-// ---------------------------------------------------------------------------
-constexpr int FILTER_HASH_LOG2 = 9;
-constexpr int FILTER_HASH = 1 << FILTER_HASH_LOG2; // id -> row table of a bucket of at most 256 points
-
-__device__ __forceinline__ void mma_tf32_16x8x8(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-        "{%0, %1, %2, %3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-
-// Squared distances from xq to the rows rows[0..n) (n <= 32, indices into X[.][D]) in the
-// summation order of leaf_dist32_*; lane l returns the distance of rows[item].
-template <bool VEC4>
-__device__ __forceinline__ float picked_dist32(const float* X, int D, const float* xq, const int* rows, int n,
-                                               int lane, int& item)
-{
-    if (VEC4) {
-        const int g = lane >> 3, t = lane & 7;
-        const float4* xq4 = reinterpret_cast<const float4*>(xq);
-        const int D4 = D >> 2;
-        float acc[8][4];
-        const float4* row[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            row[j] = reinterpret_cast<const float4*>(X) + (size_t)rows[min(4 * j + g, n - 1)] * D4;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) acc[j][q] = 0.0f;
-        }
-        for (int k4 = t; k4 < D4; k4 += 8) {
-            const float4 x = xq4[k4];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 v = row[j][k4];
-                float df;
-                df = __fsub_rn(v.x, x.x); acc[j][0] = __fmaf_rn(df, df, acc[j][0]);
-                df = __fsub_rn(v.y, x.y); acc[j][1] = __fmaf_rn(df, df, acc[j][1]);
-                df = __fsub_rn(v.z, x.z); acc[j][2] = __fmaf_rn(df, df, acc[j][2]);
-                df = __fsub_rn(v.w, x.w); acc[j][3] = __fmaf_rn(df, df, acc[j][3]);
-            }
-        }
-        float mine = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float s = __fadd_rn(__fadd_rn(acc[j][0], acc[j][1]), __fadd_rn(acc[j][2], acc[j][3]));
-            s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 1));
-            s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 2));
-            s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 4));
-            if (j == t) mine = s;
-        }
-        item = 4 * t + g;
-        return mine;
-    } else {
-        float acc[32];
-        const float* row[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            acc[c] = 0.0f;
-            row[c] = X + (size_t)rows[min(c, n - 1)] * D;
-        }
-        for (int k = lane; k < D; k += 32) {
-            const float x = xq[k];
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const float df = __fsub_rn(row[c][k], x);
-                acc[c] = __fmaf_rn(df, df, acc[c]);
-            }
-        }
-        const float dsum = transposed_sum32(acc, lane);
-        item = item32_of_lane(lane);
-        return dsum;
-    }
-}
-
-template <int KPL, bool VEC4>
-__global__ void __launch_bounds__(KNN_THREADS, 3)
-k_bucket_knn_filter(const float* __restrict__ pts, int D, int K, const int* __restrict__ perm,
-                    const int* __restrict__ leaf_start, const int* __restrict__ leaf_count,
-                    int* __restrict__ knn_idx, float* __restrict__ knn_dist, int max_leaf, float margin,
-                    unsigned long long* __restrict__ stats)
-{
-    extern __shared__ float4 smem4[];
-    const int B = (max_leaf + 3) & ~3;
-    const int PW = (B + 31) >> 5;
-    float* X = reinterpret_cast<float*>(smem4);               // [B][D]
-    float* sThr = X + (size_t)B * D;                           // [B]
-    float* sNrm = sThr + B;                                    // [B]
-    int* sIds = reinterpret_cast<int*>(sNrm + B);              // [B]
-    unsigned* sPass = reinterpret_cast<unsigned*>(sIds + B);   // [B][PW]
-    int* sQueue = reinterpret_cast<int*>(sPass + (size_t)B * PW); // [KNN_WARPS][32]
-    int* sHashId = sQueue + KNN_WARPS * 32;                        // [FILTER_HASH] point id, -1 = free
-    int* sHashPos = sHashId + FILTER_HASH;                         // [FILTER_HASH] its row in the bucket
-
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int leaf = blockIdx.x;
-    const int m = min(leaf_count[leaf], max_leaf);
-    const int* ids_g = perm + leaf_start[leaf];
-    for (int h = threadIdx.x; h < FILTER_HASH; h += blockDim.x) sHashId[h] = -1;
-    for (int w = threadIdx.x; w < B * PW; w += blockDim.x) sPass[w] = 0u;
-    __syncthreads();
-    for (int r = threadIdx.x; r < m; r += blockDim.x) {
-        const int id = ids_g[r];
-        sIds[r] = id;
-        sThr[r] = __ldcg(knn_dist + (size_t)id * K + (K - 1));
-        // id -> row, open addressing; the table is at most half full, so a free slot exists
-        unsigned h = ((unsigned)id * 2654435761u) >> (32 - FILTER_HASH_LOG2);
-        for (int probe = 0; probe < FILTER_HASH; ++probe) {
-            if (atomicCAS(&sHashId[h], -1, id) == -1) { sHashPos[h] = r; break; }
-            h = (h + 1) & (FILTER_HASH - 1);
-        }
-    }
-    __syncthreads();
-    stage_rows<VEC4>(pts, D, sIds, m, X, warp, lane);
-    __syncthreads();
-    // |y|^2 of the rows centred on the bucket's first row
-    for (int r = warp; r < m; r += KNN_WARPS) {
-        float nrm = 0.0f;
-        for (int k = lane; k < D; k += 32) {
-            const float v = X[(size_t)r * D + k] - X[k];
-            nrm = __fmaf_rn(v, v, nrm);
-        }
-#pragma unroll
-        for (int s = 16; s >= 1; s >>= 1) nrm += __shfl_xor_sync(RSFK_FULL, nrm, s);
-        if (lane == 0) sNrm[r] = nrm;
-    }
-    __syncthreads();
-    // ---- Gram tiles: a warp takes 16 rows x 32 columns at a time ----------------
-    {
-        const int gid = lane >> 2, tig = lane & 3;
-        const int row_tiles = (m + 15) >> 4, col_tiles = (m + 31) >> 5;
-        unsigned long long n_pass = 0;
-        for (int wt = warp; wt < row_tiles * col_tiles; wt += KNN_WARPS) {
-            const int rt = wt / col_tiles, ct = wt - rt * col_tiles;
-            const int ra = min(16 * rt + gid, m - 1), rb = min(16 * rt + gid + 8, m - 1);
-            const float* xa = X + (size_t)ra * D;
-            const float* xb = X + (size_t)rb * D;
-            const float* xc[4];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) xc[nt] = X + (size_t)min(32 * ct + 8 * nt + gid, m - 1) * D;
-            float acc[4][4];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
-            for (int k0 = 0; k0 < D; k0 += 8) {
-                const int ka = k0 + tig, kb = k0 + tig + 4;
-                const bool va = ka < D, vb = kb < D;
-                const float ca = va ? X[ka] : 0.0f, cb = vb ? X[kb] : 0.0f; // the centre: row 0
-                uint32_t a[4];
-                a[0] = __float_as_uint(va ? xa[ka] - ca : 0.0f);
-                a[1] = __float_as_uint(va ? xb[ka] - ca : 0.0f);
-                a[2] = __float_as_uint(vb ? xa[kb] - cb : 0.0f);
-                a[3] = __float_as_uint(vb ? xb[kb] - cb : 0.0f);
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    uint32_t b[2];
-                    b[0] = __float_as_uint(va ? xc[nt][ka] - ca : 0.0f);
-                    b[1] = __float_as_uint(vb ? xc[nt][kb] - cb : 0.0f);
-                    mma_tf32_16x8x8(acc[nt], a, b);
-                }
-            }
-            // acc[nt][0..1]: row 16rt+gid, columns 32ct+8nt+2tig, +1; acc[nt][2..3]: row +8
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int i = 16 * rt + gid + 8 * h;
-                if (i >= m) continue;
-                const float thr = sThr[i], ni = sNrm[i];
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int j = 32 * ct + 8 * nt + 2 * tig + e;
-                        if (j >= m || j == i) continue;
-                        const float nn = ni + sNrm[j];
-                        const float d2 = __fmaf_rn(-2.0f, acc[nt][2 * h + e], nn) - margin * nn;
-                        // !(d2 >= thr) keeps the candidate when anything is not a number
-                        if (!(d2 >= thr)) {
-                            atomicOr(&sPass[i * PW + (j >> 5)], 1u << (j & 31));
-                            n_pass++;
-                        }
-                    }
-            }
-        }
-        if (stats != nullptr) {
-#pragma unroll
-            for (int s = 16; s >= 1; s >>= 1) n_pass += __shfl_xor_sync(RSFK_FULL, n_pass, s);
-            if (lane == 0 && n_pass) atomicAdd(&stats[0], n_pass);
-            if (threadIdx.x == 0) atomicAdd(&stats[1], (unsigned long long)m * (unsigned long long)(m - 1));
-        }
-    }
-    __syncthreads();
-    // ---- rows with passing pairs: exact distances from the staged rows -------------
-    // A warp takes its rows RB at a time: the lists of those that have a passing pair are
-    // requested together, so that their latencies overlap.
-    constexpr int RB = KPL <= 1 ? 4 : (KPL == 2 ? 2 : 1);
-    int* queue = sQueue + warp * 32;
-    for (int base = warp; base < m; base += KNN_WARPS * RB) {
-        WarpList<KPL> Ls[RB];
-        bool need[RB];
-#pragma unroll
-        for (int u = 0; u < RB; ++u) {
-            const int r = base + u * KNN_WARPS;
-            unsigned any = 0;
-            if (r < m)
-                for (int w = lane; w < PW; w += 32) any |= sPass[r * PW + w];
-            need[u] = __any_sync(RSFK_FULL, any != 0); // without one the row's list is not even read
-            if (need[u]) {
-                const int self = sIds[r];
-                Ls[u].load_raw(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < RB; ++u) {
-            if (!need[u]) continue;
-            const int r = base + u * KNN_WARPS;
-            const int self = sIds[r];
-            WarpList<KPL>& L = Ls[u];
-            L.refresh_threshold(K);
-            // members of the list that sit in this bucket pass the filter by construction: drop them
-#pragma unroll
-            for (int q = 0; q < KPL; ++q) {
-                const int v = L.i[q];
-                if (v < 0) continue;
-                unsigned h = ((unsigned)v * 2654435761u) >> (32 - FILTER_HASH_LOG2);
-                for (int probe = 0; probe < FILTER_HASH; ++probe) {
-                    const int at = sHashId[h];
-                    if (at == -1) break;
-                    if (at == v) {
-                        const int j = sHashPos[h];
-                        atomicAnd(&sPass[r * PW + (j >> 5)], ~(1u << (j & 31)));
-                        break;
-                    }
-                    h = (h + 1) & (FILTER_HASH - 1);
-                }
-            }
-            __syncwarp();
-            const float* xq = X + (size_t)r * D;
-            bool changed = false;
-            for (int w = 0; w < PW; ++w) {
-                const unsigned bits = sPass[r * PW + w];
-                if (bits == 0) continue;
-                const int n = __popc(bits);
-                if (n <= 4) {
-                    // few candidates: the whole warp on one pair at a time (term k on lane k % 32,
-                    // xor butterfly: the same sum as the 32-wide routine)
-                    unsigned rest = bits;
-                    while (rest) {
-                        const int j = 32 * w + __ffs(rest) - 1;
-                        rest &= rest - 1;
-                        const float* xj = X + (size_t)j * D;
-                        float acc = 0.0f;
-                        for (int k = lane; k < D; k += 32) {
-                            const float df = __fsub_rn(xj[k], xq[k]);
-                            acc = __fmaf_rn(df, df, acc);
-                        }
-                        changed |= L.try_insert(butterfly_sum(acc), sIds[j], K, lane);
-                    }
-                    continue;
-                }
-                __syncwarp();
-                if ((bits >> lane) & 1u) queue[__popc(bits & ((1u << lane) - 1u))] = 32 * w + lane;
-                __syncwarp();
-                int item;
-                const float dsum = picked_dist32<VEC4>(X, D, xq, queue, n, lane, item);
-                const int ci = item < n ? sIds[queue[item]] : -1;
-                unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(dsum, ci));
-                while (mask) {
-                    const int b = __ffs(mask) - 1;
-                    mask &= mask - 1;
-                    changed |= L.try_insert(__shfl_sync(RSFK_FULL, dsum, b), __shfl_sync(RSFK_FULL, ci, b), K, lane);
-                }
-            }
-            if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------
 // host launchers
 // ---------------------------------------------------------------------------
 static int kpl_for(int K)
@@ -1238,7 +935,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
                                                                    tile_cap, rows, norms);
     const tc::Layout lay = tc::layout_for(D, tree.max_leaf);
     const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
-    const float margin = tc::filter_margin(D);
+    const float c_acc = tc::acc_margin(D);
     const int grid = tile_cap < ctx.sm_count ? tile_cap : ctx.sm_count;
     RSFK_DISPATCH_KPL(K, {
         auto kern = vec4 ? tc::k_bucket_knn_tc<KPL, true> : tc::k_bucket_knn_tc<KPL, false>;
@@ -1246,7 +943,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
                        "bucket_knn_tc smem attribute"))
             return false;
         kern<<<grid, tc::THREADS, lay.total, st>>>(map, d_points, D, Dp, K, tree.perm, norms, tiles, n_tiles,
-                                                   tile_cap, d_idx, d_dist, tree.max_leaf, margin, counters, flag);
+                                                   tile_cap, d_idx, d_dist, tree.max_leaf, c_acc, counters, flag);
     });
     count_launches(3);
     ctx.stats.tc_launches++;
@@ -1288,29 +985,6 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     if (want_tc && D >= 64 && N >= tc::BM && tree.max_leaf <= tc::MAX_LEAF &&
         tc::layout_for(D, tree.max_leaf).total <= 227 * 1024)
         return bucket_knn_tc(ctx, d_points, N, D, K, tree, d_idx, d_dist);
-    // D >= 64 and small leaves: the TF32 Gram filter on warp-level MMA tiles, rows staged once
-    const int Bf = (tree.max_leaf + 3) & ~3, PWf = (Bf + 31) >> 5;
-    const size_t filter_smem = sizeof(float) * ((size_t)Bf * D + 2 * (size_t)Bf) +
-                               sizeof(int) * ((size_t)Bf + (size_t)Bf * PWf + KNN_WARPS * 32 + 2 * FILTER_HASH);
-    if (ctx.tc_mode == -1 && D >= 64 && tree.max_leaf <= 256 && filter_smem <= 110 * 1024) {
-        const size_t smem = filter_smem;
-        unsigned long long* counters = ctx.tc_counters();
-        if (!counters) return false;
-        const bool v4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
-        const float margin = tc::filter_margin(D);
-        RSFK_DISPATCH_KPL(K, {
-            auto kern = v4 ? k_bucket_knn_filter<KPL, true> : k_bucket_knn_filter<KPL, false>;
-            if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                           "bucket_knn filter smem attribute"))
-                return false;
-            kern<<<tree.n_leaves, KNN_THREADS, smem, launch_stream>>>(d_points, D, K, tree.perm, tree.leaf_start,
-                                                                      tree.leaf_count, d_idx, d_dist, tree.max_leaf,
-                                                                      margin, counters);
-        });
-        count_launches(1);
-        ctx.stats.filter_launches++;
-        return ctx.check(cudaGetLastError(), "bucket_knn filter launch");
-    }
     // block size: the whole leaf when it fits, else the largest that fits twice
     int B = (tree.max_leaf + 3) & ~3;
     if (B < 4) B = 4;

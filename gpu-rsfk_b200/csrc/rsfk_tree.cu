@@ -310,19 +310,30 @@ __device__ __forceinline__ void decide_node(const LevelArgs& a, int node, const 
     LevelCounters* cnt = a.cnt;
     LevelState* next = &cnt->lvl[(a.level + 1) % 3];
     const int n_chunks = (nd.count + CHUNK - 1) / CHUNK;
-    // left total; chunk_left becomes the exclusive prefix inside the node
+    // left total; chunk_left becomes the exclusive prefix inside the node.  Eight rounds of
+    // loads are requested together: a node of the first levels has thousands of chunks and
+    // one warp walks them, so the loads must not wait for one another.
     int carry = 0;
-    for (int c0 = 0; c0 < n_chunks; c0 += 32) {
-        const int c = c0 + lane;
-        int v = c < n_chunks ? __ldcg(a.chunk_left + nd.chunk_base + c) : 0;
-        int incl = v;
+    for (int c0 = 0; c0 < n_chunks; c0 += 32 * 8) {
+        int v[8];
 #pragma unroll
-        for (int s = 1; s < 32; s <<= 1) {
-            int t = __shfl_up_sync(RSFK_FULL, incl, s);
-            if (lane >= s) incl += t;
+        for (int u = 0; u < 8; ++u) {
+            const int c = c0 + 32 * u + lane;
+            v[u] = c < n_chunks ? __ldcg(a.chunk_left + nd.chunk_base + c) : 0;
         }
-        if (c < n_chunks) a.chunk_left[nd.chunk_base + c] = carry + incl - v;
-        carry += __shfl_sync(RSFK_FULL, incl, 31);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int c = c0 + 32 * u + lane;
+            if (c0 + 32 * u >= n_chunks) break; // warp-uniform
+            int incl = v[u];
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) {
+                int t = __shfl_up_sync(RSFK_FULL, incl, s);
+                if (lane >= s) incl += t;
+            }
+            if (c < n_chunks) a.chunk_left[nd.chunk_base + c] = carry + incl - v[u];
+            carry += __shfl_sync(RSFK_FULL, incl, 31);
+        }
     }
     const int nL = carry;
     const Children ch = decide_children(nd.start, nd.count, nL, a.min_children, a.max_children);

@@ -246,12 +246,12 @@ class DeviceForest(object):
 
     def stats(self):
         """Work counters of this context (synchronizes the stream)."""
-        out = (ctypes.c_double * 18)()
-        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 18), "stats")
+        out = (ctypes.c_double * 17)()
+        _lib.raise_on_status(self._lib.rsfk_ctx_stats(self._ctx, out, 17), "stats")
         names = ("trees", "tree_active_points", "tree_nodes", "bucket_knn_us", "explore_candidates",
                  "subtree_us", "sub_active_points", "sub_nodes", "tree_build_us",
                  "project_us", "project_launches", "route_us", "query_update_us",
-                 "tc_launches", "tc_gram_flops", "tc_pairs_passed", "tc_pairs_seen", "filter_launches")
+                 "tc_launches", "tc_gram_flops", "tc_pairs_passed", "tc_pairs_seen")
         return dict(zip(names, [float(v) for v in out]))
 
     def kernel_launches(self):

@@ -122,9 +122,8 @@ RSFK_EXPORT int rsfk_ctx_synchronize(rsfk_ctx* ctx);
  * out[11] device microseconds of hyperplanes + descent + grouping by leaf, out[12] of
  * the query-bucket kernels; out[13] bucket-KNN launches that ran on the tensor cores and
  * out[14] the Gram-matrix flops of those launches, 2*D*sum(leaf size^2), out[15] the pairs
- * the Gram filters (tensor-core kernel and small-bucket kernel) let through to the exact
- * evaluation and out[16] the pairs they looked at, out[17] bucket-KNN launches that took the
- * small-bucket Gram-filter kernel.  The reference's
+ * the tensor-core filter let through to the exact evaluation and out[16] the pairs it
+ * looked at.  The reference's
  * counterpart is its ForestLog of per-phase wall-clock times (src/include/rsfk.h:274-392). */
 RSFK_EXPORT int rsfk_ctx_stats(rsfk_ctx* ctx, double* out, int n);
 
@@ -168,8 +167,7 @@ RSFK_EXPORT int rsfk_ctx_set_lanes(rsfk_ctx* ctx, int lanes);
 /* Which kernel the bucket KNN of this context takes where D >= 64: 1 = the tcgen05 Gram
  * filter (128-row tiles, TMA-fed) wherever the shape allows it, 0 = the exact SIMT kernel
  * only, -1 = the library's choice: the tcgen05 kernel where a leaf no longer fits one CTA's
- * shared memory, else the small-bucket Gram filter (warp-level TF32 MMA tiles over the
- * staged rows).  Either way the lists are the same bit for bit.  No reference counterpart (the reference has one
+ * shared memory, else the exact kernel.  Either way the lists are the same bit for bit.  No reference counterpart (the reference has one
  * SIMT kernel, src/kernels/compute_knn_from_buckets.cu:998-1378). */
 RSFK_EXPORT int rsfk_ctx_set_tc(rsfk_ctx* ctx, int mode);
 
