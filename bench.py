@@ -768,7 +768,16 @@ def reference_worker(args, w):
     N, D, K = args.points or w["N"], w["D"], w["K"]
     X = make_points(w, args.points)
     trees = args.ref_trees or w["trees"]
-    times = []
+    times, recalls = [], []
+    truth = queries = None
+    if not args.no_recall:
+        import torch
+        nq = min(N, args.recall_queries)
+        queries = np.sort(np.random.default_rng(w["seed"] + 1000).choice(N, nq, replace=False))
+        X_dev = torch.from_numpy(X).cuda()
+        truth = exact_knn_torch(X_dev, queries, K).cpu().numpy()
+        del X_dev
+        torch.cuda.empty_cache()
     for s in range(args.warmup + args.steps):
         idx = np.full((N, K), -1, np.int32)
         dst = np.full((N, K), np.inf, np.float32)
@@ -780,14 +789,10 @@ def reference_worker(args, w):
                             X.ctypes.data, idx.ctypes.data, dst.ctypes.data, log.ctypes.data)
         if s >= args.warmup:
             times.append(time.time() - t0)
-    recall = None
-    if not args.no_recall:
-        import torch
-        nq = min(N, args.recall_queries)
-        queries = np.sort(np.random.default_rng(w["seed"] + 1000).choice(N, nq, replace=False))
-        truth = exact_knn_torch(torch.from_numpy(X).cuda(), queries, K).cpu().numpy()
-        recall = recall_of(truth, idx[queries])
-    print("REFRESULT " + json.dumps({"times": times, "recall": recall, "trees": trees,
+            if truth is not None:       # the reference is not deterministic: every run's recall
+                recalls.append(recall_of(truth, idx[queries]))
+    recall = recalls[-1] if recalls else None
+    print("REFRESULT " + json.dumps({"times": times, "recall": recall, "recalls": recalls, "trees": trees,
                                      "forest_s": float(log[16 * trees]), "explore_s": float(log[16 * trees + 1])}))
 
 
@@ -809,6 +814,8 @@ def run_reference(args, w):
         cmd += ["--ref-trees", str(args.ref_trees)]
     if args.no_recall:
         cmd += ["--no-recall"]
+    if args.max_children:
+        cmd += ["--max-children", str(args.max_children)]
     cmd += ["--ref-variant", args.ref_variant]
     env = dict(os.environ)
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
@@ -849,6 +856,7 @@ def run_reference(args, w):
                                       if args.ref_variant == "tiles" else "")},
         "e2e": {"value": value, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "reference_forest_s": r["forest_s"], "reference_explore_s": r["explore_s"],
+        "recall_each_run": r.get("recalls"), "s_each_run": r["times"],
     }
     print(json.dumps(line))
 
@@ -873,8 +881,12 @@ def main():
                     help="reference arm: its default bucket kernel or its tile variant")
     ap.add_argument("--distinct-queries", action="store_true",
                     help="query workload: fresh draws instead of the base set itself")
+    ap.add_argument("--max-children", type=int, default=0,
+                    help="override max_tree_children of the workload (both arms), e.g. 1024 to meet the reference's limit")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.max_children:
+        w["max"] = args.max_children
     if args.workload == "ann":
         {"reference": run_ann_reference, "reference-worker": ann_reference_worker}.get(args.impl, run_ann)(args, w)
     elif args.impl == "reference":

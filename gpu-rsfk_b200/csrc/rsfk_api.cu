@@ -246,13 +246,47 @@ void destroy_lanes(rsfk_ctx* h)
 // context and stream, merged into the lane's lists.
 // With d_queries the lists are query lists (NQ rows) and every tree is followed by the
 // query update instead of the bucket KNN.
+// Stagger of the lanes: lane g+1 starts on the GPU when lane g has finished the level loop of
+// its first tree (and goes on to the latency-bound subtree and bucket kernels), so that the
+// lanes do not walk through the same phase side by side.
+struct LaneStagger {
+    std::vector<cudaEvent_t> levels_done; // per lane
+    std::vector<std::atomic<int>> recorded;
+    explicit LaneStagger(int G) : levels_done(G, nullptr), recorded(G)
+    {
+        for (int g = 0; g < G; ++g) {
+            recorded[g].store(0);
+            cudaEventCreateWithFlags(&levels_done[g], cudaEventDisableTiming);
+        }
+    }
+    ~LaneStagger()
+    {
+        for (auto& e : levels_done)
+            if (e) cudaEventDestroy(e);
+    }
+};
+
 void lane_forest(rsfk_ctx* l, int lane, int G, const float* d_points, int N, int D, int K, int n_trees,
                  int first_tree, int tree_stride, int min_children, int max_children, int max_depth, int seed,
                  int* idx, float* dist, float* log_forest, int verbose, std::vector<cudaEvent_t>* ev,
-                 const float* d_queries, int NQ)
+                 const float* d_queries, int NQ, LaneStagger* stagger)
 {
     Context& c = l->c;
     cudaSetDevice(c.device);
+    if (stagger) {
+        if (lane + 1 < G) { // the next lane waits for this one
+            c.levels_done_event = stagger->levels_done[lane];
+            c.levels_done_flag = &stagger->recorded[lane];
+        }
+        if (lane > 0) {
+            // bounded host wait until the previous lane has recorded its event (or given up)
+            const double t0 = now_s();
+            while (stagger->recorded[lane - 1].load(std::memory_order_acquire) == 0 && now_s() - t0 < 0.2)
+                std::this_thread::yield();
+            if (stagger->recorded[lane - 1].load(std::memory_order_acquire) == 1)
+                cudaStreamWaitEvent(c.stream, stagger->levels_done[lane - 1], 0);
+        }
+    }
     const bool keep_before = c.keep_index;
     c.keep_index = keep_before || d_queries != nullptr;
     bool ok = true;
@@ -274,6 +308,10 @@ void lane_forest(rsfk_ctx* l, int lane, int G, const float* d_points, int N, int
             printf("tree %d: depth %d, leaves %d, leaf size %d..%d, build %.6f s\n", t, l->tree.levels,
                    l->tree.n_leaves, l->tree.min_leaf, l->tree.max_leaf, tb1 - tb0);
     }
+    if (stagger && lane + 1 < G && stagger->recorded[lane].load() == 0)
+        stagger->recorded[lane].store(2, std::memory_order_release); // nothing to wait for: this lane built no tree
+    c.levels_done_event = nullptr;
+    c.levels_done_flag = nullptr;
     ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest lane");
     ok = ok && c.check_error_flag();
     c.resolve_ann_events();
@@ -309,6 +347,7 @@ bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, i
     for (auto& e : ev) cudaEventCreate(&e);
     if (log_forest) memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
     const double t0 = now_s();
+    LaneStagger stagger(G);
     std::vector<std::thread> workers;
     for (int g = 0; g < G; ++g) {
         rsfk_ctx* l = h->lanes[g];
@@ -323,10 +362,11 @@ bool run_forest_lanes(rsfk_ctx* h, int G, const float* d_points, int N, int D, i
         if (g == 0) continue; // lane 0 runs on the calling thread
         workers.emplace_back(lane_forest, l, g, G, d_points, N, D, K, n_trees, first_tree, tree_stride,
                              min_children, max_children, max_depth, seed, lane_idx + list_elems * g,
-                             lane_dist + list_elems * g, log_forest, verbose, &ev, d_queries, NQ);
+                             lane_dist + list_elems * g, log_forest, verbose, &ev, d_queries, NQ, &stagger);
     }
     lane_forest(h->lanes[0], 0, G, d_points, N, D, K, n_trees, first_tree, tree_stride, min_children,
-                max_children, max_depth, seed, lane_idx, lane_dist, log_forest, verbose, &ev, d_queries, NQ);
+                max_children, max_depth, seed, lane_idx, lane_dist, log_forest, verbose, &ev, d_queries, NQ,
+                &stagger);
     for (auto& w : workers) w.join();
     bool ok = c.status == RSFK_OK;
     for (int g = 0; g < G; ++g) {

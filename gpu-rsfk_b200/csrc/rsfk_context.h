@@ -191,6 +191,11 @@ struct Context {
         ann_ev_used = 0;
     }
     std::vector<cudaEvent_t> level_ev; // three per tree level, reused by every tree
+    // When set, the next tree build records this event on the stream right after its level
+    // loop is enqueued, raises the flag, and clears both (forest lanes start one after the
+    // other on the GPU with it, so that they do not run the same phase at the same time).
+    cudaEvent_t levels_done_event = nullptr;
+    std::atomic<int>* levels_done_flag = nullptr;
     int level_hint = 0;                // levels the previous tree of this context needed
     int level_chunks_hint[LEVEL_HISTORY] = {}; // and the work chunks of its first levels (0: unknown)
     long long hint_points = 0;         // the N those hints belong to

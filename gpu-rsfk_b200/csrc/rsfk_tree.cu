@@ -1109,6 +1109,12 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
         batch = 2;
     }
     const double t_levels_end = host_now();
+    if (ctx.levels_done_event) {
+        cudaEventRecord(ctx.levels_done_event, st);
+        if (ctx.levels_done_flag) ctx.levels_done_flag->store(1, std::memory_order_release);
+        ctx.levels_done_event = nullptr;
+        ctx.levels_done_flag = nullptr;
+    }
     if (open) { // depth limit: nodes[cur] still holds open nodes (level depth-1)
         int grid = node_cap < ctx.sm_count * 8 ? node_cap : ctx.sm_count * 8;
         k_force_leaves<<<grid, 256, 0, st>>>(nodes[cur], cnt, depth - 1, perm[cur], perm_final, leaf_start,
