@@ -229,13 +229,16 @@ __global__ void k_tc_tiles(const int* __restrict__ leaf_start, const int* __rest
 }
 
 // ---------------------------------------------------------------------------
-// Leaf-ordered, centred copy of the points: rows[r][0..Dp) = x[perm[r]] - x[perm[row0]]
-// rounded to TF32 (zeros beyond D), norms[r] = |row|^2.  One CTA per tile, one warp per row.
+// Leaf-ordered copies of the points: rows[r][0..Dp) = x[perm[r]] - x[perm[row0]] rounded to
+// TF32 (zeros beyond D) for the tensor cores, norms[r] = |row|^2, and rows_exact[r][0..D) =
+// x[perm[r]] unchanged, from which the exact evaluation reads (the rows of a leaf lie together
+// there and stay in L2 while the leaf's tiles are at work; gathered through the permutation
+// they would come from all over the point array).  One CTA per tile, one warp per row.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ perm,
           const Tile* __restrict__ tiles, const int* __restrict__ n_tiles_ptr, int tile_cap,
-          float* __restrict__ rows, float* __restrict__ norms)
+          float* __restrict__ rows, float* __restrict__ norms, float* __restrict__ rows_exact)
 {
     extern __shared__ float4 smem4[];
     float* centre = reinterpret_cast<float*>(smem4); // [D]
@@ -252,9 +255,12 @@ k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ 
             const size_t row = (size_t)tl.row0 + tl.i0 + r;
             const float* x = pts + (size_t)perm[row] * D;
             float* y = rows + row * Dp;
+            float* z = rows_exact + row * D;
             float nrm = 0.0f;
             for (int k = lane; k < Dp; k += 32) {
-                float v = k < D ? __fsub_rn(__ldg(x + k), centre[k]) : 0.0f;
+                const float xv = k < D ? __ldg(x + k) : 0.0f;
+                if (k < D) z[k] = xv; // the untouched coordinates, for the exact evaluation
+                float v = k < D ? __fsub_rn(xv, centre[k]) : 0.0f;
                 // nearest value with 10 explicit mantissa bits: what kind::tf32 reads anyway
                 v = __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
                 y[k] = v;
@@ -273,7 +279,7 @@ k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ 
 // ---------------------------------------------------------------------------
 template <int KPL, bool VEC4>
 __global__ void __launch_bounds__(THREADS, 1)
-k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict__ pts, int D, int Dp, int K,
+k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict__ rows_exact, int D, int Dp, int K,
                 const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
                 const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
                 float* __restrict__ knn_dist, int max_leaf, float c_acc, unsigned long long* __restrict__ stats,
@@ -547,23 +553,38 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                     if (pending == 0 || (pending < 32 && !last_group)) continue;
                     const int self = ids[tl.i0 + r];
                     __syncwarp();
-                    for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)self * D + k);
+                    for (int k = lane; k < D; k += 32)
+                        xp[k] = rows_exact[(size_t)(tl.row0 + tl.i0 + r) * D + k];
                     WarpList<KPL> L;
                     L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
                     __syncwarp();
                     bool changed = false;
                     int qn = 0;
+                    // the first n (<= 32) queued rows (leaf order): exact distances in the sweep's
+                    // arithmetic from the leaf-ordered copy, then the usual merge under their point ids
+                    auto merge = [&](float dsum, int item, int n) {
+                        const int ci = item < n ? perm[queue[item]] : -1;
+                        unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(dsum, ci));
+                        while (mask) {
+                            const int b = __ffs(mask) - 1;
+                            mask &= mask - 1;
+                            changed |= L.try_insert(__shfl_sync(RSFK_FULL, dsum, b), __shfl_sync(RSFK_FULL, ci, b), K, lane);
+                        }
+                    };
                     for (int w = 0; w < n_words; ++w) {
                         const unsigned bits = sPass[r * PW + w];
                         if (bits == 0) continue;
                         __syncwarp();
                         if (lane == 0) sPass[r * PW + w] = 0u;
                         const bool pass = (bits >> lane) & 1u;
-                        if (pass) queue[qn + __popc(bits & ((1u << lane) - 1u))] = ids[32 * w + lane];
+                        if (pass) queue[qn + __popc(bits & ((1u << lane) - 1u))] = tl.row0 + 32 * w + lane;
                         qn += __popc(bits);
                         __syncwarp();
                         if (qn >= 32) {
-                            explore_flush<KPL, VEC4>(L, pts, D, xp, queue, 32, K, lane, changed);
+                            int item;
+                            const float dsum = VEC4 ? explore_dist32_vec4(rows_exact, D, xp, queue, 32, lane, item)
+                                                    : explore_dist32_scalar(rows_exact, D, xp, queue, 32, lane, item);
+                            merge(dsum, item, 32);
                             __syncwarp();
                             const int rest = qn - 32;
                             const int tmp = lane < rest ? queue[32 + lane] : -1;
@@ -573,7 +594,12 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                             __syncwarp();
                         }
                     }
-                    if (qn > 0) explore_flush<KPL, VEC4>(L, pts, D, xp, queue, qn, K, lane, changed);
+                    if (qn > 0) { // the last, usually short batch: the routine with the fewest load rounds
+                        int item;
+                        const float dsum = VEC4 ? explore_dist_vec4_any(rows_exact, D, xp, queue, qn, lane, item)
+                                                : explore_dist32_scalar(rows_exact, D, xp, queue, qn, lane, item);
+                        merge(dsum, item, qn);
+                    }
                     if (changed) {
                         L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
                         if (lane == 0) sThr[r] = L.thr_d;

@@ -497,6 +497,69 @@ __device__ __forceinline__ float explore_dist32_vec4(const float* __restrict__ p
     return mine;
 }
 
+// The same distances for at most 4*J candidates with J in {2, 4}: a lane keeps J rows
+// instead of eight and requests U = 8/J k-steps of each before it uses them, so that the
+// number of dependent load rounds falls from D/32 to D/(32 U) -- what a batch of a few
+// candidates of many dimensions waits for.  Every sum is formed in the same order.
+template <int J, int U>
+__device__ __forceinline__ float explore_dist_few_vec4(const float* __restrict__ pts, int D, const float* xp,
+                                                       const int* queue, int n, int lane, int& cand)
+{
+    const int g = lane >> 3, t = lane & 7;
+    const float4* xp4 = reinterpret_cast<const float4*>(xp);
+    const int D4 = D >> 2;
+    float acc[J][4];
+    const float4* row[J];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        row[j] = reinterpret_cast<const float4*>(pts + (size_t)queue[min(4 * j + g, n - 1)] * D);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[j][q] = 0.0f;
+    }
+    for (int k4 = t; k4 < D4; k4 += 8 * U) {
+        float4 v[U][J];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < J; ++j)
+                if (k4 + 8 * u < D4) v[u][j] = __ldg(row[j] + k4 + 8 * u);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (k4 + 8 * u < D4) {
+                const float4 x = xp4[k4 + 8 * u];
+#pragma unroll
+                for (int j = 0; j < J; ++j) {
+                    float df;
+                    df = __fsub_rn(v[u][j].x, x.x); acc[j][0] = __fmaf_rn(df, df, acc[j][0]);
+                    df = __fsub_rn(v[u][j].y, x.y); acc[j][1] = __fmaf_rn(df, df, acc[j][1]);
+                    df = __fsub_rn(v[u][j].z, x.z); acc[j][2] = __fmaf_rn(df, df, acc[j][2]);
+                    df = __fsub_rn(v[u][j].w, x.w); acc[j][3] = __fmaf_rn(df, df, acc[j][3]);
+                }
+            }
+        }
+    }
+    float mine = 0.0f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        float s = __fadd_rn(__fadd_rn(acc[j][0], acc[j][1]), __fadd_rn(acc[j][2], acc[j][3]));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 1));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 2));
+        s = __fadd_rn(s, __shfl_xor_sync(RSFK_FULL, s, 4));
+        if (j == t) mine = s;
+    }
+    cand = 4 * t + g; // lanes with t >= J hold no candidate: 4t+g >= 4J >= n
+    return mine;
+}
+
+// n candidates (1..32) with 16-byte loads: the routine with the fewest load rounds that holds them.
+__device__ __forceinline__ float explore_dist_vec4_any(const float* __restrict__ pts, int D, const float* xp,
+                                                       const int* queue, int n, int lane, int& cand)
+{
+    if (n <= 8) return explore_dist_few_vec4<2, 4>(pts, D, xp, queue, n, lane, cand);
+    if (n <= 16) return explore_dist_few_vec4<4, 2>(pts, D, xp, queue, n, lane, cand);
+    return explore_dist32_vec4(pts, D, xp, queue, n, lane, cand);
+}
+
 template <int KPL, bool VEC4>
 __device__ __forceinline__ void explore_flush(WarpList<KPL>& L, const float* __restrict__ pts, int D,
                                               const float* xp, const int* queue, int n, int K,
@@ -908,12 +971,13 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
     const int Dp = (D + tc::KC - 1) / tc::KC * tc::KC;
     const int tile_cap = N / tc::BM + tree.n_leaves + 1;
     float* rows = (float*)ctx.scratch(Context::TC_ROWS, sizeof(float) * (size_t)N * Dp);
+    float* rows_exact = (float*)ctx.scratch(Context::TC_EXACT, sizeof(float) * (size_t)N * D);
     float* norms = (float*)ctx.scratch(Context::TC_NORMS, sizeof(float) * (size_t)N);
     tc::Tile* tiles = (tc::Tile*)ctx.scratch(Context::TC_TILES, sizeof(tc::Tile) * (size_t)tile_cap);
     int* n_tiles = (int*)ctx.scratch(Context::TC_COUNT, sizeof(int));
     unsigned long long* counters = ctx.tc_counters();
     int* flag = ctx.error_flag();
-    if (!rows || !norms || !tiles || !n_tiles || !counters || !flag) return false;
+    if (!rows || !rows_exact || !norms || !tiles || !n_tiles || !counters || !flag) return false;
     EncodeTiledFn encode = tensor_map_encoder();
     if (!encode) return ctx.fail(RSFK_ERR_CUDA, "bucket_knn: the driver offers no cuTensorMapEncodeTiled");
     // rows[N][Dp] fp32; a box is 32 floats (128 bytes, the swizzle span) by 128 rows
@@ -932,9 +996,9 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
                                                                tree.max_leaf, tiles, tile_cap, n_tiles);
     int row_grid = tile_cap < ctx.sm_count * 8 ? tile_cap : ctx.sm_count * 8;
     tc::k_tc_rows<<<row_grid, 256, sizeof(float) * (size_t)D, st>>>(d_points, D, Dp, tree.perm, tiles, n_tiles,
-                                                                   tile_cap, rows, norms);
+                                                                   tile_cap, rows, norms, rows_exact);
     const tc::Layout lay = tc::layout_for(D, tree.max_leaf);
-    const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
+    const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(rows_exact) & 15) == 0);
     const float c_acc = tc::acc_margin(D);
     const int grid = tile_cap < ctx.sm_count ? tile_cap : ctx.sm_count;
     RSFK_DISPATCH_KPL(K, {
@@ -942,7 +1006,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
         if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
                        "bucket_knn_tc smem attribute"))
             return false;
-        kern<<<grid, tc::THREADS, lay.total, st>>>(map, d_points, D, Dp, K, tree.perm, norms, tiles, n_tiles,
+        kern<<<grid, tc::THREADS, lay.total, st>>>(map, rows_exact, D, Dp, K, tree.perm, norms, tiles, n_tiles,
                                                    tile_cap, d_idx, d_dist, tree.max_leaf, c_acc, counters, flag);
     });
     count_launches(3);
