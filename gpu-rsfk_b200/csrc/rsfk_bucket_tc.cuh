@@ -594,9 +594,9 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                             __syncwarp();
                         }
                     }
-                    if (qn > 0) { // the last, usually short batch: the routine with the fewest load rounds
+                    if (qn > 0) {
                         int item;
-                        const float dsum = VEC4 ? explore_dist_vec4_any(rows_exact, D, xp, queue, qn, lane, item)
+                        const float dsum = VEC4 ? explore_dist32_vec4(rows_exact, D, xp, queue, qn, lane, item)
                                                 : explore_dist32_scalar(rows_exact, D, xp, queue, qn, lane, item);
                         merge(dsum, item, qn);
                     }
