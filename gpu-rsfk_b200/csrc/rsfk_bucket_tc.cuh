@@ -283,7 +283,8 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                 const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
                 const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
                 float* __restrict__ knn_dist, int max_leaf, float c_acc, unsigned long long* __restrict__ stats,
-                int* __restrict__ error_flag)
+                int* __restrict__ error_flag, int* __restrict__ later_count, int* __restrict__ later_rows,
+                int* __restrict__ later_cand)
 {
     extern __shared__ unsigned char smem_raw[];
     // the swizzled operand tiles want 1024-byte alignment
@@ -551,6 +552,24 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
 #pragma unroll
                     for (int sft = 16; sft >= 1; sft >>= 1) pending += __shfl_xor_sync(RSFK_FULL, pending, sft);
                     if (pending == 0 || (pending < 32 && !last_group)) continue;
+                    if (pending < 32 && later_cand != nullptr) {
+                        // fewer than a batch after the last group: handed to k_tc_later, which has the
+                        // warps in flight that these short, latency-bound evaluations want
+                        int qn = 0;
+                        for (int w = 0; w < n_words; ++w) {
+                            const unsigned bits = sPass[r * PW + w];
+                            if ((bits >> lane) & 1u) queue[qn + __popc(bits & ((1u << lane) - 1u))] = tl.row0 + 32 * w + lane;
+                            qn += __popc(bits);
+                        }
+                        __syncwarp();
+                        int slot = 0;
+                        if (lane == 0) slot = atomicAdd(later_count, 1);
+                        slot = __shfl_sync(RSFK_FULL, slot, 0);
+                        if (lane == 0) later_rows[slot] = tl.row0 + tl.i0 + r;
+                        later_cand[(size_t)slot * 32 + lane] = lane < qn ? queue[lane] : -1;
+                        __syncwarp();
+                        continue;
+                    }
                     const int self = ids[tl.i0 + r];
                     __syncwarp();
                     for (int k = lane; k < D; k += 32)
@@ -627,6 +646,73 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                      : "memory");
     }
     if (threadIdx.x == 0 && *sAbort) atomicExch(error_flag, 1);
+}
+
+// ---------------------------------------------------------------------------
+// Rows that the pipeline kernel left with fewer than 32 candidates: one warp per row
+// evaluates them exactly and merges them.  Every row occurs at most once per tree, so
+// no two warps touch one list.  later_cand[slot][0..n) are rows in leaf order.
+// ---------------------------------------------------------------------------
+constexpr int LATER_WARPS = 8;
+template <int KPL, bool VEC4>
+__global__ void __launch_bounds__(32 * LATER_WARPS, VEC4 ? 2 : 1)
+k_tc_later(const float* __restrict__ rows_exact, int D, int K, const int* __restrict__ perm,
+           const int* __restrict__ later_count, const int* __restrict__ later_rows,
+           const int* __restrict__ later_cand, int* __restrict__ knn_idx, float* __restrict__ knn_dist)
+{
+    extern __shared__ float4 later_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int xp_floats = (D + 3) & ~3;
+    float* xp = reinterpret_cast<float*>(later_smem) + (size_t)warp * (xp_floats + 32);
+    int* queue = reinterpret_cast<int*>(xp + xp_floats);
+    const int n_rows = *later_count;
+    const int step = gridDim.x * LATER_WARPS;
+    int slot = blockIdx.x * LATER_WARPS + warp;
+    // the next row's position, point and candidates are requested one row ahead
+    int pos_next = slot < n_rows ? later_rows[slot] : 0;
+    int self_next = slot < n_rows ? perm[pos_next] : 0;
+    int cand_next = slot < n_rows ? later_cand[(size_t)slot * 32 + lane] : -1;
+    for (; slot < n_rows; slot += step) {
+        const int pos = pos_next, self = self_next, cand = cand_next;
+        if (slot + step < n_rows) {
+            pos_next = later_rows[slot + step];
+            cand_next = later_cand[(size_t)(slot + step) * 32 + lane];
+        }
+        const int qn = __popc(__ballot_sync(RSFK_FULL, cand >= 0));
+        __syncwarp();
+        queue[lane] = cand;
+        if (VEC4) {
+            const float4* src = reinterpret_cast<const float4*>(rows_exact + (size_t)pos * D);
+            for (int k4 = lane; k4 < (D >> 2); k4 += 32) reinterpret_cast<float4*>(xp)[k4] = src[k4];
+        } else {
+            for (int k = lane; k < D; k += 32) xp[k] = rows_exact[(size_t)pos * D + k];
+        }
+        WarpList<KPL> L;
+        L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+        __syncwarp();
+        bool changed = false;
+        // sixteen candidates at a time: four (or two) rows per lane group and two (or four) k-steps
+        // requested together, so that few dependent load rounds are left (and registers for 16 warps per SM)
+        for (int base = 0; base < qn; base += (VEC4 ? 16 : 32)) {
+            const int m = min(qn - base, VEC4 ? 16 : 32);
+            int item;
+            float dsum;
+            if (VEC4)
+                dsum = m <= 8 ? explore_dist_few_vec4<2, 4>(rows_exact, D, xp, queue + base, m, lane, item)
+                              : explore_dist_few_vec4<4, 2>(rows_exact, D, xp, queue + base, m, lane, item);
+            else
+                dsum = explore_dist32_scalar(rows_exact, D, xp, queue + base, m, lane, item);
+            const int ci = item < m ? perm[queue[base + item]] : -1;
+            unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(dsum, ci));
+            while (mask) {
+                const int b = __ffs(mask) - 1;
+                mask &= mask - 1;
+                changed |= L.try_insert(__shfl_sync(RSFK_FULL, dsum, b), __shfl_sync(RSFK_FULL, ci, b), K, lane);
+            }
+        }
+        if (changed) L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
+        if (slot + step < n_rows) self_next = perm[pos_next];
+    }
 }
 
 } // namespace tc

@@ -974,10 +974,14 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
     float* rows_exact = (float*)ctx.scratch(Context::TC_EXACT, sizeof(float) * (size_t)N * D);
     float* norms = (float*)ctx.scratch(Context::TC_NORMS, sizeof(float) * (size_t)N);
     tc::Tile* tiles = (tc::Tile*)ctx.scratch(Context::TC_TILES, sizeof(tc::Tile) * (size_t)tile_cap);
-    int* n_tiles = (int*)ctx.scratch(Context::TC_COUNT, sizeof(int));
+    int* n_tiles = (int*)ctx.scratch(Context::TC_COUNT, 2 * sizeof(int)); // [1]: rows left to k_tc_later
+    int* later_count = n_tiles ? n_tiles + 1 : nullptr;
+    int* later_rows = (int*)ctx.scratch(Context::TC_LATER_ROWS, sizeof(int) * (size_t)N);
+    int* later_cand = (int*)ctx.scratch(Context::TC_LATER_CAND, sizeof(int) * (size_t)N * 32);
     unsigned long long* counters = ctx.tc_counters();
     int* flag = ctx.error_flag();
-    if (!rows || !rows_exact || !norms || !tiles || !n_tiles || !counters || !flag) return false;
+    if (!rows || !rows_exact || !norms || !tiles || !n_tiles || !later_rows || !later_cand || !counters || !flag)
+        return false;
     EncodeTiledFn encode = tensor_map_encoder();
     if (!encode) return ctx.fail(RSFK_ERR_CUDA, "bucket_knn: the driver offers no cuTensorMapEncodeTiled");
     // rows[N][Dp] fp32; a box is 32 floats (128 bytes, the swizzle span) by 128 rows
@@ -991,7 +995,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) return ctx.fail(RSFK_ERR_CUDA, "bucket_knn: cuTensorMapEncodeTiled failed");
 
-    if (!ctx.check(cudaMemsetAsync(n_tiles, 0, sizeof(int), st), "clear tile count")) return false;
+    if (!ctx.check(cudaMemsetAsync(n_tiles, 0, 2 * sizeof(int), st), "clear tile count")) return false;
     tc::k_tc_tiles<<<(tree.n_leaves + 255) / 256, 256, 0, st>>>(tree.leaf_start, tree.leaf_count, tree.n_leaves,
                                                                tree.max_leaf, tiles, tile_cap, n_tiles);
     int row_grid = tile_cap < ctx.sm_count * 8 ? tile_cap : ctx.sm_count * 8;
@@ -1007,9 +1011,24 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
                        "bucket_knn_tc smem attribute"))
             return false;
         kern<<<grid, tc::THREADS, lay.total, st>>>(map, rows_exact, D, Dp, K, tree.perm, norms, tiles, n_tiles,
-                                                   tile_cap, d_idx, d_dist, tree.max_leaf, c_acc, counters, flag);
+                                                   tile_cap, d_idx, d_dist, tree.max_leaf, c_acc, counters, flag,
+                                                   later_count, later_rows, later_cand);
+        // the rows it left with less than a batch of candidates (a leaf's rows are disjoint from
+        // every other leaf's, so nothing else touches their lists)
+        auto later = vec4 ? tc::k_tc_later<KPL, true> : tc::k_tc_later<KPL, false>;
+        const size_t later_smem = sizeof(float) * (size_t)tc::LATER_WARPS * (((D + 3) & ~3) + 32);
+        if (later_smem > 48 * 1024 &&
+            !ctx.check(cudaFuncSetAttribute(later, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)later_smem),
+                       "bucket_knn_tc smem attribute"))
+            return false;
+        int per_sm = (int)(200 * 1024 / (later_smem + 1024));
+        per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+        const long long want = ((long long)N + tc::LATER_WARPS - 1) / tc::LATER_WARPS;
+        const int later_grid = (int)(want < (long long)ctx.sm_count * per_sm ? want : (long long)ctx.sm_count * per_sm);
+        later<<<later_grid, 32 * tc::LATER_WARPS, later_smem, st>>>(rows_exact, D, K, tree.perm, later_count,
+                                                                    later_rows, later_cand, d_idx, d_dist);
     });
-    count_launches(3);
+    count_launches(4);
     ctx.stats.tc_launches++;
     if (tree.sum_leaf_sq > 0) ctx.stats.tc_gram_flops += 2.0 * D * tree.sum_leaf_sq;
     return ctx.check(cudaGetLastError(), "bucket_knn_tc launch");
