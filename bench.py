@@ -414,11 +414,15 @@ def run_ours(args, w):
     if args.no_e2e:
         pass
     elif world == 1:
+        import gpu_rsfk
         r = RSFK(random_state=w["seed"])
         times = []
+        lib_gpus = min(args.library_gpus, torch.cuda.device_count())
+        if lib_gpus > 1:   # one process, the library itself spreads the call over the GPUs
+            gpu_rsfk.set_devices(list(range(lib_gpus)))
         for i in range(args.e2e_steps + 2):
-            r.find_nearest_neighbors(X, K, n_trees=w["trees"], min_tree_children=w["min"],
-                                     max_tree_children=w["max"], nn_exploring_factor=w["sweeps"])
+            res = r.find_nearest_neighbors(X, K, n_trees=w["trees"], min_tree_children=w["min"],
+                                           max_tree_children=w["max"], nn_exploring_factor=w["sweeps"])
             if i > 1:          # two untimed calls: context creation, scratch growth
                 times.append(r._last_search_time)
         t_e2e = float(np.mean(times))
@@ -426,6 +430,15 @@ def run_ours(args, w):
                    d2h_bytes_per_step=8 * N * K, ms_per_step=t_e2e * 1e3,
                    ms_each=[round(t * 1e3, 2) for t in times],
                    api="gpu_rsfk.RSFK.find_nearest_neighbors -> pymodule_rsfk_knn (host buffers)")
+        if lib_gpus > 1:
+            gpu_rsfk.set_devices(None)
+            one = r.find_nearest_neighbors(X, K, n_trees=w["trees"], min_tree_children=w["min"],
+                                           max_tree_children=w["max"], nn_exploring_factor=w["sweeps"])
+            e2e["library_gpus"] = lib_gpus
+            e2e["rows_identical_to_one_gpu"] = int(((one[0] == res[0]).all(axis=1) &
+                                                    (one[1].view(np.int32) == res[1].view(np.int32)).all(axis=1)).sum())
+            del one
+        del res
     else:
         out_i = torch.empty((rdist.row_block(N, world), K), dtype=torch.int32).pin_memory()
         out_d = torch.empty((rdist.row_block(N, world), K), dtype=torch.float32).pin_memory()
@@ -881,6 +894,8 @@ def main():
                     help="reference arm: its default bucket kernel or its tile variant")
     ap.add_argument("--distinct-queries", action="store_true",
                     help="query workload: fresh draws instead of the base set itself")
+    ap.add_argument("--library-gpus", type=int, default=1,
+                    help="host-buffer leg of a single-process run: GPUs the library spreads one call over")
     ap.add_argument("--max-children", type=int, default=0,
                     help="override max_tree_children of the workload (both arms), e.g. 1024 to meet the reference's limit")
     args = ap.parse_args()

@@ -1,6 +1,8 @@
 // C ABI of librsfk.so (declarations and reference citations: include/rsfk_b200.h).
 #include <algorithm>
 #include <chrono>
+#include <condition_variable>
+#include <map>
 #include <cstdlib>
 #include <cstring>
 #include <functional>
@@ -516,6 +518,249 @@ bool run_sweeps(rsfk_ctx* h, const float* d_points, int N, int D, int K, int swe
     return true;
 }
 
+// ---------------------------------------------------------------------------
+// Several GPUs inside one host-pointer call (one process, one host thread per GPU).
+// The trees of the forest are dealt out round-robin; every GPU holds all the points
+// (its own slice uploaded over PCIe, the others' fetched from their owners over
+// NVLink) and builds its trees into lists of its own.  GPU g then owns rows
+// [N g / G, N (g+1) / G): it fetches those rows of every other GPU's lists, merges
+// them with its own and with the caller's, runs the sweeps on them (a sweep's
+// snapshot of the whole graph is gathered from the owners) and writes them back to
+// the caller.  The lists are canonical, so the result is the one a single GPU gives,
+// bit for bit.
+// ---------------------------------------------------------------------------
+std::vector<int> g_devices;                  // rsfk_set_devices
+std::map<int, rsfk_ctx*> g_device_ctx;       // one context per device used that way
+
+std::vector<int> devices_for_call()
+{
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) count = 0;
+    std::vector<int> devs = g_devices;
+    if (devs.empty()) {
+        if (const char* e = getenv("RSFK_DEVICES")) {
+            for (const char* p = e; *p;) {
+                char* end = nullptr;
+                const long v = strtol(p, &end, 10);
+                if (end == p) break;
+                devs.push_back((int)v);
+                p = *end == ',' ? end + 1 : end;
+            }
+        } else if (const char* e = getenv("RSFK_NUM_GPUS")) {
+            const int n = std::min(atoi(e), count);
+            for (int g = 0; g < n; ++g) devs.push_back(g);
+        }
+    }
+    for (int d : devs)
+        if (d < 0 || d >= count) return {}; // a list that names a missing device is ignored
+    std::sort(devs.begin(), devs.end());
+    devs.erase(std::unique(devs.begin(), devs.end()), devs.end());
+    return devs;
+}
+
+// Rendezvous of the per-GPU host threads; a failure anywhere is seen by everybody at
+// the next rendezvous, where they all leave together.
+struct HostBarrier {
+    explicit HostBarrier(int n) : n_(n) {}
+    bool wait(bool my_ok)
+    {
+        std::unique_lock<std::mutex> lock(m_);
+        ok_ = ok_ && my_ok;
+        if (++waiting_ == n_) {
+            waiting_ = 0;
+            ++phase_;
+            cv_.notify_all();
+        } else {
+            const int p = phase_;
+            cv_.wait(lock, [&] { return phase_ != p; });
+        }
+        return ok_;
+    }
+private:
+    std::mutex m_;
+    std::condition_variable cv_;
+    int n_, waiting_ = 0, phase_ = 0;
+    bool ok_ = true;
+};
+
+struct DeviceShare {
+    rsfk_ctx* h = nullptr;
+    float* d_points = nullptr;
+    int* d_idx = nullptr;
+    float* d_dist = nullptr;
+    std::vector<float> log;   // this GPU's trees, [attribute][tree] as the caller's log
+    int n_trees = 0;
+};
+
+void knn_on_devices(const std::vector<int>& devs, int n_trees, int K, int N, int D, int min_children,
+                    int max_children, int max_depth, int verbose, int seed, int sweeps, float* points,
+                    int* knn_indices, float* knn_sqr_distances, float* log_forest)
+{
+    const int G = (int)devs.size();
+    std::vector<DeviceShare> share(G);
+    for (int g = 0; g < G; ++g) {
+        auto it = g_device_ctx.find(devs[g]);
+        if (it == g_device_ctx.end()) {
+            rsfk_ctx* h = make_ctx(devs[g], nullptr, true);
+            if (!h) {
+                g_last_status = RSFK_ERR_CUDA;
+                g_last_message = "no usable CUDA device";
+                return;
+            }
+            // direct loads from the other GPUs' memory where the machine allows it
+            for (int p = 0; p < G; ++p) {
+                int can = 0;
+                if (p != g && cudaDeviceCanAccessPeer(&can, devs[g], devs[p]) == cudaSuccess && can)
+                    if (cudaDeviceEnablePeerAccess(devs[p], 0) != cudaSuccess) cudaGetLastError();
+            }
+            it = g_device_ctx.emplace(devs[g], h).first;
+        }
+        share[g].h = it->second;
+        share[g].h->c.status = RSFK_OK;
+        share[g].h->c.message.clear();
+        share[g].n_trees = n_trees > g ? (n_trees - g + G - 1) / G : 0;
+        share[g].log.assign((size_t)16 * share[g].n_trees + 2, 0.0f);
+    }
+    auto row_lo = [&](int g) { return (long long)N * g / G; };
+    HostBarrier barrier(G);
+    double t_forest = 0.0, t_sweeps = 0.0;
+    const double t_begin = now_s();
+
+    auto body = [&](int g) {
+        DeviceShare& me = share[g];
+        Context& c = me.h->c;
+        const int dev = c.device;
+        cudaSetDevice(dev);
+        const long long lo = row_lo(g), hi = row_lo(g + 1), rows = hi - lo;
+        const size_t list_elems = (size_t)N * K;
+        long long max_rows = 0;
+        for (int p = 0; p < G; ++p) max_rows = std::max(max_rows, row_lo(p + 1) - row_lo(p));
+        const size_t stage_elems = (size_t)max_rows * K;
+        me.d_points = (float*)c.scratch(Context::HOST_POINTS, sizeof(float) * (size_t)N * D);
+        me.d_idx = (int*)c.scratch(Context::HOST_IDX, sizeof(int) * list_elems);
+        me.d_dist = (float*)c.scratch(Context::HOST_DIST, sizeof(float) * list_elems);
+        // rows [lo, hi) of the G-1 other GPUs' lists and of the caller's
+        int* peer_idx = (int*)c.scratch(Context::PEER_IDX, sizeof(int) * stage_elems * G);
+        float* peer_dist = (float*)c.scratch(Context::PEER_DIST, sizeof(float) * stage_elems * G);
+        bool ok = me.d_points && me.d_idx && me.d_dist && peer_idx && peer_dist;
+        auto copy = [&](void* d, void* h, size_t n, bool to_device, const char* what) {
+            if (n == 0) return true;
+            // a copier of this thread's own: pinned buffers and streams belong to one device
+            if (cudaMemcpy(to_device ? d : h, to_device ? h : d, n,
+                           to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost) == cudaSuccess)
+                return true;
+            return c.fail(RSFK_ERR_CUDA, std::string(what) + " failed");
+        };
+        // 1. this GPU's slice of the points; the caller's lists for its rows
+        ok = ok && copy(me.d_points + (size_t)lo * D, points + (size_t)lo * D, sizeof(float) * (size_t)rows * D, true,
+                        "H2D points");
+        ok = ok && copy(peer_idx + stage_elems * (G - 1), knn_indices + (size_t)lo * K, sizeof(int) * (size_t)rows * K,
+                        true, "H2D lists");
+        ok = ok && copy(peer_dist + stage_elems * (G - 1), knn_sqr_distances + (size_t)lo * K,
+                        sizeof(float) * (size_t)rows * K, true, "H2D lists");
+        if (!barrier.wait(ok)) return;
+        // 2. the other slices from their owners
+        for (int p = 0; p < G && ok; ++p) {
+            if (p == g) continue;
+            const long long plo = row_lo(p), prow = row_lo(p + 1) - plo;
+            if (prow > 0)
+                ok = c.check(cudaMemcpyPeerAsync(me.d_points + (size_t)plo * D, dev, share[p].d_points + (size_t)plo * D,
+                                                 share[p].h->c.device, sizeof(float) * (size_t)prow * D, c.stream),
+                             "points from a peer");
+        }
+        // 3. this GPU's trees into empty lists
+        const double t0 = now_s();
+        ok = ok && rsfk::fill_empty_lists(c, me.d_idx, me.d_dist, (long long)list_elems);
+        ok = ok && run_forest(me.h, me.d_points, N, D, K, me.n_trees, g, G, min_children, max_children, max_depth,
+                              seed, me.d_idx, me.d_dist, me.log.data(), g == 0 ? verbose : 0, nullptr);
+        ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
+        if (!barrier.wait(ok)) return;
+        if (g == 0) t_forest = now_s() - t0;
+        // 4. rows [lo, hi) of everybody's lists, merged in place over this GPU's own
+        {
+            const int* ip[10];
+            const float* dp[10];
+            int n_lists = 0;
+            ip[n_lists] = me.d_idx + (size_t)lo * K;
+            dp[n_lists++] = me.d_dist + (size_t)lo * K;
+            int slot = 0;
+            for (int p = 0; p < G && ok && rows > 0; ++p) {
+                if (p == g) continue;
+                int* si = peer_idx + stage_elems * slot;
+                float* sd = peer_dist + stage_elems * slot;
+                ok = c.check(cudaMemcpyPeerAsync(si, dev, share[p].d_idx + (size_t)lo * K, share[p].h->c.device,
+                                                 sizeof(int) * (size_t)rows * K, c.stream), "lists from a peer") &&
+                     c.check(cudaMemcpyPeerAsync(sd, dev, share[p].d_dist + (size_t)lo * K, share[p].h->c.device,
+                                                 sizeof(float) * (size_t)rows * K, c.stream), "lists from a peer");
+                ip[n_lists] = si;
+                dp[n_lists++] = sd;
+                ++slot;
+            }
+            // the caller's rows in canonical form
+            ok = ok && rsfk::sort_rows(c, peer_idx + stage_elems * (G - 1), peer_dist + stage_elems * (G - 1), rows, K);
+            ip[n_lists] = peer_idx + stage_elems * (G - 1);
+            dp[n_lists++] = peer_dist + stage_elems * (G - 1);
+            ok = ok && rsfk::merge_lists(c, rows, K, n_lists, ip, dp, me.d_idx + (size_t)lo * K,
+                                         me.d_dist + (size_t)lo * K);
+            ok = ok && c.check(cudaStreamSynchronize(c.stream), "list exchange");
+        }
+        if (!barrier.wait(ok)) return;
+        // 5. sweeps over this GPU's rows; the snapshot of the whole graph comes from the owners
+        const double t1 = now_s();
+        int* snap = sweeps > 0 ? (int*)c.scratch(Context::SNAPSHOT, sizeof(int) * list_elems) : nullptr;
+        ok = ok && (sweeps <= 0 || snap != nullptr);
+        for (int s = 0; s < sweeps; ++s) {
+            for (int p = 0; p < G && ok; ++p) {
+                const long long plo = row_lo(p), prow = row_lo(p + 1) - plo;
+                if (prow <= 0) continue;
+                ok = c.check(cudaMemcpyPeerAsync(snap + (size_t)plo * K, dev, share[p].d_idx + (size_t)plo * K,
+                                                 share[p].h->c.device, sizeof(int) * (size_t)prow * K, c.stream),
+                             "snapshot");
+            }
+            ok = ok && c.check(cudaStreamSynchronize(c.stream), "snapshot");
+            if (!barrier.wait(ok)) return; // nobody changes its rows before everybody has the snapshot
+            if (rows > 0)
+                ok = rsfk::explore_sweep(c, me.d_points, N, D, K, snap, me.d_idx, me.d_dist, (int)lo, (int)hi, 0);
+            ok = ok && c.check(cudaStreamSynchronize(c.stream), "exploration");
+            if (!barrier.wait(ok)) return;
+        }
+        ok = ok && c.check_error_flag();
+        if (g == 0) t_sweeps = now_s() - t1;
+        // 6. this GPU's rows back to the caller
+        ok = ok && copy(me.d_idx + (size_t)lo * K, knn_indices + (size_t)lo * K, sizeof(int) * (size_t)rows * K, false,
+                        "D2H indices");
+        ok = ok && copy(me.d_dist + (size_t)lo * K, knn_sqr_distances + (size_t)lo * K,
+                        sizeof(float) * (size_t)rows * K, false, "D2H distances");
+        barrier.wait(ok);
+    };
+
+    std::vector<std::thread> workers;
+    for (int g = 1; g < G; ++g) workers.emplace_back(body, g);
+    body(0);
+    for (auto& w : workers) w.join();
+
+    g_last_status = RSFK_OK;
+    g_last_message.clear();
+    for (int g = 0; g < G; ++g) {
+        const Context& c = share[g].h->c;
+        if (c.status != RSFK_OK && g_last_status == RSFK_OK) publish(c);
+    }
+    if (log_forest) {
+        memset(log_forest, 0, sizeof(float) * (size_t)(16 * n_trees + 2));
+        for (int g = 0; g < G; ++g)
+            for (int i = 0; i < share[g].n_trees; ++i)
+                for (int a = 0; a < 16; ++a)
+                    log_forest[(size_t)a * n_trees + g + (size_t)i * G] = share[g].log[(size_t)a * share[g].n_trees + i];
+        log_forest[16 * n_trees] = (float)t_forest;
+        log_forest[16 * n_trees + 1] = (float)t_sweeps;
+    }
+    if (verbose >= 1 && g_last_status == RSFK_OK) {
+        printf("Creating RSFK forest takes %lf seconds\n", t_forest);
+        printf("Nearest Neighbors Exploring computation Kernel takes %lf seconds\n", t_sweeps);
+        printf("%d GPUs, whole call %lf seconds\n", G, now_s() - t_begin);
+    }
+}
+
 } // namespace
 
 extern "C" {
@@ -528,16 +773,32 @@ int rsfk_max_neighbors(void) { return rsfk::list_capacity(); }
 void rsfk_release_memory(void)
 {
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (!g_default) return;
-    cudaSetDevice(g_default->c.device);
-    cudaStreamSynchronize(g_default->c.stream);
-    destroy_lanes(g_default);
-    for (auto& b : g_default->c.slots) {
-        if (b.ptr) cudaFree(b.ptr);
-        b.ptr = nullptr;
-        b.bytes = 0;
+    std::vector<rsfk_ctx*> all;
+    if (g_default) all.push_back(g_default);
+    for (auto& kv : g_device_ctx) all.push_back(kv.second);
+    for (rsfk_ctx* h : all) {
+        cudaSetDevice(h->c.device);
+        cudaStreamSynchronize(h->c.stream);
+        destroy_lanes(h);
+        for (auto& b : h->c.slots) {
+            if (b.ptr) cudaFree(b.ptr);
+            b.ptr = nullptr;
+            b.bytes = 0;
+        }
+        h->has_tree = false;
     }
-    g_default->has_tree = false;
+    if (g_default) cudaSetDevice(g_default->c.device);
+}
+
+int rsfk_set_devices(int n, const int* devices)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int count = 0;
+    if (n < 0 || n > 8 || (n > 0 && !devices) || cudaGetDeviceCount(&count) != cudaSuccess) return RSFK_ERR_ARG;
+    for (int i = 0; i < n; ++i)
+        if (devices[i] < 0 || devices[i] >= count) return RSFK_ERR_ARG;
+    g_devices.assign(devices, devices + n);
+    return RSFK_OK;
 }
 
 long long rsfk_kernel_launches(void) { return rsfk::g_kernel_launches.load(); }
@@ -565,6 +826,15 @@ void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TRE
         c.fail(RSFK_ERR_UNSUPPORTED, "pymodule_rsfk_knn: K above 256 is not supported");
         publish(c);
         return;
+    }
+    {
+        // several GPUs when the caller asked for them (rsfk_set_devices, RSFK_DEVICES, RSFK_NUM_GPUS)
+        const std::vector<int> devs = devices_for_call();
+        if (devs.size() > 1 && (long long)N >= (long long)devs.size()) {
+            knn_on_devices(devs, n_trees, K, N, D, MIN_TREE_CHILD, MAX_TREE_CHILD, MAX_DEPTH, VERBOSE, RANDOM_STATE,
+                           nn_exploring_factor, points, knn_indices, knn_sqr_distances, log_forest);
+            return;
+        }
     }
     const size_t pts_bytes = sizeof(float) * (size_t)N * D, list_elems = (size_t)N * K;
     const double ta0 = now_s();

@@ -546,6 +546,16 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                 // tightens the filter of the following groups) and after the last group.
                 const bool last_group = (g == n_groups - 1);
                 const int n_words = min((tl.m + 31) >> 5, (g + 1) * (BN / 32));
+                // queue[0..n) of row r becomes an entry of k_tc_later's work list (a row at most once per tree)
+                auto hand_over = [&](int r, int n) {
+                    __syncwarp();
+                    int slot = 0;
+                    if (lane == 0) slot = atomicAdd(later_count, 1);
+                    slot = __shfl_sync(RSFK_FULL, slot, 0);
+                    if (lane == 0) later_rows[slot] = tl.row0 + tl.i0 + r;
+                    later_cand[(size_t)slot * 32 + lane] = lane < n ? queue[lane] : -1;
+                    __syncwarp();
+                };
                 for (int r = ew; r < mI; r += EPI_WARPS) {
                     int pending = 0;
                     for (int w = lane; w < n_words; w += 32) pending += __popc(sPass[r * PW + w]);
@@ -561,13 +571,7 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                             if ((bits >> lane) & 1u) queue[qn + __popc(bits & ((1u << lane) - 1u))] = tl.row0 + 32 * w + lane;
                             qn += __popc(bits);
                         }
-                        __syncwarp();
-                        int slot = 0;
-                        if (lane == 0) slot = atomicAdd(later_count, 1);
-                        slot = __shfl_sync(RSFK_FULL, slot, 0);
-                        if (lane == 0) later_rows[slot] = tl.row0 + tl.i0 + r;
-                        later_cand[(size_t)slot * 32 + lane] = lane < qn ? queue[lane] : -1;
-                        __syncwarp();
+                        hand_over(r, qn);
                         continue;
                     }
                     const int self = ids[tl.i0 + r];
@@ -613,7 +617,9 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                             __syncwarp();
                         }
                     }
-                    if (qn > 0) {
+                    if (qn > 0 && last_group && later_cand != nullptr) {
+                        hand_over(r, qn); // the rest after the full batches
+                    } else if (qn > 0) {
                         int item;
                         const float dsum = VEC4 ? explore_dist32_vec4(rows_exact, D, xp, queue, qn, lane, item)
                                                 : explore_dist32_scalar(rows_exact, D, xp, queue, qn, lane, item);

@@ -66,6 +66,19 @@ class ForestLog(object):
         self.exploration_time = float(data[16 * n_trees + 1]) if len(data) >= 2 else 0.0
 
 
+def set_devices(devices=None):
+    """GPUs that one ``find_nearest_neighbors`` call is spread over inside the library
+    (``rsfk_set_devices``): a list of device numbers, or None / one device for a single GPU.
+    The graph is the single-GPU graph bit for bit.  The reference has no counterpart (it runs
+    on one GPU); without this call ``RSFK_DEVICES`` or ``RSFK_NUM_GPUS`` in the environment
+    are honoured, which also works from the reference's own wrapper."""
+    devs = [] if devices is None else [int(d) for d in devices]
+    arr = (ctypes.c_int * max(1, len(devs)))(*devs)
+    rc = _lib.load().rsfk_set_devices(len(devs), arr)
+    if rc != 0:
+        raise ValueError("set_devices: unknown device in %r" % (devs,))
+
+
 def _check_children(min_tree_children, max_tree_children):
     if min_tree_children < 0:
         raise Exception('min_tree_children = {} \t => min_tree_children must be at least 1'

@@ -3,7 +3,7 @@
 ``RSFK`` is the drop-in class of the reference package; ``DeviceForest`` is the
 device-resident interface (torch CUDA tensors in and out, no host copies).
 """
-from .RSFK import RSFK, ForestLog, random_motion, test  # noqa: F401
+from .RSFK import RSFK, ForestLog, random_motion, set_devices, test  # noqa: F401
 from ._lib import RSFKLibraryError  # noqa: F401
 
-__all__ = ["RSFK", "ForestLog", "random_motion", "test", "RSFKLibraryError"]
+__all__ = ["RSFK", "ForestLog", "random_motion", "set_devices", "test", "RSFKLibraryError"]

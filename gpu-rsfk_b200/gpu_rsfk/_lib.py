@@ -72,6 +72,8 @@ def load():
     L.rsfk_release_memory.argtypes = []
     L.rsfk_max_neighbors.restype = i
     L.rsfk_max_neighbors.argtypes = []
+    L.rsfk_set_devices.restype = i
+    L.rsfk_set_devices.argtypes = [i, _c_int_p]
 
     L.rsfk_ctx_create.restype = vp
     L.rsfk_ctx_create.argtypes = [i, vp]

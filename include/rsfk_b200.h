@@ -95,6 +95,17 @@ RSFK_EXPORT long long rsfk_kernel_launches(void);
 RSFK_EXPORT void rsfk_release_memory(void);
 /* Largest K the K-list kernels support. */
 RSFK_EXPORT int rsfk_max_neighbors(void);
+/* GPUs that pymodule_rsfk_knn spreads one call over (one process, one host thread
+ * per GPU).  The trees are dealt out round-robin, every GPU holds all the points
+ * (its slice comes from the host, the rest from the other GPUs), GPU g merges and
+ * sweeps rows [N g / G, N (g+1) / G) of the graph, fetched from the other GPUs'
+ * lists; the result is the single-GPU result bit for bit.  n = 0 or 1 returns to
+ * one GPU (RSFK_DEVICE).  Without this call the environment decides:
+ * RSFK_DEVICES="0,1,..." or RSFK_NUM_GPUS=G (devices 0..G-1).  At most 8 devices.
+ * No reference counterpart: the reference runs on one GPU (it calls no
+ * cudaSetDevice anywhere; src/rsfk.cu:2033-2228).  Returns RSFK_OK or
+ * RSFK_ERR_ARG. */
+RSFK_EXPORT int rsfk_set_devices(int n, const int* devices);
 
 /* ---------------------------------------------------------------- part 3 -- */
 
