@@ -111,6 +111,9 @@ private:
     cudaEvent_t event_[THREADS][2] = {};
 };
 StagedCopier g_copier;
+// Copiers of the devices a multi-GPU call uses (streams and events belong to one device);
+// entries are created before the per-GPU host threads start.
+std::map<int, StagedCopier*> g_device_copier;
 
 double now_s()
 {
@@ -615,6 +618,7 @@ void knn_on_devices(const std::vector<int>& devs, int n_trees, int K, int N, int
             }
             it = g_device_ctx.emplace(devs[g], h).first;
         }
+        if (!g_device_copier.count(devs[g])) g_device_copier[devs[g]] = new StagedCopier();
         share[g].h = it->second;
         share[g].h->c.status = RSFK_OK;
         share[g].h->c.message.clear();
@@ -643,12 +647,10 @@ void knn_on_devices(const std::vector<int>& devs, int n_trees, int K, int N, int
         int* peer_idx = (int*)c.scratch(Context::PEER_IDX, sizeof(int) * stage_elems * G);
         float* peer_dist = (float*)c.scratch(Context::PEER_DIST, sizeof(float) * stage_elems * G);
         bool ok = me.d_points && me.d_idx && me.d_dist && peer_idx && peer_dist;
+        StagedCopier* copier = g_device_copier.find(dev)->second; // the map is not modified while the threads run
         auto copy = [&](void* d, void* h, size_t n, bool to_device, const char* what) {
             if (n == 0) return true;
-            // a copier of this thread's own: pinned buffers and streams belong to one device
-            if (cudaMemcpy(to_device ? d : h, to_device ? h : d, n,
-                           to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost) == cudaSuccess)
-                return true;
+            if (copier->copy(d, h, n, to_device, dev)) return true;
             return c.fail(RSFK_ERR_CUDA, std::string(what) + " failed");
         };
         // 1. this GPU's slice of the points; the caller's lists for its rows
