@@ -32,6 +32,14 @@
 //             pair, and evaluate the passing pairs exactly -- while the tensor
 //             cores already work on the next column group.
 //
+// Three kernels share the work of a tree.  k_tc_thresholds (the same pipeline, another
+// epilogue) runs first and only over tiles with a row whose list is not full: it gives
+// such rows a threshold from the approximate distances to their whole leaf.
+// k_bucket_knn_tc filters and evaluates whatever comes in batches of 32 while a row's
+// threshold can still tighten the filter of the following column groups; what is left
+// of a row after the last group (fewer than 32 candidates) goes to a work list that
+// k_tc_later evaluates with more warps in flight.
+//
 // Every wait on an mbarrier is bounded; a wait that runs out raises an abort flag
 // that all roles poll, the MMA thread drains its outstanding work with a last
 // commit before tensor memory is released, the producer waits (bounded) for the
@@ -277,14 +285,18 @@ k_tc_rows(const float* __restrict__ pts, int D, int Dp, const int* __restrict__ 
 // The pipeline kernel.  stats[0] += pairs that passed the filter, stats[1] += pairs
 // looked at.
 // ---------------------------------------------------------------------------
-template <int KPL, bool VEC4>
-__global__ void __launch_bounds__(THREADS, 1)
-k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict__ rows_exact, int D, int Dp, int K,
-                const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
-                const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
-                float* __restrict__ knn_dist, int max_leaf, float c_acc, unsigned long long* __restrict__ stats,
-                int* __restrict__ error_flag, int* __restrict__ later_count, int* __restrict__ later_rows,
-                int* __restrict__ later_cand)
+// MODE 0: the filter and the exact evaluation.  MODE 1: the same pipeline over the tiles
+// flagged in open_tile (tiles with a row whose list is not full), whose epilogue only
+// derives a threshold for every row from the approximate distances of the WHOLE leaf
+// (thr0[row], see the MODE 1 block below); nothing is evaluated and no list is touched.
+template <int KPL, bool VEC4, int MODE>
+__device__ __forceinline__ void
+tc_pipeline(const CUtensorMap* map, const float* __restrict__ rows_exact, int D, int Dp, int K,
+            const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
+            const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
+            float* __restrict__ knn_dist, int max_leaf, float c_acc, unsigned long long* __restrict__ stats,
+            int* __restrict__ error_flag, int* __restrict__ later_count, int* __restrict__ later_rows,
+            int* __restrict__ later_cand, const int* __restrict__ open_tile, float* __restrict__ thr0)
 {
     extern __shared__ unsigned char smem_raw[];
     // the swizzled operand tiles want 1024-byte alignment
@@ -338,6 +350,7 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
             unsigned it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                if (MODE == 1 && !open_tile[t]) continue;
                 const Tile tl = tiles[t];
                 const int n_groups = (tl.m + BN - 1) / BN;
                 for (int g = 0; g < n_groups && ok; ++g) {
@@ -346,9 +359,9 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                         if (!mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1u) ^ 1u, sAbort)) { ok = false; break; }
                         const uint32_t dst = smem_u32(smem + s * STAGE_BYTES);
                         mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
-                        tma_load_2d(dst, &map, c * KC, tl.row0 + tl.i0, bar_full + 8 * s);
-                        tma_load_2d(dst + A_BYTES, &map, c * KC, tl.row0 + g * BN, bar_full + 8 * s);
-                        tma_load_2d(dst + 2 * A_BYTES, &map, c * KC, tl.row0 + g * BN + BM, bar_full + 8 * s);
+                        tma_load_2d(dst, map, c * KC, tl.row0 + tl.i0, bar_full + 8 * s);
+                        tma_load_2d(dst + A_BYTES, map, c * KC, tl.row0 + g * BN, bar_full + 8 * s);
+                        tma_load_2d(dst + 2 * A_BYTES, map, c * KC, tl.row0 + g * BN + BM, bar_full + 8 * s);
                     }
                 }
             }
@@ -370,6 +383,7 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
             unsigned it = 0, gc = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                if (MODE == 1 && !open_tile[t]) continue;
                 const Tile tl = tiles[t];
                 const int n_groups = (tl.m + BN - 1) / BN;
                 for (int g = 0; g < n_groups && ok; ++g, ++gc) {
@@ -411,7 +425,10 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
         bool ok = true;
         unsigned long long n_passed = 0, n_pairs = 0;
         int tile_parity = 0;
+        // MODE 1: what a thread keeps of its row from the first column group on
+        float h_lo = 0.0f, h_hi = CUDART_INF_F, h_scale = 0.0f, h_nbmax = 0.0f;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, tile_parity ^= 1) {
+            if (MODE == 1 && !open_tile[t]) continue;
             const Tile tl = tiles[t];
             const int n_groups = (tl.m + BN - 1) / BN;
             const int mI = min(BM, tl.m - tl.i0);
@@ -425,6 +442,8 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                     const int id = ids[tl.i0 + et];
                     thr = __ldcg(knn_dist + (size_t)id * K + (K - 1));
                     nrm = norms[tl.row0 + tl.i0 + et];
+                    // a row without a full list takes the threshold the first pass derived for it
+                    if (MODE == 0 && thr0 != nullptr && thr == CUDART_INF_F) thr = thr0[tl.row0 + tl.i0 + et];
                     if (thr == CUDART_INF_F) sOpen[tile_parity] = 1;
                 }
                 sThr[et] = thr;
@@ -444,6 +463,112 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                 epi_barrier();                    // also: sThr (row phase), sNrm*, cleared sPass
                 if (*sAbort) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if constexpr (MODE == 1) {
+                    // Threshold of a row from the approximate distances v = |y~i|^2 + |y~j|^2 - 2 y~i.y~j to
+                    // ALL the leaf's rows.  The first group gives [lo, hi]: lo its smallest v, hi the larger
+                    // of the two column halves' ceil(K/2)-th smallest (bisection, as in MODE 0), so at least
+                    // K pairs have v <= hi.  Every group then counts its v <= hi in NB bins over [lo, hi]
+                    // (shared memory, the pass-bit array).  After the last group the first bin edge with at
+                    // least K pairs at or below it is a v that K pairs do not exceed; their true distances
+                    // are then at most (sqrt(v + e1) + delta)^2, which is the threshold (e1 and delta with
+                    // the largest column norm among the counted pairs).
+                    const int NB = PW >= 64 ? 64 : (PW >= 32 ? 32 : (PW >= 16 ? 16 : 8));
+                    const float n_row = sNrmA[erow];
+                    const uint32_t trow = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(ab * BN + 128 * half);
+                    if (g == 0) {
+                        const int need = (K + 1) >> 1;
+                        int n_valid = 0;
+                        float vmin = CUDART_INF_F, vmax = -CUDART_INF_F;
+#pragma unroll 1
+                        for (int sb = 0; sb < 4; ++sb) {
+                            float gv[32];
+                            tmem_ld32(trow + (uint32_t)(32 * sb), gv);
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) {
+                                const int j = j0 + 128 * half + 32 * sb + c;
+                                const float v = __fmaf_rn(-2.0f, gv[c], n_row + nB[128 * half + 32 * sb + c]);
+                                if (j < tl.m && j != tl.i0 + erow) {
+                                    n_valid++;
+                                    vmin = fminf(vmin, v);
+                                    vmax = fmaxf(vmax, v);
+                                }
+                            }
+                        }
+                        float lo = vmin, hi = vmax;
+#pragma unroll 1
+                        for (int it = 0; it < 12; ++it) {
+                            const float mid = 0.5f * (lo + hi);
+                            int below = 0;
+#pragma unroll 1
+                            for (int sb = 0; sb < 4; ++sb) {
+                                float gv[32];
+                                tmem_ld32(trow + (uint32_t)(32 * sb), gv);
+#pragma unroll
+                                for (int c = 0; c < 32; ++c) {
+                                    const int j = j0 + 128 * half + 32 * sb + c;
+                                    const float v = __fmaf_rn(-2.0f, gv[c], n_row + nB[128 * half + 32 * sb + c]);
+                                    below += (j < tl.m && j != tl.i0 + erow && v <= mid) ? 1 : 0;
+                                }
+                            }
+                            if (below >= need) hi = mid; else lo = mid;
+                        }
+                        sBootT[half * BM + erow] = n_valid >= need ? hi : CUDART_INF_F;
+                        sBootN[half * BM + erow] = vmin;
+                        epi_barrier();
+                        h_hi = fmaxf(sBootT[erow], sBootT[BM + erow]);
+                        h_lo = fminf(sBootN[erow], sBootN[BM + erow]);
+                        h_scale = (h_hi < CUDART_INF_F && h_hi > h_lo) ? (float)NB / (h_hi - h_lo) : 0.0f;
+                        h_nbmax = 0.0f;
+                        epi_barrier(); // sBoot* are written again at the end of the tile
+                    }
+#pragma unroll 1
+                    for (int sb = 0; sb < 4; ++sb) { // every lane takes part in the loads
+                        float gv[32];
+                        tmem_ld32(trow + (uint32_t)(32 * sb), gv);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const int j = j0 + 128 * half + 32 * sb + c;
+                            const float nb = nB[128 * half + 32 * sb + c];
+                            const float v = __fmaf_rn(-2.0f, gv[c], n_row + nb);
+                            if (j < tl.m && j != tl.i0 + erow && v <= h_hi) {
+                                int bin = (int)((v - h_lo) * h_scale);
+                                bin = bin < 0 ? 0 : (bin > NB - 1 ? NB - 1 : bin);
+                                atomicAdd(&sPass[erow * PW + ((bin + erow) & (NB - 1))], 1u);
+                                h_nbmax = fmaxf(h_nbmax, nb);
+                            }
+                        }
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
+                    if (g == n_groups - 1) {
+                        sBootN[half * BM + erow] = h_nbmax;
+                        epi_barrier(); // both halves' counts and largest norms are in
+                        if (half == 0 && erow < mI) {
+                            float thr_row = CUDART_INF_F;
+                            if (h_hi < CUDART_INF_F) {
+                                unsigned cum = 0;
+                                int edge = NB;
+                                for (int bin = 0; bin < NB; ++bin) {
+                                    cum += sPass[erow * PW + ((bin + erow) & (NB - 1))];
+                                    if (cum >= (unsigned)K) { edge = bin + 1; break; }
+                                }
+                                // a v counted in bins < edge is below lo + edge (hi - lo) / NB up to the
+                                // rounding of the bin index (a few units in the last place of v - lo)
+                                float v_k = h_hi;
+                                if (edge < NB && h_scale > 0.0f)
+                                    v_k = fminf(h_hi, h_lo + ((float)edge / h_scale) * 1.00001f);
+                                const float nb_most = fmaxf(sBootN[erow], sBootN[BM + erow]);
+                                const float e1 = c_acc * (n_row + nb_most);
+                                const float delta = DELTA_REL * (sSqA[erow] + sqrtf(nb_most));
+                                const float root = sqrtf(fmaxf(v_k + e1, 0.0f)) + delta;
+                                thr_row = root * root * 1.000001f + 1e-30f;
+                            }
+                            thr0[tl.row0 + tl.i0 + erow] = thr_row;
+                        }
+                    }
+                    continue;
+                }
                 {
                     float thr = sThr[erow];
                     const float n_row = sNrmA[erow];
@@ -627,7 +752,7 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                     }
                     if (changed) {
                         L.store(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
-                        if (lane == 0) sThr[r] = L.thr_d;
+                        if (lane == 0) sThr[r] = fminf(sThr[r], L.thr_d); // a first-pass threshold stays until the list is full
                     }
                 }
             }
@@ -652,6 +777,54 @@ k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict
                      : "memory");
     }
     if (threadIdx.x == 0 && *sAbort) atomicExch(error_flag, 1);
+}
+
+template <int KPL, bool VEC4>
+__global__ void __launch_bounds__(THREADS, 1)
+k_bucket_knn_tc(const __grid_constant__ CUtensorMap map, const float* __restrict__ rows_exact, int D, int Dp, int K,
+                const int* __restrict__ perm, const float* __restrict__ norms, const Tile* __restrict__ tiles,
+                const int* __restrict__ n_tiles_ptr, int tile_cap, int* __restrict__ knn_idx,
+                float* __restrict__ knn_dist, int max_leaf, float c_acc, unsigned long long* __restrict__ stats,
+                int* __restrict__ error_flag, int* __restrict__ later_count, int* __restrict__ later_rows,
+                int* __restrict__ later_cand, const float* __restrict__ thr0)
+{
+    tc_pipeline<KPL, VEC4, 0>(&map, rows_exact, D, Dp, K, perm, norms, tiles, n_tiles_ptr, tile_cap, knn_idx, knn_dist,
+                              max_leaf, c_acc, stats, error_flag, later_count, later_rows, later_cand, nullptr,
+                              const_cast<float*>(thr0));
+}
+
+// First pass over the tiles that have a row without a full list (open_tile, n_open of them):
+// thr0[row] for every row of those tiles.  Leaves at once when there is no such tile.
+__global__ void __launch_bounds__(THREADS, 1)
+k_tc_thresholds(const __grid_constant__ CUtensorMap map, int D, int Dp, int K, const int* __restrict__ perm,
+                const float* __restrict__ norms, const Tile* __restrict__ tiles, const int* __restrict__ n_tiles_ptr,
+                int tile_cap, float* __restrict__ knn_dist, int max_leaf, float c_acc, int* __restrict__ error_flag,
+                const int* __restrict__ open_tile, const int* __restrict__ n_open, float* __restrict__ thr0)
+{
+    if (*n_open == 0) return;
+    tc_pipeline<1, false, 1>(&map, nullptr, D, Dp, K, perm, norms, tiles, n_tiles_ptr, tile_cap, nullptr, knn_dist,
+                             max_leaf, c_acc, nullptr, error_flag, nullptr, nullptr, nullptr, open_tile, thr0);
+}
+
+// open_tile[t] = 1 when tile t has a row whose list is not full; *n_open counts them.  One warp per tile.
+__global__ void k_tc_open_tiles(const Tile* __restrict__ tiles, const int* __restrict__ n_tiles_ptr, int tile_cap,
+                                const int* __restrict__ perm, const float* __restrict__ knn_dist, int K,
+                                int* __restrict__ open_tile, int* __restrict__ n_open)
+{
+    const int lane = threadIdx.x & 31;
+    const int n_tiles = min(*n_tiles_ptr, tile_cap);
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < n_tiles; t += (gridDim.x * blockDim.x) >> 5) {
+        const Tile tl = tiles[t];
+        const int n = min(BM, tl.m - tl.i0);
+        bool open = false;
+        for (int r = lane; r < n; r += 32)
+            open |= knn_dist[(size_t)perm[tl.row0 + tl.i0 + r] * K + (K - 1)] == CUDART_INF_F;
+        open = __any_sync(RSFK_FULL, open);
+        if (lane == 0) {
+            open_tile[t] = open ? 1 : 0;
+            if (open) atomicAdd(n_open, 1);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------

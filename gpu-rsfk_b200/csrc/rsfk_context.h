@@ -137,7 +137,7 @@ struct Context {
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
         SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
         RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
-        LANE_IDX, LANE_DIST, SYM_DEGREE, SYM_BLOCKS, TC_ROWS, TC_EXACT, TC_NORMS, TC_TILES, TC_COUNT, TC_STATS, TC_LATER_ROWS, TC_LATER_CAND,
+        LANE_IDX, LANE_DIST, SYM_DEGREE, SYM_BLOCKS, TC_ROWS, TC_EXACT, TC_NORMS, TC_TILES, TC_COUNT, TC_STATS, TC_LATER_ROWS, TC_LATER_CAND, TC_OPEN, TC_THR0,
         PEER_IDX, PEER_DIST,
         KM_IOTA, KM_KEYS, KM_ORDER, KM_START, KM_TEMP, KM_CHANGED, KM_POINTS, KM_CENTROIDS, KM_LABELS, KM_DIST,
         N_SLOTS

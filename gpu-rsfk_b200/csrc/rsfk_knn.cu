@@ -974,13 +974,18 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
     float* rows_exact = (float*)ctx.scratch(Context::TC_EXACT, sizeof(float) * (size_t)N * D);
     float* norms = (float*)ctx.scratch(Context::TC_NORMS, sizeof(float) * (size_t)N);
     tc::Tile* tiles = (tc::Tile*)ctx.scratch(Context::TC_TILES, sizeof(tc::Tile) * (size_t)tile_cap);
-    int* n_tiles = (int*)ctx.scratch(Context::TC_COUNT, 2 * sizeof(int)); // [1]: rows left to k_tc_later
+    // [1]: rows left to k_tc_later, [2]: tiles with a row whose list is not full
+    int* n_tiles = (int*)ctx.scratch(Context::TC_COUNT, 3 * sizeof(int));
     int* later_count = n_tiles ? n_tiles + 1 : nullptr;
+    int* n_open = n_tiles ? n_tiles + 2 : nullptr;
+    int* open_tile = (int*)ctx.scratch(Context::TC_OPEN, sizeof(int) * (size_t)tile_cap);
+    float* thr0 = (float*)ctx.scratch(Context::TC_THR0, sizeof(float) * (size_t)N);
     int* later_rows = (int*)ctx.scratch(Context::TC_LATER_ROWS, sizeof(int) * (size_t)N);
     int* later_cand = (int*)ctx.scratch(Context::TC_LATER_CAND, sizeof(int) * (size_t)N * 32);
     unsigned long long* counters = ctx.tc_counters();
     int* flag = ctx.error_flag();
-    if (!rows || !rows_exact || !norms || !tiles || !n_tiles || !later_rows || !later_cand || !counters || !flag)
+    if (!rows || !rows_exact || !norms || !tiles || !n_tiles || !later_rows || !later_cand || !open_tile || !thr0 ||
+        !counters || !flag)
         return false;
     EncodeTiledFn encode = tensor_map_encoder();
     if (!encode) return ctx.fail(RSFK_ERR_CUDA, "bucket_knn: the driver offers no cuTensorMapEncodeTiled");
@@ -995,7 +1000,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) return ctx.fail(RSFK_ERR_CUDA, "bucket_knn: cuTensorMapEncodeTiled failed");
 
-    if (!ctx.check(cudaMemsetAsync(n_tiles, 0, 2 * sizeof(int), st), "clear tile count")) return false;
+    if (!ctx.check(cudaMemsetAsync(n_tiles, 0, 3 * sizeof(int), st), "clear tile count")) return false;
     tc::k_tc_tiles<<<(tree.n_leaves + 255) / 256, 256, 0, st>>>(tree.leaf_start, tree.leaf_count, tree.n_leaves,
                                                                tree.max_leaf, tiles, tile_cap, n_tiles);
     int row_grid = tile_cap < ctx.sm_count * 8 ? tile_cap : ctx.sm_count * 8;
@@ -1005,6 +1010,20 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
     const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(rows_exact) & 15) == 0);
     const float c_acc = tc::acc_margin(D);
     const int grid = tile_cap < ctx.sm_count ? tile_cap : ctx.sm_count;
+    // Rows without a full list (a first tree): a first pass of the same pipeline over their tiles
+    // derives each row's threshold from the approximate distances to its whole leaf; it leaves at
+    // once when every list is full.
+    {
+        int open_grid = (tile_cap + 7) / 8;
+        if (open_grid > ctx.sm_count * 8) open_grid = ctx.sm_count * 8;
+        tc::k_tc_open_tiles<<<open_grid, 256, 0, st>>>(tiles, n_tiles, tile_cap, tree.perm, d_dist, K, open_tile, n_open);
+        if (!ctx.check(cudaFuncSetAttribute(tc::k_tc_thresholds, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
+                       "bucket_knn_tc smem attribute"))
+            return false;
+        tc::k_tc_thresholds<<<grid, tc::THREADS, lay.total, st>>>(map, D, Dp, K, tree.perm, norms, tiles, n_tiles,
+                                                                  tile_cap, d_dist, tree.max_leaf, c_acc, flag,
+                                                                  open_tile, n_open, thr0);
+    }
     RSFK_DISPATCH_KPL(K, {
         auto kern = vec4 ? tc::k_bucket_knn_tc<KPL, true> : tc::k_bucket_knn_tc<KPL, false>;
         if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total),
@@ -1012,7 +1031,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
             return false;
         kern<<<grid, tc::THREADS, lay.total, st>>>(map, rows_exact, D, Dp, K, tree.perm, norms, tiles, n_tiles,
                                                    tile_cap, d_idx, d_dist, tree.max_leaf, c_acc, counters, flag,
-                                                   later_count, later_rows, later_cand);
+                                                   later_count, later_rows, later_cand, thr0);
         // the rows it left with less than a batch of candidates (a leaf's rows are disjoint from
         // every other leaf's, so nothing else touches their lists)
         auto later = vec4 ? tc::k_tc_later<KPL, true> : tc::k_tc_later<KPL, false>;
@@ -1028,7 +1047,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
         later<<<later_grid, 32 * tc::LATER_WARPS, later_smem, st>>>(rows_exact, D, K, tree.perm, later_count,
                                                                     later_rows, later_cand, d_idx, d_dist);
     });
-    count_launches(4);
+    count_launches(6);
     ctx.stats.tc_launches++;
     if (tree.sum_leaf_sq > 0) ctx.stats.tc_gram_flops += 2.0 * D * tree.sum_leaf_sq;
     return ctx.check(cudaGetLastError(), "bucket_knn_tc launch");
