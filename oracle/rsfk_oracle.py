@@ -32,13 +32,14 @@ def build_reference():
     sources are present on this machine; returns the path or None."""
     out = os.path.join(_HERE, "_ref", "librsfk_ref.so")
     tiles = os.path.join(_HERE, "_ref", "librsfk_ref_tiles.so")
+    dump = os.path.join(_HERE, "_ref", "librsfk_ref_dump.so")
     wrapper = os.path.join(_HERE, "_ref", "ref_wrapper", "RSFK.py")
-    if os.path.exists(out) and os.path.exists(tiles) and os.path.exists(wrapper):
+    if os.path.exists(out) and os.path.exists(tiles) and os.path.exists(dump) and os.path.exists(wrapper):
         return out
     ref = reference_root()
     if ref is None:
         return out if os.path.exists(out) else None
-    subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "ref_tiles", "ref_wrapper", "REF=" + ref])
+    subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "ref_tiles", "ref_dump", "ref_wrapper", "REF=" + ref])
     return out
 
 
