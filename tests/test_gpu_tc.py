@@ -239,3 +239,29 @@ def test_every_kernel_choice_gives_the_same_lists(forest, oracle, N, D, K, MIN, 
         assert ran_tc == 4 if mode == 1 else (ran_tc == 0 if mode == 0 else 0 <= ran_tc <= 4)
     finally:
         forest.set_tc(-1)
+
+
+@pytest.mark.parametrize("N,D,K,MIN,MAX", [(6000, 128, 16, 400, 1200), (4000, 96, 32, 300, 700)])
+def test_rows_with_and_without_a_full_list_in_the_same_tiles(tc_forest, oracle, N, D, K, MIN, MAX):
+    """Lists of two trees, then every third row emptied again (and a few rows left half full): the
+    first pass gives the emptied rows a threshold from their whole leaf while their neighbours in
+    the same 128-row tile keep the threshold of their own full list."""
+    X = _clustered(N, D, 23, centers=5, sigma=0.6)
+    idx, dist = oracle.init_lists(N, K)
+    for t in range(2):
+        tr = oracle.build_tree(X, MIN, MAX, seed=70 + t)
+        idx, dist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+    empty_i, empty_d = oracle.init_lists(N, K)
+    idx[::3], dist[::3] = empty_i[::3], empty_d[::3]
+    idx[1::7, K // 2:], dist[1::7, K // 2:] = -1, np.inf          # rows that are half full
+    d_idx, d_dist, d_X = _dev(idx), _dev(dist), _dev(X)
+    before = tc_forest.stats()
+    for t in range(2):
+        tr = oracle.build_tree(X, MIN, MAX, seed=80 + t)
+        idx, dist = oracle.bucket_knn(X, K, tr["perm"], tr["leaf_start"], tr["leaf_count"], idx, dist)
+        tc_forest.bucket_knn_table(d_X, _dev(tr["perm"]), _dev(tr["leaf_start"]), _dev(tr["leaf_count"]),
+                                   int(tr["leaf_count"].max()), d_idx, d_dist)
+        tc_forest.synchronize()
+        np.testing.assert_array_equal(d_idx.cpu().numpy(), idx)
+        np.testing.assert_array_equal(d_dist.cpu().numpy().view(np.int32), dist.view(np.int32))
+    assert tc_forest.stats()["tc_launches"] - before["tc_launches"] == 2
