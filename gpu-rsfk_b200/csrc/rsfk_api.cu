@@ -810,6 +810,7 @@ void pymodule_rsfk_knn(int n_trees, int num_neighbors, int N, int D, int MIN_TRE
                        int nn_exploring_factor, float* points, int* knn_indices,
                        float* knn_sqr_distances, float* log_forest)
 {
+    rsfk::TraceRange trace("pymodule_rsfk_knn");
     std::lock_guard<std::mutex> lock(g_mutex);
     rsfk_ctx* h = default_ctx();
     if (!h) {
@@ -905,6 +906,7 @@ void pymodule_cluster_by_sample_tree(int N, int D, int MIN_TREE_CHILD, int MAX_T
                                      int** nodes_buckets, int** bucket_sizes, int* total_leaves,
                                      int* max_child)
 {
+    rsfk::TraceRange trace("pymodule_cluster_by_sample_tree");
     std::lock_guard<std::mutex> lock(g_mutex);
     rsfk_ctx* h = default_ctx();
     if (!h) {
@@ -972,6 +974,7 @@ void pymodule_rsfk_knn_ann(int n_trees, int num_neighbors, int N, int NQ, int D,
                            int nn_exploring_factor, float* points, float* query_points,
                            int* knn_indices, float* knn_sqr_distances, float* log_forest)
 {
+    rsfk::TraceRange trace("pymodule_rsfk_knn_ann");
     (void)nn_exploring_factor; // the reference's query path runs no exploration (src/rsfk.cu:98-152)
     (void)log_forest;          // nor does it write the log (its ForestLog is a local, src/rsfk.cu:169)
     std::lock_guard<std::mutex> lock(g_mutex);

@@ -11,9 +11,21 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "rsfk_common.cuh"
 
 namespace rsfk {
+
+// Named range on the calling host thread for timeline tools (NVTX, header-only: costs a
+// few nanoseconds when no tool is attached).  The reference brackets the same phases with
+// its Cron timers (src/rsfk.cu:509-512, 2076-2147).
+struct TraceRange {
+    explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+    ~TraceRange() { nvtxRangePop(); }
+    TraceRange(const TraceRange&) = delete;
+    TraceRange& operator=(const TraceRange&) = delete;
+};
 
 // kernels of this library launched so far in this process
 inline std::atomic<long long> g_kernel_launches{0};

@@ -176,6 +176,7 @@ static bool kmeans_update(Context& ctx, const float* d_points, int N, int D, int
 bool kmeans(Context& ctx, const float* d_points, int N, int D, int C, int max_iter, bool init_from_labels,
             float* d_centroids, int* d_labels, float* d_sq_dist, int* iterations)
 {
+    TraceRange trace("rsfk kmeans");
     if (N <= 0 || D <= 0 || C <= 0 || max_iter < 0) return ctx.fail(RSFK_ERR_ARG, "kmeans: invalid argument");
     if (C > N) return ctx.fail(RSFK_ERR_ARG, "kmeans: more clusters than points");
     cudaStream_t st = ctx.stream;

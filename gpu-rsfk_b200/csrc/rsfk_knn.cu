@@ -1056,6 +1056,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
 bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const TreeResult& tree,
                 int* d_idx, float* d_dist)
 {
+    TraceRange trace("rsfk bucket knn");
     (void)N;
     cudaStream_t launch_stream = ctx.stream;
     if (!check_k(ctx, K)) return false;
@@ -1116,6 +1117,7 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
                    int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0)
 {
+    TraceRange trace("rsfk exploration sweep");
     if (!check_k(ctx, K)) return false;
     if (row_end <= row_begin) return true;
     const ExploreShape shape = explore_shape(D, K);
@@ -1143,6 +1145,7 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
 bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_queries, int NQ, int D,
                     int K, const TreeResult& tree, int* d_idx, float* d_dist)
 {
+    TraceRange trace("rsfk query update");
     (void)N;
     if (!check_k(ctx, K)) return false;
     if (NQ <= 0) return true;
@@ -1207,6 +1210,7 @@ bool ann_bucket_knn(Context& ctx, const float* d_points, int N, const float* d_q
 bool merge_lists(Context& ctx, long long rows, int K, int G, const int* const* d_idx_lists,
                  const float* const* d_dist_lists, int* d_out_idx, float* d_out_dist)
 {
+    TraceRange trace("rsfk merge lists");
     if (!check_k(ctx, K)) return false;
     if (G < 1 || G > 16) return ctx.fail(RSFK_ERR_ARG, "merge_lists: between 1 and 16 lists");
     if (rows <= 0) return true;

@@ -950,6 +950,7 @@ bool tree_build(Context& ctx, const float* d_points, int N, int D, int min_child
                 int max_children, int max_depth, int seed, const int* d_table, int n_table,
                 TreeResult& out)
 {
+    TraceRange trace("rsfk tree build");
     out = TreeResult();
     if (N <= 0 || D <= 0) return ctx.fail(RSFK_ERR_ARG, "tree_build: N and D must be positive");
     if (D > 12000) return ctx.fail(RSFK_ERR_UNSUPPORTED, "tree_build: D above 12000 is not supported");
