@@ -147,7 +147,7 @@ struct Context {
     enum Slot {
         PERM_A, PERM_B, PERM_FINAL, SIDE_BITS, CHUNK_NODE_A, CHUNK_NODE_B, CHUNK_LEFT, NODE_DONE,
         NODES_A, NODES_B, NODE_SPLIT, SMALL_NODES, LEAF_START, LEAF_COUNT, COUNTERS, TABLE,
-        SNAPSHOT, EXPLORE_COUNT, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
+        SNAPSHOT, EXPLORE_COUNT, EXPLORE_CAND, ERROR_FLAG, HOST_POINTS, HOST_IDX, HOST_DIST,
         RECORDS, PLANE_NORMALS, PLANE_OFFSETS, QUERY_LEAF, QUERY_ORDER, LEAF_QUERIES, HOST_QUERIES,
         LANE_IDX, LANE_DIST, SYM_DEGREE, SYM_BLOCKS, TC_ROWS, TC_EXACT, TC_NORMS, TC_TILES, TC_COUNT, TC_STATS, TC_LATER_ROWS, TC_LATER_CAND, TC_OPEN, TC_THR0,
         PEER_IDX, PEER_DIST,

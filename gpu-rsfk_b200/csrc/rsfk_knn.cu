@@ -1114,6 +1114,186 @@ bool bucket_knn(Context& ctx, const float* d_points, int N, int D, int K, const 
     return ctx.check(cudaGetLastError(), "bucket_knn launch");
 }
 
+// ---------------------------------------------------------------------------
+// The sweep for long lists of medium-sized rows (32 < K <= 64, 64 <= D <= 128: 20 M x 128 with
+// K = 64).  There the per-warp hash set takes 16 KiB, twelve warps fit an SM, and with register
+// loads (k_explore) those twelve warps keep 48 KiB of rows in flight: 0.59 of the bandwidth that
+// random row gathers reach.  Here a point is handled in two steps.  First all its candidates are
+// gathered and made distinct (same hash set, same rule) and written to a list in global memory.
+// Then the hash set's shared memory becomes two buffers of 16 whole rows each, filled by bulk
+// copies (cp.async.bulk, one per row, completion counted on an mbarrier per buffer) while the
+// other buffer is evaluated: up to 16 KiB in flight per warp, no registers held by loads.
+// Distances are formed as k_explore's scalar routine forms them (lane l owns dimensions l, l+32,
+// ..., transposed butterfly), so the bits are the same.
+// Every wait is bounded; one that runs out raises the error flag and the warp leaves.
+// Measured on 2 M x 128, K = 64 (one B200): 241 ms per sweep against 302 ms for k_explore.
+// Tried and slower: four buffers of 8 rows with three in flight (314 ms: the work per batch of
+// eight rows, not the bytes in flight, sets the pace) and 16-byte cp.async copies with commit
+// groups instead of the bulk copies (262 ms).
+// ---------------------------------------------------------------------------
+constexpr int STAGED_WARPS = 4;
+constexpr int STAGED_ROWS = 16; // rows per buffer
+
+__device__ __forceinline__ void bulk_row_to_shared(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int KPL>
+__global__ void __launch_bounds__(32 * STAGED_WARPS, 3)
+k_explore_staged(const float* __restrict__ pts, int N, int D, int K, const int* __restrict__ old_idx,
+                 int* __restrict__ knn_idx, float* __restrict__ knn_dist, int row_begin, int row_end,
+                 int list_row0, unsigned long long* __restrict__ evaluated, int table_log2,
+                 int* __restrict__ cand_scratch, int cand_cap, int* __restrict__ error_flag)
+{
+    extern __shared__ float4 smem4[];
+    __shared__ uint64_t sBar[STAGED_WARPS][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int table_slots = 1 << table_log2;
+    // per warp: xp[D] | table_slots words: the hash set, later 2 x 16 rows of D floats
+    float* xp = reinterpret_cast<float*>(smem4) + (size_t)warp * (D + table_slots);
+    int* table = reinterpret_cast<int*>(xp + D);
+    const float* rows = xp + D;
+    const uint32_t rows_addr = tc::smem_u32(rows);
+    const uint32_t row_bytes = (uint32_t)D * 4u;
+    const uint32_t bar[2] = {tc::smem_u32(&sBar[warp][0]), tc::smem_u32(&sBar[warp][1])};
+    if (lane == 0) {
+        tc::mbar_init(bar[0], 1);
+        tc::mbar_init(bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    unsigned parity[2] = {0u, 0u};
+    int* cand = cand_scratch + (size_t)(blockIdx.x * STAGED_WARPS + warp) * cand_cap;
+
+    const int warp0 = blockIdx.x * STAGED_WARPS + warp;
+    const int n_warps = gridDim.x * STAGED_WARPS;
+    unsigned long long n_eval = 0;
+    bool alive = true;
+    for (int p = row_begin + warp0; p < row_end && alive; p += n_warps) {
+        __syncwarp();
+        // ---- the point's distinct candidates -> cand[0..n) -------------------
+        for (int t = lane; t < table_slots; t += 32) table[t] = -1;
+        WarpList<KPL> L;
+        L.load(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
+        int nb[KPL];
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            const int e = r * 32 + lane;
+            nb[r] = e < K ? old_idx[(size_t)p * K + e] : -1;
+        }
+        for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)p * D + k);
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < KPL; ++r)
+            if (L.i[r] >= 0) seen_before(table, table_log2, L.i[r]);
+        __syncwarp();
+        int n = 0;
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            for (int b0 = 0; b0 < 32; b0 += 4) {
+                if (r * 32 + b0 >= K) break;
+                // four neighbours' lists are requested together
+                int c[4][KPL];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int nbr = __shfl_sync(RSFK_FULL, nb[r], b0 + u);
+                    const bool live = r * 32 + b0 + u < K && nbr >= 0 && nbr < N;
+#pragma unroll
+                    for (int q = 0; q < KPL; ++q) {
+                        const int e = q * 32 + lane;
+                        c[u][q] = (live && e < K) ? old_idx[(size_t)nbr * K + e] : -1;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int q = 0; q < KPL; ++q) {
+                        const int v = c[u][q];
+                        bool ok = v >= 0 && v < N;
+                        if (ok) ok = !seen_before(table, table_log2, v);
+                        const unsigned mask = __ballot_sync(RSFK_FULL, ok);
+                        const int at = n + __popc(mask & ((1u << lane) - 1u));
+                        if (ok && at < cand_cap) cand[at] = v;
+                        n = min(n + __popc(mask), cand_cap);
+                    }
+            }
+        }
+        n_eval += n;
+        __syncwarp();
+        if (n == 0) continue;
+        // ---- evaluation: the hash set's memory becomes the row buffers --------
+        __threadfence_block(); // the list written above is read back by other lanes below
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        const int n_batches = (n + STAGED_ROWS - 1) / STAGED_ROWS;
+        // ids of the rows a buffer holds (lane j: row j), and of the rows it takes next
+        int id_next[2], id_cur[2] = {-1, -1};
+        id_next[0] = (lane < STAGED_ROWS && lane < n) ? cand[lane] : -1;
+        id_next[1] = (lane < STAGED_ROWS && STAGED_ROWS + lane < n) ? cand[STAGED_ROWS + lane] : -1;
+        auto issue = [&](int b) { // batch b -> buffer b & 1
+            const int h = b & 1;
+            const int m = min(STAGED_ROWS, n - STAGED_ROWS * b);
+            id_cur[h] = id_next[h];
+            if (lane == 0) tc::mbar_expect_tx(bar[h], (uint32_t)m * row_bytes);
+            __syncwarp();
+            if (lane < m)
+                bulk_row_to_shared(rows_addr + (uint32_t)(h * STAGED_ROWS + lane) * row_bytes,
+                                   pts + (size_t)id_cur[h] * D, row_bytes, bar[h]);
+            const int later = STAGED_ROWS * (b + 2) + lane;
+            id_next[h] = (lane < STAGED_ROWS && later < n) ? cand[later] : -1;
+        };
+        issue(0);
+        if (n_batches > 1) issue(1);
+        bool changed = false;
+        for (int b = 0; b < n_batches; ++b) {
+            const int h = b & 1;
+            const int m = min(STAGED_ROWS, n - STAGED_ROWS * b);
+            bool arrived = false;
+            for (unsigned it = 0; it < tc::WAIT_LIMIT && !arrived; ++it) arrived = tc::mbar_try(bar[h], parity[h]);
+            parity[h] ^= 1u;
+            if (!__all_sync(RSFK_FULL, arrived)) { // give up: wait once more for what is in flight, then leave
+                const int o = h ^ 1;
+                if (b + 1 < n_batches)
+                    for (unsigned it = 0; it < tc::WAIT_LIMIT; ++it)
+                        if (tc::mbar_try(bar[o], parity[o])) break;
+                if (lane == 0) atomicExch(error_flag, 1);
+                alive = false;
+                break;
+            }
+            const float* R = rows + (size_t)h * STAGED_ROWS * D;
+            float acc[STAGED_ROWS];
+#pragma unroll
+            for (int c = 0; c < STAGED_ROWS; ++c) acc[c] = 0.0f;
+            for (int k = lane; k < D; k += 32) {
+                const float x = xp[k];
+#pragma unroll
+                for (int c = 0; c < STAGED_ROWS; ++c) {
+                    const float df = __fsub_rn(R[(size_t)c * D + k], x);
+                    acc[c] = __fmaf_rn(df, df, acc[c]);
+                }
+            }
+            const float dsum = transposed_sum16(acc, lane);
+            const int item = item16_of_lane(lane);
+            int ci = __shfl_sync(RSFK_FULL, id_cur[h], item);
+            if (lane >= 16 || item >= m) ci = -1;
+            unsigned mask = __ballot_sync(RSFK_FULL, ci >= 0 && L.beats_threshold(dsum, ci));
+            while (mask) {
+                const int w = __ffs(mask) - 1;
+                mask &= mask - 1;
+                changed |= L.try_insert(__shfl_sync(RSFK_FULL, dsum, w), __shfl_sync(RSFK_FULL, ci, w), K, lane);
+            }
+            __syncwarp(); // the buffer's rows are read; it may be filled again
+            if (b + 2 < n_batches) issue(b + 2);
+        }
+        if (alive && changed)
+            L.store(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
+    }
+    if (lane == 0 && n_eval) atomicAdd(evaluated, n_eval);
+}
+
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
                    int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0)
 {
@@ -1129,6 +1309,25 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
     unsigned long long* counter = ctx.explore_counter();
     if (!counter) return false;
     const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
+    // long lists of medium rows: rows staged in shared memory by bulk copies (k_explore_staged)
+    if (vec4 && K > 32 && K <= 64 && D >= 64 && 32 * D <= (1 << shape.table_log2)) {
+        const size_t st_smem = sizeof(float) * (size_t)STAGED_WARPS * (D + (1 << shape.table_log2));
+        long long st_blocks = (rows + STAGED_WARPS - 1) / STAGED_WARPS;
+        if (st_blocks > ctx.sm_count * 3) st_blocks = ctx.sm_count * 3;
+        const int cand_cap = K * K;
+        int* cand = (int*)ctx.scratch(Context::EXPLORE_CAND, sizeof(int) * (size_t)st_blocks * STAGED_WARPS * cand_cap);
+        int* flag = ctx.error_flag();
+        if (!cand || !flag) return false;
+        auto kern = k_explore_staged<2>;
+        if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem),
+                       "explore smem attribute"))
+            return false;
+        kern<<<(int)st_blocks, 32 * STAGED_WARPS, st_smem, ctx.stream>>>(d_points, N, D, K, d_old_idx, d_idx, d_dist,
+                                                                        row_begin, row_end, list_row0, counter,
+                                                                        shape.table_log2, cand, cand_cap, flag);
+        count_launches(1);
+        return ctx.check(cudaGetLastError(), "explore launch");
+    }
     RSFK_DISPATCH_KPL(K, {
         auto kern = vec4 ? k_explore<KPL, true> : k_explore<KPL, false>;
         if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),

@@ -157,7 +157,9 @@ def test_sort_rows_canonicalises(forest, oracle):
     np.testing.assert_array_equal(d_dist.cpu().numpy(), rdist)
 
 
-@pytest.mark.parametrize("N,D,K", [(20000, 32, 16), (5000, 100, 32), (3000, 128, 64), (4000, 2, 32), (2000, 50, 7)])
+@pytest.mark.parametrize("N,D,K", [(20000, 32, 16), (5000, 100, 32), (3000, 128, 64), (4000, 2, 32), (2000, 50, 7),
+                                   # long lists of medium rows: the sweep that stages rows in shared memory
+                                   (2500, 100, 64), (2000, 64, 40), (1500, 96, 33), (1800, 128, 50)])
 def test_explore_bit_exact(forest, oracle, N, D, K):
     X = _uniform(N, D, 6)
     idx, dist = oracle.init_lists(N, K)
@@ -174,8 +176,8 @@ def test_explore_bit_exact(forest, oracle, N, D, K):
         idx, dist = ridx, rdist
 
 
-def test_explore_skips_empty_slots_and_row_range(forest, oracle):
-    N, D, K = 3000, 24, 20
+@pytest.mark.parametrize("N,D,K", [(3000, 24, 20), (3000, 72, 40)])
+def test_explore_skips_empty_slots_and_row_range(forest, oracle, N, D, K):
     X = _uniform(N, D, 8)
     idx, dist = oracle.init_lists(N, K)
     tr = oracle.build_tree(X, 8, 16, seed=0)     # buckets smaller than K leave -1 slots
