@@ -653,14 +653,20 @@ void knn_on_devices(const std::vector<int>& devs, int n_trees, int K, int N, int
             if (copier->copy(d, h, n, to_device, dev)) return true;
             return c.fail(RSFK_ERR_CUDA, std::string(what) + " failed");
         };
-        // 1. this GPU's slice of the points; the caller's lists for its rows
+        // 1. this GPU's slice of the points
         ok = ok && copy(me.d_points + (size_t)lo * D, points + (size_t)lo * D, sizeof(float) * (size_t)rows * D, true,
                         "H2D points");
-        ok = ok && copy(peer_idx + stage_elems * (G - 1), knn_indices + (size_t)lo * K, sizeof(int) * (size_t)rows * K,
-                        true, "H2D lists");
-        ok = ok && copy(peer_dist + stage_elems * (G - 1), knn_sqr_distances + (size_t)lo * K,
-                        sizeof(float) * (size_t)rows * K, true, "H2D lists");
         if (!barrier.wait(ok)) return;
+        // the caller's lists for this GPU's rows are needed at the merge only: they travel beside the trees
+        bool lists_up = true;
+        std::thread uploader([&] {
+            cudaSetDevice(dev);
+            if (rows > 0) // the context's status belongs to the GPU's own thread: only the flag is set here
+                lists_up = copier->copy(peer_idx + stage_elems * (G - 1), knn_indices + (size_t)lo * K,
+                                        sizeof(int) * (size_t)rows * K, true, dev) &&
+                           copier->copy(peer_dist + stage_elems * (G - 1), knn_sqr_distances + (size_t)lo * K,
+                                        sizeof(float) * (size_t)rows * K, true, dev);
+        });
         // 2. the other slices from their owners
         for (int p = 0; p < G && ok; ++p) {
             if (p == g) continue;
@@ -676,6 +682,8 @@ void knn_on_devices(const std::vector<int>& devs, int n_trees, int K, int N, int
         ok = ok && run_forest(me.h, me.d_points, N, D, K, me.n_trees, g, G, min_children, max_children, max_depth,
                               seed, me.d_idx, me.d_dist, me.log.data(), g == 0 ? verbose : 0, nullptr);
         ok = ok && c.check(cudaStreamSynchronize(c.stream), "forest");
+        uploader.join();
+        if (!lists_up) ok = c.fail(RSFK_ERR_CUDA, "H2D lists failed");
         if (!barrier.wait(ok)) return;
         if (g == 0) t_forest = now_s() - t0;
         // 4. rows [lo, hi) of everybody's lists, merged in place over this GPU's own
