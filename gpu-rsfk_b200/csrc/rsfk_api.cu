@@ -610,13 +610,15 @@ void knn_on_devices(const std::vector<int>& devs, int n_trees, int K, int N, int
                 g_last_message = "no usable CUDA device";
                 return;
             }
-            // direct loads from the other GPUs' memory where the machine allows it
-            for (int p = 0; p < G; ++p) {
-                int can = 0;
-                if (p != g && cudaDeviceCanAccessPeer(&can, devs[g], devs[p]) == cudaSuccess && can)
-                    if (cudaDeviceEnablePeerAccess(devs[p], 0) != cudaSuccess) cudaGetLastError();
-            }
             it = g_device_ctx.emplace(devs[g], h).first;
+        }
+        // direct copies from the other GPUs' memory where the machine allows it (every call: the
+        // list of devices may have grown; asking again for access that exists is an error to forget)
+        cudaSetDevice(devs[g]);
+        for (int p = 0; p < G; ++p) {
+            int can = 0;
+            if (p != g && cudaDeviceCanAccessPeer(&can, devs[g], devs[p]) == cudaSuccess && can)
+                if (cudaDeviceEnablePeerAccess(devs[p], 0) != cudaSuccess) cudaGetLastError();
         }
         if (!g_device_copier.count(devs[g])) g_device_copier[devs[g]] = new StagedCopier();
         share[g].h = it->second;
