@@ -805,8 +805,13 @@ void rsfk_release_memory(void)
 int rsfk_set_devices(int n, const int* devices)
 {
     std::lock_guard<std::mutex> lock(g_mutex);
+    if (n < 0 || n > 8 || (n > 0 && !devices)) return RSFK_ERR_ARG;
+    if (n == 0) { // back to one GPU; needs no device to say so
+        g_devices.clear();
+        return RSFK_OK;
+    }
     int count = 0;
-    if (n < 0 || n > 8 || (n > 0 && !devices) || cudaGetDeviceCount(&count) != cudaSuccess) return RSFK_ERR_ARG;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) return RSFK_ERR_ARG;
     for (int i = 0; i < n; ++i)
         if (devices[i] < 0 || devices[i] >= count) return RSFK_ERR_ARG;
     g_devices.assign(devices, devices + n);

@@ -42,6 +42,25 @@ def test_status_entry_points_without_a_gpu():
     L.rsfk_free(None)
 
 
+def test_device_list_arguments_without_a_gpu():
+    """rsfk_set_devices: an empty list (back to one GPU) needs no device; impossible lists are refused."""
+    import gpu_rsfk
+    from gpu_rsfk import _lib
+    L = _lib.load()
+    assert L.rsfk_set_devices(0, None) == 0
+    gpu_rsfk.set_devices(None)
+    gpu_rsfk.set_devices([])
+    three = (ctypes.c_int * 3)(0, 1, 2)
+    assert L.rsfk_set_devices(-1, three) == 2           # invalid argument
+    assert L.rsfk_set_devices(9, three) == 2
+    assert L.rsfk_set_devices(3, None) == 2
+    many = (ctypes.c_int * 2)(0, 1000)
+    assert L.rsfk_set_devices(2, many) == 2             # no such device (or no device at all)
+    with pytest.raises(ValueError):
+        gpu_rsfk.set_devices([0, 1000])
+    assert L.rsfk_set_devices(0, None) == 0
+
+
 def test_ann_entry_point_refuses_null_buffers():
     from gpu_rsfk import _lib
     _lib.load()
