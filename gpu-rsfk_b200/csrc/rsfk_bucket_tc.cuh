@@ -832,9 +832,9 @@ __global__ void k_tc_open_tiles(const Tile* __restrict__ tiles, const int* __res
 // evaluates them exactly and merges them.  Every row occurs at most once per tree, so
 // no two warps touch one list.  later_cand[slot][0..n) are rows in leaf order.
 // ---------------------------------------------------------------------------
-constexpr int LATER_WARPS = 8;
+constexpr int LATER_WARPS = 4;
 template <int KPL, bool VEC4>
-__global__ void __launch_bounds__(32 * LATER_WARPS, VEC4 ? 2 : 1)
+__global__ void __launch_bounds__(32 * LATER_WARPS, VEC4 ? 6 : 1)
 k_tc_later(const float* __restrict__ rows_exact, int D, int K, const int* __restrict__ perm,
            const int* __restrict__ later_count, const int* __restrict__ later_rows,
            const int* __restrict__ later_cand, int* __restrict__ knn_idx, float* __restrict__ knn_dist)
@@ -870,15 +870,14 @@ k_tc_later(const float* __restrict__ rows_exact, int D, int K, const int* __rest
         L.load(knn_idx + (size_t)self * K, knn_dist + (size_t)self * K, K, lane);
         __syncwarp();
         bool changed = false;
-        // sixteen candidates at a time: four (or two) rows per lane group and two (or four) k-steps
-        // requested together, so that few dependent load rounds are left (and registers for 16 warps per SM)
-        for (int base = 0; base < qn; base += (VEC4 ? 16 : 32)) {
-            const int m = min(qn - base, VEC4 ? 16 : 32);
+        // eight candidates at a time: two rows per lane group and four k-steps requested together, so
+        // that few dependent load rounds are left, in few enough registers for 24 warps per SM
+        for (int base = 0; base < qn; base += (VEC4 ? 8 : 32)) {
+            const int m = min(qn - base, VEC4 ? 8 : 32);
             int item;
             float dsum;
             if (VEC4)
-                dsum = m <= 8 ? explore_dist_few_vec4<2, 4>(rows_exact, D, xp, queue + base, m, lane, item)
-                              : explore_dist_few_vec4<4, 2>(rows_exact, D, xp, queue + base, m, lane, item);
+                dsum = explore_dist_few_vec4<2, 4>(rows_exact, D, xp, queue + base, m, lane, item);
             else
                 dsum = explore_dist32_scalar(rows_exact, D, xp, queue + base, m, lane, item);
             const int ci = item < m ? perm[queue[base + item]] : -1;

@@ -1041,7 +1041,7 @@ static bool bucket_knn_tc(Context& ctx, const float* d_points, int N, int D, int
                        "bucket_knn_tc smem attribute"))
             return false;
         int per_sm = (int)(200 * 1024 / (later_smem + 1024));
-        per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+        per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
         const long long want = ((long long)N + tc::LATER_WARPS - 1) / tc::LATER_WARPS;
         const int later_grid = (int)(want < (long long)ctx.sm_count * per_sm ? want : (long long)ctx.sm_count * per_sm);
         later<<<later_grid, 32 * tc::LATER_WARPS, later_smem, st>>>(rows_exact, D, K, tree.perm, later_count,
