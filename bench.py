@@ -359,7 +359,8 @@ def run_ours(args, w):
                  "tree_project": "k_project_wide", "tree_level_rest": "k_decide + k_scatter + host read-back",
                  "tree_subtrees": "k_subtree", "merge_lists": "k_merge_lists",
                  # the library stages rows in shared memory for long lists of medium rows (rsfk_knn.cu)
-                 "explore": "k_explore_staged" if (32 < K <= 64 and 64 <= D <= 128 and D % 4 == 0) else "k_explore"}
+                 "explore": "k_explore_staged" if (32 < K <= 64 and 64 <= D <= 128 and D % 4 == 0) else
+                            ("k_explore_wide" if (K <= 32 and 512 <= D <= 1950 and D % 4 == 0) else "k_explore")}
     traffic_unit = NCU_TRAFFIC_PER_POINT.get(dom)
     roofline = dict(bound="hbm", kernel=kernel_of[dom], achieved=phases[dom]["gbs"], peak=peak_gbs,
                     unit="GB/s", frac=(phases[dom]["gbs"] or 0) / peak_gbs, peak_kind=peak_kind,

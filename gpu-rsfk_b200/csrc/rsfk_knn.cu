@@ -1294,6 +1294,140 @@ k_explore_staged(const float* __restrict__ pts, int N, int D, int K, const int* 
     if (lane == 0 && n_eval) atomicAdd(evaluated, n_eval);
 }
 
+// ---------------------------------------------------------------------------
+// The sweep for wide rows (K <= 32, rows of 2 KiB and more: 1 M x 960).  The same two steps as
+// k_explore_staged -- a point's distinct candidates are listed first (here in shared memory),
+// then their rows come into shared memory by bulk copies -- but a buffer is ONE row and a warp
+// has NBUF of them (the hash set's memory and what eight warps per SM instead of sixteen leave
+// free): NBUF - 1 rows of 4 D bytes are in flight while one is evaluated, against 4 KiB per warp
+// with register loads.  A row is evaluated by the whole warp in the reference's order (lane l
+// takes dimensions l, l+32, ..., xor butterfly), one candidate at a time.  Every wait is bounded;
+// one that runs out raises the error flag and the warp leaves.
+// ---------------------------------------------------------------------------
+constexpr int WIDE_WARPS = 4;
+constexpr int WIDE_CAND = 1024; // K * K for K <= 32
+
+template <int NBUF>
+__global__ void __launch_bounds__(32 * WIDE_WARPS, 2)
+k_explore_wide(const float* __restrict__ pts, int N, int D, int K, const int* __restrict__ old_idx,
+               int* __restrict__ knn_idx, float* __restrict__ knn_dist, int row_begin, int row_end,
+               int list_row0, unsigned long long* __restrict__ evaluated, int table_log2,
+               int area_floats, int* __restrict__ error_flag)
+{
+    extern __shared__ float4 smem4[];
+    __shared__ uint64_t sBar[WIDE_WARPS][NBUF];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // per warp: xp[D] | cand[WIDE_CAND] | area: the hash set (1 << table_log2 words), later NBUF rows of D floats
+    float* xp = reinterpret_cast<float*>(smem4) + (size_t)warp * (D + WIDE_CAND + area_floats);
+    int* cand = reinterpret_cast<int*>(xp + D);
+    int* table = cand + WIDE_CAND;
+    const float* rows = reinterpret_cast<const float*>(table);
+    const uint32_t rows_addr = tc::smem_u32(rows);
+    const uint32_t row_bytes = (uint32_t)D * 4u;
+    uint32_t bar[NBUF];
+    unsigned parity[NBUF];
+#pragma unroll
+    for (int u = 0; u < NBUF; ++u) {
+        bar[u] = tc::smem_u32(&sBar[warp][u]);
+        parity[u] = 0u;
+        if (lane == 0) tc::mbar_init(bar[u], 1);
+    }
+    if (lane == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+    const int table_slots = 1 << table_log2;
+
+    const int warp0 = blockIdx.x * WIDE_WARPS + warp;
+    const int n_warps = gridDim.x * WIDE_WARPS;
+    unsigned long long n_eval = 0;
+    bool alive = true;
+    for (int p = row_begin + warp0; p < row_end && alive; p += n_warps) {
+        __syncwarp();
+        // ---- the point's distinct candidates -> cand[0..n) -------------------
+        for (int t = lane; t < table_slots; t += 32) table[t] = -1;
+        WarpList<1> L;
+        L.load(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
+        const int nb = lane < K ? old_idx[(size_t)p * K + lane] : -1;
+        for (int k = lane; k < D; k += 32) xp[k] = __ldg(pts + (size_t)p * D + k);
+        __syncwarp();
+        if (L.i[0] >= 0) seen_before(table, table_log2, L.i[0]);
+        __syncwarp();
+        int n = 0;
+        for (int b0 = 0; b0 < K; b0 += 8) {
+            int c[8]; // eight neighbours' lists are requested together
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int nbr = __shfl_sync(RSFK_FULL, nb, min(b0 + u, 31));
+                const bool live = b0 + u < K && nbr >= 0 && nbr < N;
+                c[u] = (live && lane < K) ? old_idx[(size_t)nbr * K + lane] : -1;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int v = c[u];
+                bool ok = v >= 0 && v < N;
+                if (ok) ok = !seen_before(table, table_log2, v);
+                const unsigned mask = __ballot_sync(RSFK_FULL, ok);
+                const int at = n + __popc(mask & ((1u << lane) - 1u));
+                if (ok && at < WIDE_CAND) cand[at] = v;
+                n = min(n + __popc(mask), WIDE_CAND);
+            }
+        }
+        n_eval += n;
+        __syncwarp();
+        if (n == 0) continue;
+        // ---- evaluation: the hash set's memory becomes the row buffers --------
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        auto issue = [&](int b, int u) { // candidate b -> buffer u
+            if (lane == 0) {
+                tc::mbar_expect_tx(bar[u], row_bytes);
+                bulk_row_to_shared(rows_addr + (uint32_t)u * row_bytes, pts + (size_t)cand[b] * D, row_bytes, bar[u]);
+            }
+        };
+#pragma unroll
+        for (int u = 0; u < NBUF - 1; ++u)
+            if (u < n) issue(u, u);
+        bool changed = false;
+        for (int b0 = 0; b0 < n && alive; b0 += NBUF) {
+#pragma unroll
+            for (int u = 0; u < NBUF; ++u) {
+                const int b = b0 + u;
+                if (b >= n || !alive) break;
+                // all but one buffer in flight: the one candidate b-1 was read from is free again
+                if (b + NBUF - 1 < n) issue(b + NBUF - 1, (u + NBUF - 1) % NBUF);
+                const int ci = cand[b];
+                bool arrived = false;
+                for (unsigned it = 0; it < tc::WAIT_LIMIT && !arrived; ++it) arrived = tc::mbar_try(bar[u], parity[u]);
+                parity[u] ^= 1u;
+                if (!__all_sync(RSFK_FULL, arrived)) {
+                    // give up: wait once more (bounded) for the copies still in flight, then leave
+#pragma unroll
+                    for (int o = 0; o < NBUF; ++o) {
+                        const int ob = b + ((o - u + NBUF) % NBUF);
+                        if (o != u && ob < n)
+                            for (unsigned it = 0; it < tc::WAIT_LIMIT; ++it)
+                                if (tc::mbar_try(bar[o], parity[o])) break;
+                    }
+                    if (lane == 0) atomicExch(error_flag, 1);
+                    alive = false;
+                    break;
+                }
+                const float* R = rows + (size_t)u * D;
+                float acc = 0.0f;
+                for (int k = lane; k < D; k += 32) {
+                    const float df = __fsub_rn(R[k], xp[k]);
+                    acc = __fmaf_rn(df, df, acc);
+                }
+                const float dsum = butterfly_sum(acc);
+                if (L.beats_threshold(dsum, ci)) changed |= L.try_insert(dsum, ci, K, lane);
+                __syncwarp(); // the buffer's row is read; it may be filled again
+            }
+        }
+        if (alive && changed)
+            L.store(knn_idx + (size_t)(p - list_row0) * K, knn_dist + (size_t)(p - list_row0) * K, K, lane);
+    }
+    if (lane == 0 && n_eval) atomicAdd(evaluated, n_eval);
+}
+
 bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, const int* d_old_idx,
                    int* d_idx, float* d_dist, int row_begin, int row_end, int list_row0)
 {
@@ -1309,6 +1443,28 @@ bool explore_sweep(Context& ctx, const float* d_points, int N, int D, int K, con
     unsigned long long* counter = ctx.explore_counter();
     if (!counter) return false;
     const bool vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_points) & 15) == 0);
+    // wide rows: one row per buffer, several buffers per warp (k_explore_wide)
+    if (vec4 && K <= 32 && D >= 512 && D <= 1950) {
+        const int per_warp = 110 * 1024 / 4 / WIDE_WARPS;              // floats a warp may use: two CTAs per SM
+        const int fit = (per_warp - D - WIDE_CAND) / D;
+        const int nbuf = fit >= 5 ? 5 : (fit >= 3 ? 3 : 2);
+        const int table_slots = 1 << shape.table_log2;
+        const int area = nbuf * D > table_slots ? nbuf * D : table_slots;
+        const size_t w_smem = sizeof(float) * (size_t)WIDE_WARPS * (D + WIDE_CAND + area);
+        long long w_blocks = (rows + WIDE_WARPS - 1) / WIDE_WARPS;
+        if (w_blocks > ctx.sm_count * 2) w_blocks = ctx.sm_count * 2;
+        int* flag = ctx.error_flag();
+        if (!flag) return false;
+        auto kern = nbuf == 5 ? k_explore_wide<5> : (nbuf == 3 ? k_explore_wide<3> : k_explore_wide<2>);
+        if (!ctx.check(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w_smem),
+                       "explore smem attribute"))
+            return false;
+        kern<<<(int)w_blocks, 32 * WIDE_WARPS, w_smem, ctx.stream>>>(d_points, N, D, K, d_old_idx, d_idx, d_dist,
+                                                                    row_begin, row_end, list_row0, counter,
+                                                                    shape.table_log2, area, flag);
+        count_launches(1);
+        return ctx.check(cudaGetLastError(), "explore launch");
+    }
     // long lists of medium rows: rows staged in shared memory by bulk copies (k_explore_staged)
     if (vec4 && K > 32 && K <= 64 && D >= 64 && 32 * D <= (1 << shape.table_log2)) {
         const size_t st_smem = sizeof(float) * (size_t)STAGED_WARPS * (D + (1 << shape.table_log2));

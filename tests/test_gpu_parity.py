@@ -159,7 +159,9 @@ def test_sort_rows_canonicalises(forest, oracle):
 
 @pytest.mark.parametrize("N,D,K", [(20000, 32, 16), (5000, 100, 32), (3000, 128, 64), (4000, 2, 32), (2000, 50, 7),
                                    # long lists of medium rows: the sweep that stages rows in shared memory
-                                   (2500, 100, 64), (2000, 64, 40), (1500, 96, 33), (1800, 128, 50)])
+                                   (2500, 100, 64), (2000, 64, 40), (1500, 96, 33), (1800, 128, 50),
+                                   # wide rows: one row per shared-memory buffer, five, three or two buffers per warp
+                                   (1500, 960, 32), (1200, 512, 16), (900, 1024, 20), (700, 1500, 8), (600, 1900, 5)])
 def test_explore_bit_exact(forest, oracle, N, D, K):
     X = _uniform(N, D, 6)
     idx, dist = oracle.init_lists(N, K)
@@ -176,7 +178,7 @@ def test_explore_bit_exact(forest, oracle, N, D, K):
         idx, dist = ridx, rdist
 
 
-@pytest.mark.parametrize("N,D,K", [(3000, 24, 20), (3000, 72, 40)])
+@pytest.mark.parametrize("N,D,K", [(3000, 24, 20), (3000, 72, 40), (2500, 640, 20)])
 def test_explore_skips_empty_slots_and_row_range(forest, oracle, N, D, K):
     X = _uniform(N, D, 8)
     idx, dist = oracle.init_lists(N, K)
