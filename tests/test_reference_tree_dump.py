@@ -132,3 +132,23 @@ def test_gpu_tree_replaying_the_reference_pairs_has_the_reference_buckets(oracle
     perm, ls, lc = f.tree_export()
     got = {frozenset(int(v) for v in perm[s:s + c]) for s, c in zip(ls, lc)}
     assert got == t.buckets
+
+
+def test_dump_patch_applies_to_the_reference_driver(oracle, tmp_path):
+    """The script that adds the tree dump to a scratch copy of the reference's driver finds its two
+    anchors exactly once (skipped where the reference's sources are not on this machine)."""
+    import subprocess
+    import sys
+    ref = oracle.reference_root()
+    if ref is None:
+        pytest.skip("reference sources not on this machine")
+    out = tmp_path / "rsfk.cu"
+    script = os.path.join(os.path.dirname(HERE), "oracle", "patch_ref_dump.py")
+    subprocess.run([sys.executable, script, ref, str(out)], check=True)
+    patched = out.read_text()
+    original = open(os.path.join(ref, "src", "rsfk.cu")).read()
+    assert patched.count("rsfk_b200_dump_tree(") == 2          # the definition and the one call
+    assert patched.count('getenv("RSFK_DUMP_TREE")') == 1
+    # nothing of the reference is removed: taking the two additions out gives the original back
+    added = len(patched) - len(original)
+    assert added > 0 and patched.replace("\r", "").count("\n") > original.count("\n")
