@@ -61,6 +61,11 @@ NCU_TRAFFIC_PER_POINT = {"explore": 58.81e9 / 400_000, "bucket_knn": 359.7e6 / 4
                          "tree_project": 174.1e6 / 400_000, "tree_subtrees": 702.5e6 / 400_000}
 
 
+# (DRAM read + write bytes) / algorithmic bytes of the sweep kernel in the committed captures
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {("c4", "explore"): ((492.004e9 + 0.011e9) / 615.675e9, "300 000-point"),
+                                    ("c5", "explore"): ((975.550e9 + 12.547e9) / 1082.055e9, "2 000 000-point")}
+
+
 def make_points(w, n_override=None):
     N = n_override or w["N"]
     D = w["D"]
@@ -371,6 +376,14 @@ def run_ours(args, w):
                     if traffic_unit and args.workload == "c2" else None,
                     algorithmic_bytes_per_launch=phases[dom]["bytes_per_launch"],
                     ms_per_launch=phases[dom]["ms_per_launch"])
+    # the sweeps of the wide-row and long-list configurations: DRAM bytes of an ncu capture of a smaller
+    # case (summaries under profiles/) per algorithmic byte, scaled by this launch's algorithmic bytes
+    ratio = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get((args.workload, dom))
+    if ratio is not None and roofline["traffic"] is None:
+        roofline["traffic"] = ratio[0] * phases[dom]["bytes_per_launch"]
+        roofline["traffic_from"] = ("ncu capture of a %s case (DRAM bytes per algorithmic byte %.3f) scaled by the "
+                                    "algorithmic bytes of this launch (an under-estimate where the L2 hit rate "
+                                    "falls with N)" % (ratio[1], ratio[0]))
     tensor_roofline = None
     if "tensor_tflops" in phases["bucket_knn"]:
         tf32_peak = 0.5 * float(peaks.get("bf16_tflops", 1590.0))
