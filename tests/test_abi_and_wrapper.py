@@ -127,3 +127,18 @@ def test_no_gpu_means_loud_failure():
     from gpu_rsfk.device import DeviceForest
     with pytest.raises(RSFKLibraryError):
         DeviceForest()
+
+
+def test_bench_names_the_larger_kernel_when_two_phases_tie():
+    """bench.py's roofline names the phase with the most kernel time; phases within 2 % count as tied
+    and the one with the fewest launches wins, so the line does not flip between runs."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("rsfk_bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    phases = {"bucket_knn": {"total_ms": 59.0, "launches": 50.0}, "tree_project": {"total_ms": 66.2, "launches": 753.0},
+              "tree_level_rest": {"total_ms": 99.0, "launches": 753.0}, "explore": {"total_ms": 66.0, "launches": 1}}
+    assert bench.dominant_phase(phases) == "explore"
+    phases["explore"]["total_ms"] = 60.0
+    assert bench.dominant_phase(phases) == "tree_project"
